@@ -1,0 +1,192 @@
+/*
+ * CPU oracle for the MTP-4 speculative decode step -- TEST INFRASTRUCTURE ONLY.
+ *
+ * This is a scalar restatement, on the host, of the arithmetic and control
+ * flow of quantum-llm's exact-decode path.  It exists so that the CUDA path
+ * can be checked against it; nothing in the shipped library links, loads or
+ * calls it.  Only tests, the smoke check and the CPU-baseline leg of the
+ * benchmark may use it.
+ *
+ * Reference files restated (paths inside the quantum-llm project):
+ *   runtime/src/speculative_sampling.cpp              sampler, counter RNG
+ *   runtime/src/cuda/transformer_kernels.cu:1917-2002 NVFP4 fake-quant + GEMV
+ *   runtime/src/cuda/transformer_kernels.cu:229-288   Q4H record store
+ *   runtime/src/cuda/transformer_kernels.cu:601-625   Q8 record store
+ *   runtime/src/cuda/transformer_kernels.cu:4391-4976 Q8 query + Q4H attention
+ *   runtime/src/cuda/transformer_kernels.cu:4985-5340 Q8-KV attention (BF16 MMA)
+ *   runtime/src/cuda/transformer_kernels.cu:6610-6665 exact-F16 softmax
+ *   runtime/src/cuda/transformer_kernels.cu:5741-5798 split combine
+ *   runtime/src/cuda/transformer_kernels.cu:7059-7178 argmax / top-k tie rules
+ *   runtime/tools/dense_fp4_provider.cpp:8529-8852    run_target / run_mtp / rollout
+ *   runtime/tools/dense_fp4_provider.cpp:11011-11318  sync batch / execute_exact_decode
+ *
+ * Parity pin status: the sampler, the counter RNG and the E2M1/E4M3 decoders
+ * are pinned against the reference's own code and vectors (see tests/);
+ * the whole-step token sequences are "parity unpinned" because the reference
+ * holds no end-to-end vector for its MTP loop.
+ */
+#ifndef QLLM_ORACLE_H_
+#define QLLM_ORACLE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { QO_KV_F16 = 0, QO_KV_Q4H = 1, QO_KV_Q8 = 2 };
+
+typedef struct qo_matrix {
+  const uint8_t* codes;   /* [rows, cols/2], low nibble = even column */
+  const uint8_t* scales;  /* [rows, cols/16] E4M3FN */
+  float weight_scale;     /* multiplier applied at run time (1 / stored divisor) */
+  float input_scale;      /* activation global scale (multiplier before E4M3) */
+  uint32_t rows;
+  uint32_t cols;
+} qo_matrix;
+
+typedef struct qo_block {
+  const float* input_norm;  /* [hidden] */
+  qo_matrix qkv;            /* [(q+2kv)*head_dim, hidden]: q rows, k rows, v rows */
+  qo_matrix o;              /* [hidden, q*head_dim] */
+  const float* post_norm;   /* [hidden] */
+  qo_matrix gate_up;        /* [2*ffn, hidden]: gate rows then up rows */
+  qo_matrix down;           /* [hidden, ffn] */
+} qo_block;
+
+typedef struct qo_config {
+  uint32_t layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, draft_vocab;
+  uint32_t rotary_dim;
+  float rope_theta;
+  float eps;
+  uint32_t page_tokens;
+  uint32_t kv_encoding;      /* target KV: QO_KV_* */
+  uint32_t mtp_kv_encoding;  /* draft KV */
+  uint32_t activation_bf16;  /* round at the reference's BF16 points */
+  uint32_t draft_depth;      /* D (<= 4) */
+  uint32_t max_context;
+  uint32_t split_tokens;     /* attention split length (multiple of 32) */
+} qo_config;
+
+typedef struct qo_weights {
+  const uint16_t* embedding;  /* [vocab, hidden] bf16 bits */
+  const qo_block* layers;     /* [layers] */
+  const float* final_norm;
+  qo_matrix head;             /* [vocab, hidden] */
+  const float* mtp_embedding_norm;
+  const float* mtp_hidden_norm;
+  qo_matrix mtp_fusion;       /* [hidden, 2*hidden] */
+  qo_block mtp_block;
+  const float* mtp_draft_norm;
+} qo_weights;
+
+typedef struct qo_request {
+  uint64_t seed;
+  uint32_t temperature_ppm; /* 0 = greedy */
+  uint32_t top_p_ppm;
+  uint32_t top_k;           /* 1..64 when temperature_ppm != 0 */
+  uint32_t min_p_ppm;
+  uint32_t context_limit;   /* reserved_context_tokens */
+} qo_request;
+
+typedef struct qo_step_result {
+  uint32_t emitted[8];
+  uint32_t emitted_count;
+  uint32_t next_token;
+  uint32_t positions_advanced;
+  uint32_t rejected; /* 1 when next_token came from the residual distribution */
+} qo_step_result;
+
+typedef struct qo_session qo_session;
+
+/* ---- number formats ------------------------------------------------ */
+float qo_e2m1_decode(uint8_t code);
+uint8_t qo_e2m1_encode(float value);
+float qo_e4m3_decode(uint8_t code);
+uint8_t qo_e4m3_encode(float value);
+float qo_bf16_round(float value);
+uint16_t qo_f16_bits(float value);
+float qo_f16_value(uint16_t bits);
+
+/* ---- NVFP4 ----------------------------------------------------------- */
+void qo_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols,
+                               float global_scale, uint8_t* codes,
+                               uint8_t* scales);
+void qo_nvfp4_dequant(const qo_matrix* m, float* out);
+void qo_nvfp4_fake_quant(const float* x, uint32_t rows, uint32_t cols,
+                         float global_scale, float* out);
+void qo_nvfp4_gemv(const qo_matrix* m, uint32_t first_row, uint32_t row_count,
+                   const float* x, uint32_t batch, float* y);
+
+/* ---- layer pieces ---------------------------------------------------- */
+void qo_rmsnorm(const float* x, const float* w, float* out, uint32_t rows,
+                uint32_t cols, float eps);
+void qo_rope(float* heads, uint32_t rows, uint32_t head_count,
+             uint32_t head_dim, uint32_t rotary_dim, float theta,
+             const uint32_t* positions, int act_bf16);
+size_t qo_kv_layer_bytes(uint32_t encoding, uint32_t page_tokens,
+                         uint32_t kv_heads, uint32_t head_dim);
+void qo_kv_store(uint32_t encoding, uint8_t* const* pages, size_t layer_offset,
+                 uint32_t page_tokens, uint32_t kv_heads, uint32_t head_dim,
+                 const float* key, const float* value, uint32_t rows,
+                 uint32_t row_stride, uint32_t first_cache_position);
+void qo_attention(uint32_t encoding, const uint8_t* const* pages,
+                  size_t layer_offset, uint32_t page_tokens, const float* query,
+                  uint32_t query_row_stride, uint32_t rows,
+                  uint32_t first_context_tokens, uint32_t q_heads,
+                  uint32_t kv_heads, uint32_t head_dim, uint32_t split_tokens,
+                  int act_bf16, float* out);
+uint32_t qo_argmax(const float* values, uint32_t count);
+void qo_topk(const float* values, uint32_t count, uint32_t k, float* out_values,
+             uint32_t* out_tokens);
+
+/* ---- sampler ---------------------------------------------------------- */
+double qo_counter_uniform(uint64_t seed, uint32_t position, uint32_t stream,
+                          uint32_t index);
+/* returns the number of retained entries, or -1 on invalid input */
+int qo_make_distribution(const float* sorted_logits,
+                         const uint32_t* sorted_tokens, uint32_t count,
+                         uint32_t temperature_ppm, uint32_t top_p_ppm,
+                         uint32_t min_p_ppm, uint32_t* out_tokens,
+                         double* out_probabilities);
+uint32_t qo_sample_distribution(const uint32_t* tokens,
+                                const double* probabilities, uint32_t count,
+                                double uniform);
+/* returns 1 accepted, 0 rejected (token = residual sample), -1 error */
+int qo_rejection_sample(uint32_t proposal, const uint32_t* target_tokens,
+                        const double* target_probabilities,
+                        uint32_t target_count, const uint32_t* draft_tokens,
+                        const double* draft_probabilities, uint32_t draft_count,
+                        double acceptance_uniform, double correction_uniform,
+                        uint32_t* token);
+
+/* ---- whole step -------------------------------------------------------- */
+qo_session* qo_session_create(const qo_config* config,
+                              const qo_weights* weights);
+void qo_session_destroy(qo_session* session);
+/* Prefill the prompt through the target in chunks of chunk_rows, prime the
+ * draft cache through synchronisation batches, pick the first token and roll
+ * out the first drafts.  Returns 0 on success. */
+int qo_prefill(qo_session* session, const uint32_t* tokens, uint32_t count,
+               uint32_t chunk_rows, const qo_request* request,
+               uint32_t* first_token);
+int qo_execute_exact_decode(qo_session* session, const qo_request* request,
+                            uint32_t guaranteed_token, uint32_t position,
+                            qo_step_result* result);
+/* inspection for parity tests */
+uint32_t qo_draft_count(const qo_session* session);
+void qo_drafts(const qo_session* session, uint32_t* tokens);
+const float* qo_last_logits(const qo_session* session); /* [rows, vocab] */
+const float* qo_last_hidden(const qo_session* session); /* [rows, hidden] */
+size_t qo_page_bytes(const qo_session* session);
+uint32_t qo_page_count(const qo_session* session);
+const uint8_t* qo_page(const qo_session* session, uint32_t index);
+size_t qo_layer_offset(const qo_session* session, uint32_t layer); /* layer == layers -> draft layer */
+uint32_t qo_mtp_length(const qo_session* session);
+const char* qo_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLLM_ORACLE_H_ */
