@@ -1,0 +1,268 @@
+/*
+ * qllm_b200 -- C ABI of the B200 (sm_100a) provider for quantum-llm's MTP-4
+ * speculative decode step.
+ *
+ * Two layers are exported:
+ *   1. kernel launchers (qllm_k_*): one call per reference launcher in
+ *      runtime/include/expert/runtime/cuda/transformer_kernels.hpp; raw device
+ *      pointers, a CUDA stream as void*, int status (0 = ok).
+ *   2. the provider (qllm_provider_*): the exact-decode subset of
+ *      expert::runtime::IOperationProvider
+ *      (runtime/include/expert/runtime/program_executor.hpp:244-370) flattened
+ *      to C: prepare_exact_decode, create_request_state,
+ *      synchronize_exact_decode_batch, execute_exact_decode.
+ *
+ * Every function returns 0 on success and a negative qllm_status otherwise;
+ * qllm_last_error() gives the message of the calling thread's last failure.
+ * No function falls back to a CPU path.
+ */
+#ifndef QLLM_B200_H_
+#define QLLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Mirrors expert::runtime::ErrorCode (runtime/include/expert/runtime/storage.hpp:17-29). */
+typedef enum qllm_status {
+  QLLM_OK = 0,
+  QLLM_CANCELLED = -1,
+  QLLM_DEADLINE_EXCEEDED = -2,
+  QLLM_BACKPRESSURE = -3,
+  QLLM_INVALID_ARGUMENT = -4,
+  QLLM_UPLOAD_FAILED = -9,
+  QLLM_INTERNAL = -10
+} qllm_status;
+
+/* PagedKvEncoding subset (runtime/src/cuda/transformer_kernels.cu:50-59). */
+enum { QLLM_KV_F16 = 0, QLLM_KV_Q4H = 1, QLLM_KV_Q8 = 2 };
+
+/* Nvfp4Block16Matrix (runtime/include/expert/runtime/cuda/transformer_kernels.hpp:47-54):
+ * codes [rows, cols/2] (low nibble = even column), scales [rows, cols/16] E4M3FN. */
+typedef struct qllm_matrix {
+  const uint8_t* codes;
+  const uint8_t* scales;
+  float weight_scale; /* multiplier: 1 / stored weight divisor */
+  float input_scale;  /* activation global scale */
+  uint32_t rows;
+  uint32_t cols;
+} qllm_matrix;
+
+typedef struct qllm_block {
+  const float* input_norm;
+  qllm_matrix qkv;     /* [(q+2kv)*head_dim, hidden] */
+  qllm_matrix o;       /* [hidden, q*head_dim] */
+  const float* post_norm;
+  qllm_matrix gate_up; /* [2*ffn, hidden] gate rows then up rows */
+  qllm_matrix down;    /* [hidden, ffn] */
+} qllm_block;
+
+/* Geometry the artifact declares (runtime/tools/dense_fp4_provider.cpp:804-960). */
+typedef struct qllm_config {
+  uint32_t layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, draft_vocab;
+  uint32_t rotary_dim;
+  float rope_theta;
+  float eps;
+  uint32_t page_tokens;
+  uint32_t kv_encoding;
+  uint32_t mtp_kv_encoding;
+  uint32_t activation_bf16;
+  uint32_t draft_depth;
+  uint32_t max_context;
+  uint32_t split_tokens;
+} qllm_config;
+
+/* Tensor roles of the exact-decode program (dense_fp4_provider.cpp:4733-4786). */
+typedef struct qllm_weights {
+  const uint16_t* embedding; /* [vocab, hidden] bf16 */
+  const qllm_block* layers;  /* host array [layers] of device (or host) pointers */
+  const float* final_norm;
+  qllm_matrix head;
+  const float* mtp_embedding_norm;
+  const float* mtp_hidden_norm;
+  qllm_matrix mtp_fusion;
+  qllm_block mtp_block;
+  const float* mtp_draft_norm;
+} qllm_weights;
+
+/* ProgramRequestContext.parameters read on this path (runtime/tools/moe_vm_runner.cpp:318-347). */
+typedef struct qllm_request {
+  uint64_t sampling_seed;
+  uint32_t sampling_temperature_ppm; /* 0 = greedy */
+  uint32_t sampling_top_p_ppm;
+  uint32_t sampling_top_k; /* 1..64 when sampling */
+  uint32_t sampling_min_p_ppm;
+  uint32_t reserved_context_tokens; /* context limit of the request */
+} qllm_request;
+
+/* ExactDecodeExecutionResult (program_executor.hpp:205-212). */
+typedef struct qllm_exact_result {
+  uint32_t emitted_tokens[8];
+  uint32_t emitted_count;
+  uint32_t next_token;
+  uint32_t positions_advanced;
+  uint32_t rejected;
+} qllm_exact_result;
+
+typedef struct qllm_provider qllm_provider;
+typedef struct qllm_request_state qllm_request_state;
+
+const char* qllm_last_error(void);
+/* Capability string and ABI the provider advertises to the registry
+ * (KernelCapability, runtime/include/expert/runtime/model_descriptor.hpp:65-80). */
+const char* qllm_capability_name(void);
+uint32_t qllm_capability_abi(void);
+
+/* ------------------------------------------------------------ provider */
+/* weights_on_device != 0: every pointer in `weights` is device memory that
+ * outlives the provider (borrowed); otherwise host memory, uploaded once
+ * (ensure_tensor, dense_fp4_provider.cpp:3486-3677).
+ * Replaces make_dense_fp4_callable_provider + prepare_exact_decode
+ * (dense_fp4_provider.cpp:11398-11499, 2865-2984). */
+int qllm_provider_create(const qllm_config* config, const qllm_weights* weights,
+                         int weights_on_device, int device, qllm_provider** out);
+void qllm_provider_destroy(qllm_provider* provider);
+/* IOperationProvider::create_request_state (program_executor.hpp:249). */
+int qllm_provider_create_request_state(qllm_provider* provider, qllm_request_state** out);
+void qllm_provider_destroy_request_state(qllm_provider* provider, qllm_request_state* state);
+/* One prefill chunk of the target program (execute_program_sequence,
+ * dense_fp4_provider.cpp:8854-9200 as driven by moe_vm_runner.cpp:679-778): stores
+ * target KV for positions first_position.. and retains the hidden rows for the
+ * following synchronisation batch. tokens: host. */
+int qllm_provider_prefill_chunk(qllm_provider* provider, qllm_request_state* state,
+                                const uint32_t* tokens, uint32_t count, uint32_t first_position);
+/* Token selected by the head for the last retained row (run_head sampling
+ * branch, dense_fp4_provider.cpp:8436-8517). */
+int qllm_provider_first_token(qllm_provider* provider, qllm_request_state* state,
+                              const qllm_request* request, uint32_t sample_position,
+                              uint32_t* token);
+/* IOperationProvider::synchronize_exact_decode_batch (program_executor.hpp:344;
+ * dense_fp4_provider.cpp:11011-11137). next_tokens: host. */
+int qllm_provider_synchronize_exact_decode_batch(qllm_provider* provider,
+                                                 qllm_request_state* state,
+                                                 const qllm_request* request,
+                                                 const uint32_t* next_tokens, uint32_t count,
+                                                 uint32_t first_target_position,
+                                                 int produce_final_draft);
+/* IOperationProvider::execute_exact_decode (program_executor.hpp:364;
+ * dense_fp4_provider.cpp:11139-11318). Completes synchronously. */
+int qllm_provider_execute_exact_decode(qllm_provider* provider, qllm_request_state* state,
+                                       const qllm_request* request, uint32_t guaranteed_token,
+                                       uint32_t position, uint32_t context_limit,
+                                       qllm_exact_result* result);
+/* Enqueue-only form for pipelined callers: `steps` consecutive steps whose
+ * guaranteed token/position come from the device-resident state; results are
+ * written to host memory after one synchronisation. */
+int qllm_provider_execute_exact_decode_steps(qllm_provider* provider, qllm_request_state* state,
+                                             const qllm_request* request, uint32_t context_limit,
+                                             uint32_t steps, qllm_exact_result* results);
+/* Counters of ExecutionProviderModule::telemetry (dense_fp4_provider.cpp:3109-, 11313-11316):
+ * out[0]=exact_calls, out[1]=accepted_drafts, out[2..6]=accepted_depth_calls[0..4],
+ * out[7]=kernel launches enqueued since creation. */
+int qllm_provider_telemetry(qllm_provider* provider, qllm_request_state* state, uint64_t* out,
+                            uint32_t count);
+/* 0 = launch kernels one by one, 1 = replay the captured CUDA graph of the step. */
+int qllm_provider_set_graph_mode(qllm_provider* provider, int enabled);
+/* GEMV implementation: 0 = CUDA-core kernel, 1 = tcgen05 block-scaled MMA kernel. */
+int qllm_provider_set_gemv_impl(qllm_provider* provider, int impl);
+
+/* inspection for parity tests (device -> host copies) */
+int qllm_provider_read_logits(qllm_provider* provider, float* out, uint32_t rows);
+/* which = 0: rows retained by the last prefill chunk; 1: target rows of the last exact step. */
+int qllm_provider_read_hidden(qllm_provider* provider, qllm_request_state* state, int which,
+                              float* out, uint32_t rows);
+int qllm_provider_read_drafts(qllm_provider* provider, qllm_request_state* state,
+                              uint32_t* tokens, uint32_t* count);
+size_t qllm_provider_page_bytes(qllm_provider* provider);
+size_t qllm_provider_layer_offset(qllm_provider* provider, uint32_t layer);
+int qllm_provider_read_page(qllm_provider* provider, qllm_request_state* state, uint32_t page,
+                            uint8_t* out);
+/* Test/bench hook without a reference counterpart: fill token positions
+ * [first, first+count) of every layer's cache (target and draft) with seeded
+ * pseudo-random records and advance the cached prefix; stands in for a long prompt. */
+int qllm_provider_fill_synthetic_kv(qllm_provider* provider, qllm_request_state* state,
+                                    uint32_t first, uint32_t count, uint64_t seed);
+
+/* ------------------------------------------------------- kernel layer */
+/* All pointers are device memory unless stated; stream is a cudaStream_t. */
+
+/* embedding_bf16_batch (transformer_kernels.cu:1901-1915) */
+int qllm_k_embedding_bf16(const uint16_t* table, const uint32_t* tokens, float* out,
+                          uint32_t rows, uint32_t hidden, uint32_t vocab, void* stream);
+/* rms_norm_batch (transformer_kernels.cu:2487-2503) */
+int qllm_k_rms_norm(const float* x, const float* weight, float* out, uint32_t rows,
+                    uint32_t cols, float eps, void* stream);
+/* nvfp4_quant_dequant_kernel (transformer_kernels.cu:1943-1968) */
+int qllm_k_nvfp4_fake_quant(const float* x, float* out, uint32_t rows, uint32_t cols,
+                            float global_scale, void* stream);
+/* nvfp4_gemv_f32_batch (transformer_kernels.cu:7970-8001): y[batch, row_count] =
+ * bf16(fakequant(x) . W[first_row..]^T).  workspace: device scratch of at least
+ * qllm_k_nvfp4_gemv_workspace_bytes(batch, cols) bytes. impl as in
+ * qllm_provider_set_gemv_impl. */
+size_t qllm_k_nvfp4_gemv_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);
+int qllm_k_nvfp4_gemv(const qllm_matrix* matrix, uint32_t first_row, uint32_t row_count,
+                      const float* x, float* y, uint32_t batch, void* workspace,
+                      size_t workspace_bytes, int impl, void* stream);
+/* Harness-owned weight quantiser on the device (formula of transformer_kernels.cu:1960-1967
+ * applied to weight rows); w is fp32 [rows, cols]. */
+int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols,
+                                  float global_scale, uint8_t* codes, uint8_t* scales,
+                                  void* stream);
+/* add_kernel / silu_product_kernel (transformer_kernels.cu:2522-2528, 2774-2783) */
+int qllm_k_add(float* dst, const float* src, uint64_t count, int bf16, void* stream);
+int qllm_k_silu_product(const float* gate_up, float* out, uint32_t rows, uint32_t ffn, int bf16,
+                        void* stream);
+/* RoPE of q and k heads in place + K/V record store
+ * (gated_gqa_qkv_rope_paged_batch_kernel without the per-head norm, 3551-3643;
+ * store_paged_kv_record 229-288 / 601-625; store_gqa_kv_fp16_to_paged 4208-4230).
+ * qkv: [rows, (q+2kv)*head_dim]; position of row r = *first_position + r;
+ * rotary position = that + rotary_offset. inv_freq: [rotary_dim/2]. */
+int qllm_k_rope_kv_store(float* qkv, uint32_t rows, uint32_t q_heads, uint32_t kv_heads,
+                         uint32_t head_dim, uint32_t rotary_dim, const float* inv_freq,
+                         const uint32_t* first_position, uint32_t position_offset,
+                         uint32_t rotary_offset, uint8_t* const* page_table, size_t layer_offset,
+                         uint32_t page_tokens, uint32_t encoding, int bf16, void* stream);
+size_t qllm_k_kv_layer_bytes(uint32_t encoding, uint32_t page_tokens, uint32_t kv_heads,
+                             uint32_t head_dim);
+/* Split attention + combine (Q4H: 4391-4976, Q8: 4985-5340, F16: 6610-6665; combine
+ * 5741-5798).  workspace >= qllm_k_attention_workspace_bytes(...). impl 0 = scalar
+ * kernel (all encodings), 1 = tensor-core kernel (Q4H). */
+size_t qllm_k_attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                                        uint32_t max_splits);
+int qllm_k_attention(uint32_t encoding, const uint8_t* const* page_table, size_t layer_offset,
+                     uint32_t page_tokens, const float* query, uint32_t query_row_stride,
+                     uint32_t rows, const uint32_t* first_position, uint32_t position_offset,
+                     uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                     uint32_t split_tokens, uint32_t max_splits, int bf16, void* workspace,
+                     float* out, int impl, void* stream);
+/* argmax_batch / topk_logits (transformer_kernels.cu:7059-7178) */
+int qllm_k_argmax(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
+                  uint32_t* out, void* stream);
+size_t qllm_k_topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k);
+int qllm_k_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
+                uint32_t k, float* out_values, uint32_t* out_tokens, void* workspace,
+                void* stream);
+/* Device form of rejection_sample / make_sampling_distribution / counter_uniform
+ * (runtime/src/speculative_sampling.cpp:52-182) over host-visible arrays, for the
+ * parity tests of the acceptance kernel: one decision per call.
+ * All pointers here are HOST memory; the call copies, runs the device kernel
+ * and copies back. Returns 1 accepted / 0 rejected / negative status. */
+int qllm_k_rejection_sample_host(uint32_t proposal, const uint32_t* target_tokens,
+                                 const double* target_probabilities, uint32_t target_count,
+                                 const uint32_t* draft_tokens, const double* draft_probabilities,
+                                 uint32_t draft_count, double acceptance_uniform,
+                                 double correction_uniform, uint32_t* token);
+int qllm_k_make_distribution_host(const float* sorted_logits, const uint32_t* sorted_tokens,
+                                  uint32_t count, uint32_t temperature_ppm, uint32_t top_p_ppm,
+                                  uint32_t min_p_ppm, uint32_t* out_tokens,
+                                  double* out_probabilities);
+int qllm_k_counter_uniform_host(uint64_t seed, uint32_t position, uint32_t stream_id,
+                                uint32_t index, double* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLLM_B200_H_ */

@@ -89,6 +89,7 @@ def lib():
             "qo_nvfp4_quantize_weights": (None, [vp, u32, u32, f32, vp, vp]),
             "qo_nvfp4_dequant": (None, [C.POINTER(Matrix), vp]),
             "qo_nvfp4_fake_quant": (None, [vp, u32, u32, f32, vp]),
+            "qo_nvfp4_quantize_activations": (None, [vp, u32, u32, f32, vp, vp]),
             "qo_nvfp4_gemv": (None, [C.POINTER(Matrix), u32, u32, vp, u32, vp]),
             "qo_rmsnorm": (None, [vp, vp, vp, u32, u32, f32]),
             "qo_rope": (None, [vp, u32, u32, u32, u32, f32, vp, C.c_int]),

@@ -145,37 +145,69 @@ void nvfp4_fake_quant(const float* x, uint32_t rows, uint32_t cols, float g, flo
     }
 }
 
-// transformer_kernels.cu:1970-2002 + launcher 7970-8001: fake-quantise the
-// activations with the matrix's input scale, FP32 dot, BF16-rounded output.
+// Activation side of the W4A4 product: per 16 values the E4M3 block scale and the
+// E2M1 codes of transformer_kernels.cu:1943-1968 (the fake-quantised value is
+// code * scale / g).
+void nvfp4_quantize_activations(const float* x, uint32_t rows, uint32_t cols, float g,
+                                uint8_t* codes, uint8_t* scales) {
+  for (uint32_t r = 0; r < rows; ++r)
+    for (uint32_t b = 0; b < cols / 16U; ++b) {
+      const float* in = x + static_cast<size_t>(r) * cols + b * 16U;
+      float amax = 0.0F;
+      for (int i = 0; i < 16; ++i) amax = std::fmax(amax, std::fabs(in[i]));
+      const uint8_t sc = e4m3_encode(std::fmin(448.0F, g * amax / 6.0F));
+      const float local = e4m3_decode(sc);
+      scales[static_cast<size_t>(r) * (cols / 16U) + b] = sc;
+      for (int i = 0; i < 16; ++i) {
+        const float scaled =
+            local == 0.0F ? 0.0F : std::fmin(6.0F, std::fmax(-6.0F, in[i] * g / local));
+        codes[static_cast<size_t>(r) * cols + b * 16U + i] = e2m1_encode(scaled);
+      }
+    }
+}
+
+// transformer_kernels.cu:1970-2002 + launcher 7970-8001: W4A4 product of the
+// fake-quantised activations with the decoded weights, BF16-rounded output.
+// The reference accumulates in FP32 in an order that is not part of its contract;
+// here the sum is formed (to double precision) exactly and rounded once:
+//   S = sum_blocks (sum_i cw_i * cx_i) * sw * sx          (every block term is exact)
+//   y = bf16(float(S) * weight_scale / input_scale)
 void nvfp4_gemv(const qo_matrix& m, uint32_t first_row, uint32_t row_count,
                 const float* x, uint32_t batch, float* y) {
-  std::vector<float> xq(static_cast<size_t>(batch) * m.cols);
-  nvfp4_fake_quant(x, batch, m.cols, m.input_scale, xq.data());
-  static const float levels[16] = {0.0F, 0.5F, 1.0F, 1.5F, 2.0F, 3.0F, 4.0F, 6.0F,
-                                   -0.0F, -0.5F, -1.0F, -1.5F, -2.0F, -3.0F, -4.0F, -6.0F};
+  const uint32_t blocks = m.cols / 16U;
+  std::vector<uint8_t> xc(static_cast<size_t>(batch) * m.cols), xs(static_cast<size_t>(batch) * blocks);
+  nvfp4_quantize_activations(x, batch, m.cols, m.input_scale, xc.data(), xs.data());
+  // twice the E2M1 value as an integer
+  static const int twice[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+  std::vector<int8_t> xi(xc.size());
+  for (size_t i = 0; i < xc.size(); ++i) xi[i] = static_cast<int8_t>(twice[xc[i]]);
+  std::vector<float> xsf(xs.size());
+  for (size_t i = 0; i < xs.size(); ++i) xsf[i] = e4m3_decode(xs[i]);
 #pragma omp parallel for schedule(static)
   for (int64_t rr = 0; rr < static_cast<int64_t>(row_count); ++rr) {
     const uint32_t row = first_row + static_cast<uint32_t>(rr);
     const uint8_t* codes = m.codes + static_cast<size_t>(row) * (m.cols / 2U);
-    const uint8_t* scales = m.scales + static_cast<size_t>(row) * (m.cols / 16U);
-    std::vector<float> acc(batch, 0.0F);
-    std::vector<float> wrow(16);
-    for (uint32_t b = 0; b < m.cols / 16U; ++b) {
-      const float sc = e4m3_decode(scales[b]);
+    const uint8_t* scales = m.scales + static_cast<size_t>(row) * blocks;
+    std::vector<double> acc(batch, 0.0);
+    int wi[16];
+    for (uint32_t b = 0; b < blocks; ++b) {
+      const float sw = e4m3_decode(scales[b]);
       for (int i = 0; i < 8; ++i) {
         const uint8_t p = codes[b * 8U + i];
-        wrow[2 * i] = levels[p & 15U] * sc * m.weight_scale;
-        wrow[2 * i + 1] = levels[p >> 4U] * sc * m.weight_scale;
+        wi[2 * i] = twice[p & 15U];
+        wi[2 * i + 1] = twice[p >> 4U];
       }
       for (uint32_t q = 0; q < batch; ++q) {
-        const float* xr = xq.data() + static_cast<size_t>(q) * m.cols + b * 16U;
-        float a = acc[q];
-        for (int i = 0; i < 16; ++i) a += wrow[i] * xr[i];
-        acc[q] = a;
+        const int8_t* xr = xi.data() + static_cast<size_t>(q) * m.cols + b * 16U;
+        int isum = 0;
+        for (int i = 0; i < 16; ++i) isum += wi[i] * xr[i];
+        const float term = static_cast<float>(isum) * (sw * xsf[static_cast<size_t>(q) * blocks + b]) * 0.25F;
+        acc[q] += static_cast<double>(term);
       }
     }
     for (uint32_t q = 0; q < batch; ++q)
-      y[static_cast<size_t>(q) * row_count + rr] = bf16_round(acc[q]);
+      y[static_cast<size_t>(q) * row_count + rr] =
+          bf16_round(static_cast<float>(acc[q]) * m.weight_scale / m.input_scale);
   }
 }
 
@@ -318,7 +350,7 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
   const uint32_t total = first_ctx + rows - 1U;  // tokens visible to the last row
   const uint32_t splits = (total + split_tokens - 1U) / split_tokens;
   const float inv_sqrt = 1.0F / std::sqrt(static_cast<float>(hd));
-  const uint32_t tile = enc == QO_KV_Q4H ? 32U : (enc == QO_KV_Q8 ? 16U : split_tokens);
+  const uint32_t tile = 32U;  // the reference tiles by 32 (Q4H), 16 (Q8) or the split (F16)
   const int64_t items = static_cast<int64_t>(rows) * qh;
 #pragma omp parallel for schedule(dynamic)
   for (int64_t item = 0; item < items; ++item) {
@@ -372,36 +404,37 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
             }
           } else if (tok < ctx) {
             const size_t rec = static_cast<size_t>(tok % pt) * kvh + kv;
-            float dot = 0.0F;
+            double dot = 0.0;  // products of BF16/F16 values are exact; sum once
             if (enc == QO_KV_Q8) {
               const uint8_t* kr = layer + rec * (hd + 2U);
               uint16_t sb;
               std::memcpy(&sb, kr + hd, 2);
               const float ks = f16_value(sb);
               for (uint32_t d = 0; d < hd; ++d)
-                dot += qf[d] * bf16_round(static_cast<float>(static_cast<int8_t>(kr[d])) * ks);
+                dot += static_cast<double>(qf[d] * bf16_round(static_cast<float>(static_cast<int8_t>(kr[d])) * ks));
             } else {
               const uint8_t* kr = layer + rec * hd * 2U;
               for (uint32_t d = 0; d < hd; ++d) {
                 uint16_t kb;
                 std::memcpy(&kb, kr + 2U * d, 2);
-                dot += qf[d] * f16_value(kb);
+                dot += static_cast<double>(qf[d] * f16_value(kb));
               }
             }
-            score[j] = dot * inv_sqrt;
+            score[j] = static_cast<float>(dot) * inv_sqrt;
           }
           tmax = std::fmax(tmax, score[j]);
         }
         const float next = std::fmax(m, tmax);
         const float prev = m == kNegInf ? 0.0F : std::exp(m - next);
-        float tsum = 0.0F;
+        double tsum_d = 0.0;
         for (uint32_t j = 0; j < n; ++j) {
           float p = (t0 + j < ctx) ? std::exp(score[j] - next) : 0.0F;
           if (enc == QO_KV_Q8) p = bf16_round(p);
           else if (enc == QO_KV_F16) p = f16_round(p);
           prob[j] = p;
-          tsum += p;
+          tsum_d += static_cast<double>(p);
         }
+        const float tsum = static_cast<float>(tsum_d);
         for (uint32_t d = 0; d < hd; ++d) acc[d] *= prev;
         if (enc == QO_KV_Q4H) {
           float wmax = 0.0F;
@@ -421,6 +454,7 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
             acc[d] += static_cast<float>(dot) * pscale;
           }
         } else {
+          std::vector<double> tdot(hd, 0.0);
           for (uint32_t j = 0; j < n; ++j) {
             if (prob[j] == 0.0F) continue;
             const uint32_t tok = t0 + j;
@@ -432,16 +466,17 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
               std::memcpy(&sb, vr + hd, 2);
               const float vs = f16_value(sb);
               for (uint32_t d = 0; d < hd; ++d)
-                acc[d] += prob[j] * bf16_round(static_cast<float>(static_cast<int8_t>(vr[d])) * vs);
+                tdot[d] += static_cast<double>(prob[j] * bf16_round(static_cast<float>(static_cast<int8_t>(vr[d])) * vs));
             } else {
               const uint8_t* vr = layer + records * hd * 2U + rec * hd * 2U;
               for (uint32_t d = 0; d < hd; ++d) {
                 uint16_t vb;
                 std::memcpy(&vb, vr + 2U * d, 2);
-                acc[d] += prob[j] * f16_value(vb);
+                tdot[d] += static_cast<double>(prob[j] * f16_value(vb));
               }
             }
           }
+          for (uint32_t d = 0; d < hd; ++d) acc[d] += static_cast<float>(tdot[d]);
         }
         sum = sum * prev + tsum;
         m = next;
@@ -802,6 +837,10 @@ void qo_nvfp4_dequant(const qo_matrix* m, float* out) {
 }
 void qo_nvfp4_fake_quant(const float* x, uint32_t rows, uint32_t cols, float g, float* out) {
   nvfp4_fake_quant(x, rows, cols, g, out);
+}
+void qo_nvfp4_quantize_activations(const float* x, uint32_t rows, uint32_t cols, float g,
+                                   uint8_t* codes, uint8_t* scales) {
+  nvfp4_quantize_activations(x, rows, cols, g, codes, scales);
 }
 void qo_nvfp4_gemv(const qo_matrix* m, uint32_t first_row, uint32_t row_count, const float* x,
                    uint32_t batch, float* y) {

@@ -116,6 +116,9 @@ void qo_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols,
 void qo_nvfp4_dequant(const qo_matrix* m, float* out);
 void qo_nvfp4_fake_quant(const float* x, uint32_t rows, uint32_t cols,
                          float global_scale, float* out);
+/* codes: one E2M1 code per byte [rows, cols]; scales: E4M3 [rows, cols/16] */
+void qo_nvfp4_quantize_activations(const float* x, uint32_t rows, uint32_t cols,
+                                   float global_scale, uint8_t* codes, uint8_t* scales);
 void qo_nvfp4_gemv(const qo_matrix* m, uint32_t first_row, uint32_t row_count,
                    const float* x, uint32_t batch, float* y);
 

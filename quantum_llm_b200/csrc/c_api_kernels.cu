@@ -1,0 +1,153 @@
+// extern "C" forms of the kernel launchers declared in include/qllm_b200.h.
+#include "common.cuh"
+#include "gemv_mma.h"
+#include "kernels.h"
+
+using namespace qllm;
+
+extern "C" {
+
+int qllm_k_embedding_bf16(const uint16_t* table, const uint32_t* tokens, float* out, uint32_t rows,
+                          uint32_t hidden, uint32_t vocab, void* stream) {
+  if (!table || !tokens || !out || !rows || !hidden || !vocab)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid embedding batch");
+  return launch_embedding(table, tokens, out, rows, hidden, vocab, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_rms_norm(const float* x, const float* weight, float* out, uint32_t rows, uint32_t cols,
+                    float eps, void* stream) {
+  if (!x || !weight || !out || !rows || !cols) return fail(QLLM_INVALID_ARGUMENT, "invalid RMSNorm batch");
+  return launch_rms_norm(x, weight, out, rows, cols, cols, cols, eps, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_nvfp4_fake_quant(const float* x, float* out, uint32_t rows, uint32_t cols,
+                            float global_scale, void* stream) {
+  if (!x || !out || !rows || !cols || cols % 16U || !(global_scale > 0.0F))
+    return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 activation quant-dequant");
+  return launch_fake_quant(x, out, rows, cols, global_scale, static_cast<cudaStream_t>(stream));
+}
+
+size_t qllm_k_nvfp4_gemv_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols) {
+  const size_t simt = act_quant_bytes(batch, cols);
+  const size_t mma = gemv_mma_workspace_bytes(batch, rows, cols);
+  return simt > mma ? simt : mma;
+}
+
+int qllm_k_nvfp4_gemv(const qllm_matrix* m, uint32_t first_row, uint32_t row_count, const float* x,
+                      float* y, uint32_t batch, void* workspace, size_t workspace_bytes, int impl,
+                      void* stream) {
+  if (!m || !m->codes || !m->scales || !x || !y || !workspace || !m->rows || !m->cols ||
+      m->cols % 16U || !batch || !row_count || first_row + row_count > m->rows ||
+      !(m->weight_scale > 0.0F) || !(m->input_scale > 0.0F))
+    return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 GEMV");
+  if (workspace_bytes < qllm_k_nvfp4_gemv_workspace_bytes(batch, row_count, m->cols))
+    return fail(QLLM_INVALID_ARGUMENT, "native NVFP4 GEMV workspace is too small");
+  auto s = static_cast<cudaStream_t>(stream);
+  if (impl == 0) {
+    int rc = launch_act_quant_i8(x, workspace, batch, m->cols, m->input_scale, s);
+    if (rc) return rc;
+    return launch_gemv_simt(*m, first_row, row_count, workspace, batch, y, batch, s);
+  }
+  if (impl == 1) {
+    // one-shot form: build the tensor map and the re-tiled scales for this call
+    MmaWeights w;
+    int rc = w.prepare(*m, s);
+    if (rc) return rc;
+    rc = launch_gemv_mma(w, *m, first_row, row_count, x, y, batch, workspace, workspace_bytes, s);
+    if (rc) return rc;
+    return check_cuda(cudaStreamSynchronize(s), "native NVFP4 tensor-core GEMV");
+  }
+  return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
+}
+
+int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols, float global_scale,
+                                  uint8_t* codes, uint8_t* scales, void* stream) {
+  if (!w || !codes || !scales || !rows || !cols || cols % 16U || !(global_scale > 0.0F))
+    return fail(QLLM_INVALID_ARGUMENT, "invalid NVFP4 weight quantisation");
+  return launch_quantize_weights(w, rows, cols, global_scale, codes, scales, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_add(float* dst, const float* src, uint64_t count, int bf16, void* stream) {
+  if (!dst || !src || !count) return fail(QLLM_INVALID_ARGUMENT, "invalid add");
+  return launch_add(dst, src, count, bf16 != 0, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_silu_product(const float* gate_up, float* out, uint32_t rows, uint32_t ffn, int bf16,
+                        void* stream) {
+  if (!gate_up || !out || !rows || !ffn) return fail(QLLM_INVALID_ARGUMENT, "invalid SiLU product");
+  return launch_silu_product(gate_up, out, rows, ffn, bf16 != 0, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_rope_kv_store(float* qkv, uint32_t rows, uint32_t q_heads, uint32_t kv_heads,
+                         uint32_t head_dim, uint32_t rotary_dim, const float* inv_freq,
+                         const uint32_t* first_position, uint32_t position_offset,
+                         uint32_t rotary_offset, uint8_t* const* page_table, size_t layer_offset,
+                         uint32_t page_tokens, uint32_t encoding, int bf16, void* stream) {
+  if (!qkv || !rows || !q_heads || !kv_heads || !inv_freq || !first_position || !page_table ||
+      !page_tokens || encoding > 2U)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid RoPE/KV store batch");
+  RopeStoreArgs a{qkv, rows, q_heads, kv_heads, head_dim, rotary_dim, inv_freq, first_position,
+                  position_offset, rotary_offset, page_table, layer_offset, page_tokens, encoding,
+                  bf16 != 0};
+  return launch_rope_kv_store(a, static_cast<cudaStream_t>(stream));
+}
+
+size_t qllm_k_kv_layer_bytes(uint32_t encoding, uint32_t page_tokens, uint32_t kv_heads,
+                             uint32_t head_dim) {
+  return kv_layer_bytes(encoding, page_tokens, kv_heads, head_dim);
+}
+
+size_t qllm_k_attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                                        uint32_t max_splits) {
+  return attention_workspace_bytes(rows, q_heads, head_dim, max_splits);
+}
+
+int qllm_k_attention(uint32_t encoding, const uint8_t* const* page_table, size_t layer_offset,
+                     uint32_t page_tokens, const float* query, uint32_t query_row_stride,
+                     uint32_t rows, const uint32_t* first_position, uint32_t position_offset,
+                     uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t split_tokens,
+                     uint32_t max_splits, int bf16, void* workspace, float* out, int impl,
+                     void* stream) {
+  if (!page_table || !query || !first_position || !workspace || !out || !kv_heads)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid attention launch");
+  AttentionArgs a{};
+  a.encoding = encoding;
+  a.page_table = page_table;
+  a.layer_offset = layer_offset;
+  a.page_tokens = page_tokens;
+  a.query = query;
+  a.query_row_stride = query_row_stride;
+  a.rows = rows;
+  a.first_position = first_position;
+  a.position_offset = position_offset;
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.split_tokens = split_tokens;
+  a.max_splits = max_splits;
+  a.bf16 = bf16 != 0;
+  a.workspace = workspace;
+  a.out = out;
+  a.impl = impl;
+  return launch_attention(a, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_argmax(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
+                  uint32_t* out, void* stream) {
+  if (!values || !rows || !count || !out) return fail(QLLM_INVALID_ARGUMENT, "invalid argmax");
+  return launch_argmax(values, rows, count, row_stride, out, static_cast<cudaStream_t>(stream));
+}
+
+size_t qllm_k_topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k) {
+  return topk_workspace_bytes(rows, count, k);
+}
+
+int qllm_k_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride, uint32_t k,
+                float* out_values, uint32_t* out_tokens, void* workspace, void* stream) {
+  if (!values || !rows || !count || !k || k > 64U || k > count || !out_values || !out_tokens || !workspace)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid top-k");
+  return launch_topk(values, rows, count, row_stride, k, out_values, out_tokens, workspace,
+                     static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

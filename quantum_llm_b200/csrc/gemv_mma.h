@@ -1,0 +1,38 @@
+// tcgen05 block-scaled NVFP4 GEMV: prepared weight view and launcher.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/qllm_b200.h"
+
+namespace qllm {
+
+// Per-matrix state of the tensor-core path: a TMA descriptor over the packed
+// codes and the block scales re-tiled into the layout tcgen05 reads from
+// tensor memory.  Owned by the provider; released with it.
+struct MmaWeights {
+  alignas(64) CUtensorMap codes_map;
+  uint8_t* tiled_scales = nullptr;  // [row_tiles, k_atoms, 512]
+  uint32_t rows = 0, cols = 0;
+  bool ready = false;
+  int prepare(const qllm_matrix& device_matrix, cudaStream_t stream);
+  void release();
+  MmaWeights() = default;
+  MmaWeights(const MmaWeights&) = delete;
+  MmaWeights& operator=(const MmaWeights&) = delete;
+  MmaWeights(MmaWeights&& o) noexcept { *this = static_cast<MmaWeights&&>(o); }
+  MmaWeights& operator=(MmaWeights&& o) noexcept;
+  ~MmaWeights() { release(); }
+};
+
+size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);
+// y[batch, row_count] = bf16(fakequant(x) . W[first_row .. first_row+row_count)^T)
+int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
+                    uint32_t row_count, const float* x, float* y, uint32_t batch, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream);
+
+}  // namespace qllm

@@ -1,0 +1,130 @@
+// Internal C++ launch interface of the kernel layer (one function per kernel
+// family).  All pointers are device memory; every function returns 0 or a
+// negative qllm_status and never synchronises.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/qllm_b200.h"
+
+namespace qllm {
+
+int launch_embedding(const uint16_t* table, const uint32_t* tokens, float* out, uint32_t rows,
+                     uint32_t hidden, uint32_t vocab, cudaStream_t stream);
+int launch_rms_norm(const float* x, const float* weight, float* out, uint32_t rows, uint32_t cols,
+                    uint32_t in_stride, uint32_t out_stride, float eps,
+                    const uint32_t* row_select, cudaStream_t stream);
+int launch_fake_quant(const float* x, float* out, uint32_t rows, uint32_t cols, float g,
+                      cudaStream_t stream);
+// Quantised activations of the CUDA-core GEMV: INT8 (twice the E2M1 value) [rows, cols]
+// followed by FP32 block scales [rows, cols/16].
+size_t act_quant_bytes(uint32_t rows, uint32_t cols);
+int launch_act_quant_i8(const float* x, void* qact, uint32_t rows, uint32_t cols, float g,
+                        cudaStream_t stream);
+int launch_gemv_simt(const qllm_matrix& m, uint32_t first_row, uint32_t row_count, const void* qact,
+                     uint32_t qact_rows, float* y, uint32_t batch, cudaStream_t stream);
+int launch_quantize_weights(const float* w, uint32_t rows, uint32_t cols, float g, uint8_t* codes,
+                            uint8_t* scales, cudaStream_t stream);
+int launch_add(float* dst, const float* src, uint64_t count, bool bf16, cudaStream_t stream);
+int launch_silu_product(const float* gate_up, float* out, uint32_t rows, uint32_t ffn, bool bf16,
+                        cudaStream_t stream);
+int launch_copy_rows(float* dst, uint32_t dst_stride, const float* src, uint32_t src_stride,
+                     uint32_t rows, uint32_t cols, const uint32_t* row_select, cudaStream_t stream);
+int launch_argmax(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
+                  uint32_t* out, cudaStream_t stream);
+size_t topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k);
+int launch_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride, uint32_t k,
+                float* out_values, uint32_t* out_tokens, void* workspace, cudaStream_t stream);
+
+// ---- attention -----------------------------------------------------------
+size_t kv_layer_bytes(uint32_t encoding, uint32_t page_tokens, uint32_t kv_heads, uint32_t head_dim);
+struct RopeStoreArgs {
+  float* qkv;                 // [rows, (q+2kv)*head_dim]
+  uint32_t rows, q_heads, kv_heads, head_dim, rotary_dim;
+  const float* inv_freq;      // [rotary_dim/2]
+  const uint32_t* first_position;  // device scalar
+  uint32_t position_offset;   // cache position of row r = *first_position + position_offset + r
+  uint32_t rotary_offset;     // rotary position = cache position + rotary_offset
+  uint8_t* const* page_table;
+  size_t layer_offset;
+  uint32_t page_tokens, encoding;
+  bool bf16;
+};
+int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream);
+
+struct AttentionArgs {
+  uint32_t encoding;
+  const uint8_t* const* page_table;
+  size_t layer_offset;
+  uint32_t page_tokens;
+  const float* query;         // row r, head h at query + r*query_row_stride + h*head_dim
+  uint32_t query_row_stride;
+  uint32_t rows;
+  const uint32_t* first_position;  // device scalar; row r sees *first_position + position_offset + r + 1 tokens
+  uint32_t position_offset;
+  uint32_t q_heads, kv_heads, head_dim;
+  uint32_t split_tokens, max_splits;
+  bool bf16;
+  void* workspace;
+  float* out;                 // [rows, q_heads*head_dim]
+  int impl;                   // 0 scalar, 1 tensor-core (Q4H)
+};
+size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                                 uint32_t max_splits);
+int launch_attention(const AttentionArgs& a, cudaStream_t stream);
+int launch_fill_synthetic_kv(uint8_t* const* page_table, size_t layer_offset, uint32_t encoding,
+                             uint32_t page_tokens, uint32_t kv_heads, uint32_t head_dim,
+                             uint32_t first, uint32_t count, uint64_t seed, cudaStream_t stream);
+
+// ---- sampler --------------------------------------------------------------
+// Device-resident request/step state; layout shared with the provider.
+struct DraftDistribution {
+  uint32_t count;
+  uint32_t pad;
+  uint32_t tokens[64];
+  double probabilities[64];
+};
+struct StepState {
+  // request parameters
+  unsigned long long seed;
+  uint32_t temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit, draft_depth;
+  // cursor
+  uint32_t position;        // position of verify_tokens[0]; also the draft cache length
+  uint32_t draft_count;     // proposals available for the next verify
+  uint32_t verify_tokens[8];
+  // outputs of the acceptance kernel
+  uint32_t accepted, next_token, rejected, new_position;
+  uint32_t mtp_tokens[8];   // accepted drafts + next token, padded with next token
+  uint32_t mtp_rows;        // accepted + 1
+  uint32_t error;           // sticky: non-zero when a kernel met an invalid state
+  uint32_t step_index;      // results ring cursor
+  uint32_t pad;
+  unsigned long long exact_calls, accepted_drafts, accepted_depth_calls[5];
+  DraftDistribution drafts[4];
+};
+struct AcceptArgs {
+  StepState* state;
+  const uint32_t* argmax_tokens;  // [rows] (greedy)
+  const float* top_values;        // [rows, top_k] (sampling)
+  const uint32_t* top_tokens;
+  qllm_exact_result* results;     // device ring [results_capacity]
+  uint32_t results_capacity;
+};
+int launch_accept(const AcceptArgs& a, cudaStream_t stream);
+struct DraftSampleArgs {
+  StepState* state;
+  const uint32_t* argmax_token;   // [1] (greedy)
+  const float* top_values;        // [top_k]
+  const uint32_t* top_tokens;
+  uint32_t pass;                  // 0 = first draft pass of a step, 1.. = chained passes
+  uint32_t from_sync;             // 1: called from a synchronisation batch (position is final)
+};
+int launch_draft_sample(const DraftSampleArgs& a, cudaStream_t stream);
+int launch_first_token(StepState* state, const uint32_t* argmax_token, const float* top_values,
+                       const uint32_t* top_tokens, uint32_t sample_position, uint32_t* out,
+                       cudaStream_t stream);
+
+}  // namespace qllm

@@ -1,0 +1,682 @@
+// RoPE + K/V record store, split flash-decode attention over the paged cache with
+// the dequantisation fused into the kernel, and the split combine.
+//
+// Page layout per layer (byte-identical to the reference's records,
+// runtime/src/cuda/transformer_kernels.cu:229-288, 560-625, 4208-4230):
+//   Q4H: [K codes kv*pt*hd/2][K scales f16 kv*pt][V codes][V scales], record = kv_head*pt + pos%pt
+//   Q8 : [K records pt*kv*(hd+2)][V records], record = (pos%pt)*kv + kv_head, int8[hd] + f16 scale
+//   F16: [K pt*kv*hd f16][V ...], token-major
+#include <mma.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace qllm {
+
+size_t kv_layer_bytes(uint32_t enc, uint32_t pt, uint32_t kv, uint32_t hd) {
+  const size_t records = static_cast<size_t>(pt) * kv;
+  switch (enc) {
+    case QLLM_KV_F16: return records * hd * 2U * 2U;
+    case QLLM_KV_Q4H: return records * (hd / 2U + 2U) * 2U;
+    case QLLM_KV_Q8: return records * (hd + 2U) * 2U;
+  }
+  return 0;
+}
+
+__device__ __forceinline__ float block_max_small(float v, float* scratch) {
+  // blockDim.x <= 256, all threads participate
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31U) == 0U) scratch[threadIdx.x >> 5U] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (uint32_t w = 1; w < (blockDim.x + 31U) / 32U; ++w) r = fmaxf(r, scratch[w]);
+  return r;
+}
+
+// grid (q_heads + kv_heads, rows), block head_dim threads.
+__global__ void rope_kv_store_kernel(RopeStoreArgs a) {
+  __shared__ float src[256];
+  __shared__ float scratch[8];
+  const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  const uint32_t hd = a.head_dim;
+  const uint32_t width = (a.q_heads + 2U * a.kv_heads) * hd;
+  const uint32_t cache_position = *a.first_position + a.position_offset + row;
+  const uint32_t rotary_position = cache_position + a.rotary_offset;
+  float* v = a.qkv + static_cast<size_t>(row) * width + static_cast<size_t>(head) * hd;
+  src[d] = actv(v[d], a.bf16);
+  __syncthreads();
+  float result = src[d];
+  if (d < a.rotary_dim) {
+    const uint32_t half = a.rotary_dim / 2U;
+    const uint32_t pair = d % half;
+    const float angle = static_cast<float>(rotary_position) * a.inv_freq[pair];
+    const float other = d < half ? -src[d + half] : src[d - half];
+    result = src[d] * actv(cosf(angle), a.bf16) + other * actv(sinf(angle), a.bf16);
+  }
+  result = actv(result, a.bf16);
+  v[d] = result;
+  if (head < a.q_heads) return;
+
+  // K head: quantise and store the K record and the V record of the same kv head
+  const uint32_t kvh = head - a.q_heads;
+  const float key = result;
+  const float value = a.qkv[static_cast<size_t>(row) * width +
+                            static_cast<size_t>(a.q_heads + a.kv_heads + kvh) * hd + d];
+  const uint32_t pt = a.page_tokens;
+  uint8_t* layer = a.page_table[cache_position / pt] + a.layer_offset;
+  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
+  const uint32_t slot = cache_position % pt;
+  if (a.encoding == QLLM_KV_F16) {
+    const size_t rec = static_cast<size_t>(slot) * a.kv_heads + kvh;
+    reinterpret_cast<__half*>(layer)[rec * hd + d] = __float2half_rn(key);
+    reinterpret_cast<__half*>(layer + records * hd * 2U)[rec * hd + d] = __float2half_rn(value);
+    return;
+  }
+  const float kmax = block_max_small(fabsf(key), scratch);
+  const float vmax = block_max_small(fabsf(value), scratch);
+  // the pair partner's values travel through shared memory
+  __shared__ float kbuf[256], vbuf[256];
+  kbuf[d] = key;
+  vbuf[d] = value;
+  __syncthreads();
+  if (a.encoding == QLLM_KV_Q4H) {
+    const __half ksh = __float2half_rn(fmaxf(kmax / 7.0F, 0x1p-24F));
+    const __half vsh = __float2half_rn(fmaxf(vmax / 7.0F, 0x1p-24F));
+    const float ks = __half2float(ksh), vs = __half2float(vsh);
+    uint8_t* kc = layer;
+    uint8_t* ksc = kc + records * (hd / 2U);
+    uint8_t* vc = ksc + records * 2U;
+    uint8_t* vsc = vc + records * (hd / 2U);
+    const size_t rec = static_cast<size_t>(kvh) * pt + slot;
+    if (d == 0U) {
+      reinterpret_cast<__half*>(ksc)[rec] = ksh;
+      reinterpret_cast<__half*>(vsc)[rec] = vsh;
+    }
+    if (d < hd / 2U) {
+      const int kl = max(-7, min(7, __float2int_rn(kbuf[2U * d] / ks)));
+      const int kh = max(-7, min(7, __float2int_rn(kbuf[2U * d + 1U] / ks)));
+      const int vl = max(-7, min(7, __float2int_rn(vbuf[2U * d] / vs)));
+      const int vh = max(-7, min(7, __float2int_rn(vbuf[2U * d + 1U] / vs)));
+      kc[rec * (hd / 2U) + d] = static_cast<uint8_t>((kl & 15) | ((kh & 15) << 4));
+      vc[rec * (hd / 2U) + d] = static_cast<uint8_t>((vl & 15) | ((vh & 15) << 4));
+    }
+  } else {  // Q8
+    const __half ksh = __float2half_rn(fmaxf(kmax / 127.0F, 0x1p-24F));
+    const __half vsh = __float2half_rn(fmaxf(vmax / 127.0F, 0x1p-24F));
+    const float ks = __half2float(ksh), vs = __half2float(vsh);
+    const size_t rb = hd + 2U;
+    const size_t rec = static_cast<size_t>(slot) * a.kv_heads + kvh;
+    uint8_t* kr = layer + rec * rb;
+    uint8_t* vr = layer + records * rb + rec * rb;
+    if (d == 0U) {
+      *reinterpret_cast<__half*>(kr + hd) = ksh;
+      *reinterpret_cast<__half*>(vr + hd) = vsh;
+    }
+    kr[d] = static_cast<uint8_t>(static_cast<int8_t>(max(-127, min(127, __float2int_rn(key / ks)))));
+    vr[d] = static_cast<uint8_t>(static_cast<int8_t>(max(-127, min(127, __float2int_rn(value / vs)))));
+  }
+}
+
+int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream) {
+  if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U)
+    return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
+  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a);
+  count_launch();
+  return check_launch("rope_kv_store");
+}
+
+// ------------------------------------------------------------------ partials
+struct Partials {
+  float* maxima;   // [rows, max_splits, q_heads]
+  float* sums;     // same
+  float* outputs;  // [rows, max_splits, q_heads, head_dim]
+};
+size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                                 uint32_t max_splits) {
+  const size_t items = static_cast<size_t>(rows) * max_splits * q_heads;
+  return items * (2U + head_dim) * sizeof(float);
+}
+static Partials partials_of(const AttentionArgs& a) {
+  const size_t items = static_cast<size_t>(a.rows) * a.max_splits * a.q_heads;
+  float* base = static_cast<float*>(a.workspace);
+  return {base, base + items, base + 2U * items};
+}
+
+// ------------------------------------------------- scalar attention (all encodings)
+// CTA = (kv head, split), 256 threads, 32-key tiles staged in shared memory.
+// Dynamic shared memory: q[MR][hd] | tile[32][hd+1] | S[MR][33] | P[MR][33] | stats.
+template <uint32_t ENC>
+__global__ void __launch_bounds__(256)
+attention_scalar_kernel(AttentionArgs a, Partials part) {
+  extern __shared__ float smem[];
+  const uint32_t hd = a.head_dim, group = a.q_heads / a.kv_heads;
+  const uint32_t MR = a.rows * group;
+  float* qs = smem;
+  float* tile = qs + MR * hd;
+  float* S = tile + 32U * (hd + 1U);
+  float* P = S + MR * 33U;
+  float* rmax = P + MR * 33U;
+  float* rsum = rmax + MR;
+  float* rprev = rsum + MR;
+  float* rpscale = rprev + MR;
+  float* rqscale = rpscale + MR;
+  float* kscale = rqscale + MR;  // [32]
+  float* vscale = kscale + 32U;  // [32]
+  const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
+  const uint32_t kvh = blockIdx.x, split = blockIdx.y;
+  const uint32_t first_ctx = *a.first_position + a.position_offset + 1U;
+  const uint32_t total = first_ctx + a.rows - 1U;
+  const uint32_t first = split * a.split_tokens;
+  if (first >= total) return;  // inactive split: the combine never reads it
+  const uint32_t last = min(total, first + a.split_tokens);
+  const uint32_t pt = a.page_tokens;
+  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
+  const float inv_sqrt = 1.0F / sqrtf(static_cast<float>(hd));
+
+  // queries: quantise / round per encoding
+  for (uint32_t mr = warp; mr < MR; mr += 8U) {
+    const uint32_t row = mr / group, head = kvh * group + mr % group;
+    const float* q = a.query + static_cast<size_t>(row) * a.query_row_stride + static_cast<size_t>(head) * hd;
+    if (ENC == QLLM_KV_Q4H) {
+      float m = 0.0F;
+      for (uint32_t d = lane; d < hd; d += 32U) m = fmaxf(m, fabsf(q[d]));
+      m = warp_max(m);
+      const float sc = fmaxf(m / 127.0F, 0x1p-24F);
+      for (uint32_t d = lane; d < hd; d += 32U)
+        qs[mr * hd + d] = static_cast<float>(max(-127, min(127, __float2int_rn(q[d] / sc))));
+      if (lane == 0U) rqscale[mr] = sc;
+    } else {
+      for (uint32_t d = lane; d < hd; d += 32U)
+        qs[mr * hd + d] = ENC == QLLM_KV_Q8 ? bf16r(q[d]) : __half2float(__float2half_rn(q[d]));
+    }
+    if (lane == 0U) { rmax[mr] = kNegInf; rsum[mr] = 0.0F; }
+  }
+  constexpr uint32_t kAcc = 32;  // MR*hd/256 <= 64*256/256 = 64 -> two passes of 32
+  float acc[2][kAcc];
+#pragma unroll
+  for (int p = 0; p < 2; ++p)
+#pragma unroll
+    for (uint32_t i = 0; i < kAcc; ++i) acc[p][i] = 0.0F;
+  const uint32_t outputs = MR * hd;
+  __syncthreads();
+
+  for (uint32_t t0 = first; t0 < last; t0 += 32U) {
+    const uint32_t n = min(32U, last - t0);
+    // ---- K tile
+    for (uint32_t item = tid; item < 32U * hd; item += 256U) {
+      const uint32_t j = item / hd, d = item % hd;
+      float value = 0.0F;
+      if (j < n) {
+        const uint32_t tok = t0 + j;
+        const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
+        if (ENC == QLLM_KV_Q4H) {
+          const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
+          const uint8_t byte = layer[rec * (hd / 2U) + d / 2U];
+          const int nib = (d & 1U) ? (byte >> 4) : (byte & 15);
+          value = static_cast<float>(nib >= 8 ? nib - 16 : nib);
+        } else if (ENC == QLLM_KV_Q8) {
+          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+          const uint8_t* kr = layer + rec * (hd + 2U);
+          const float sc = __half2float(*reinterpret_cast<const __half*>(kr + hd));
+          value = bf16r(static_cast<float>(static_cast<int8_t>(kr[d])) * sc);
+        } else {
+          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+          value = __half2float(reinterpret_cast<const __half*>(layer)[rec * hd + d]);
+        }
+      }
+      tile[j * (hd + 1U) + d] = value;
+    }
+    if (ENC == QLLM_KV_Q4H && tid < 64U) {
+      const uint32_t j = tid & 31U;
+      float sc = 0.0F;
+      if (j < n) {
+        const uint32_t tok = t0 + j;
+        const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
+        const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
+        const uint8_t* base = tid < 32U ? layer + records * (hd / 2U)
+                                        : layer + records * (hd / 2U) * 2U + records * 2U;
+        sc = __half2float(reinterpret_cast<const __half*>(base)[rec]);
+      }
+      (tid < 32U ? kscale : vscale)[j] = sc;
+    }
+    __syncthreads();
+    // ---- scores
+    for (uint32_t pair = tid; pair < MR * 32U; pair += 256U) {
+      const uint32_t mr = pair / 32U, j = pair % 32U;
+      const float* qr = qs + mr * hd;
+      const float* kr = tile + j * (hd + 1U);
+      float dot;
+      if (ENC == QLLM_KV_Q4H) {
+        float idot = 0.0F;  // integer-valued terms: exact in FP32
+        for (uint32_t d = 0; d < hd; ++d) idot += qr[d] * kr[d];
+        dot = idot * rqscale[mr] * kscale[j];
+      } else {
+        double ddot = 0.0;  // products of BF16/F16 values are exact; sum once
+        for (uint32_t d = 0; d < hd; ++d) ddot += static_cast<double>(qr[d] * kr[d]);
+        dot = static_cast<float>(ddot);
+      }
+      S[mr * 33U + j] = dot * inv_sqrt;
+    }
+    __syncthreads();
+    // ---- online softmax, one warp per matrix row, lane = key
+    for (uint32_t mr = warp; mr < MR; mr += 8U) {
+      const uint32_t ctx = first_ctx + mr / group;
+      const bool visible = lane < n && t0 + lane < ctx;
+      const float score = visible ? S[mr * 33U + lane] : kNegInf;
+      const float tmax = warp_max(score);
+      const float old = rmax[mr];
+      const float next = fmaxf(old, tmax);
+      const float prev = old == kNegInf ? 0.0F : expf(old - next);
+      float p = visible ? expf(score - next) : 0.0F;
+      float stored;
+      if (ENC == QLLM_KV_Q4H) {
+        const float w = visible ? p * vscale[lane] : 0.0F;
+        const float wmax = warp_max(w);
+        const float pscale = fmaxf(wmax / 127.0F, 0x1p-24F);
+        stored = static_cast<float>(max(0, min(127, __float2int_rn(w / pscale))));
+        if (lane == 0U) rpscale[mr] = pscale;
+      } else {
+        p = ENC == QLLM_KV_Q8 ? bf16r(p) : __half2float(__float2half_rn(p));
+        stored = p;
+      }
+      const float tsum = static_cast<float>(warp_sum_f64(static_cast<double>(p)));
+      P[mr * 33U + lane] = stored;
+      if (lane == 0U) {
+        rsum[mr] = rsum[mr] * prev + tsum;
+        rmax[mr] = next;
+        rprev[mr] = prev;
+      }
+    }
+    __syncthreads();
+    // ---- V tile (reuses the K buffer)
+    for (uint32_t item = tid; item < 32U * hd; item += 256U) {
+      const uint32_t j = item / hd, d = item % hd;
+      float value = 0.0F;
+      if (j < n) {
+        const uint32_t tok = t0 + j;
+        const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
+        if (ENC == QLLM_KV_Q4H) {
+          const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
+          const uint8_t byte = layer[records * (hd / 2U) + records * 2U + rec * (hd / 2U) + d / 2U];
+          const int nib = (d & 1U) ? (byte >> 4) : (byte & 15);
+          value = static_cast<float>(nib >= 8 ? nib - 16 : nib);
+        } else if (ENC == QLLM_KV_Q8) {
+          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+          const uint8_t* vr = layer + records * (hd + 2U) + rec * (hd + 2U);
+          const float sc = __half2float(*reinterpret_cast<const __half*>(vr + hd));
+          value = bf16r(static_cast<float>(static_cast<int8_t>(vr[d])) * sc);
+        } else {
+          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+          value = __half2float(reinterpret_cast<const __half*>(layer + records * hd * 2U)[rec * hd + d]);
+        }
+      }
+      tile[j * (hd + 1U) + d] = value;
+    }
+    __syncthreads();
+    // ---- P.V, each thread owns outputs tid, tid+256, ...
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll 4
+      for (uint32_t i = 0; i < kAcc; ++i) {
+        const uint32_t o = (pass * kAcc + i) * 256U + tid;
+        if (o < outputs) {
+          const uint32_t mr = o / hd, d = o % hd;
+          float dot;
+          if (ENC == QLLM_KV_Q4H) {
+            float idot = 0.0F;  // integer-valued terms: exact in FP32
+            for (uint32_t j = 0; j < 32U; ++j) idot += P[mr * 33U + j] * tile[j * (hd + 1U) + d];
+            dot = idot * rpscale[mr];
+          } else {
+            double ddot = 0.0;
+            for (uint32_t j = 0; j < 32U; ++j)
+              ddot += static_cast<double>(P[mr * 33U + j] * tile[j * (hd + 1U) + d]);
+            dot = static_cast<float>(ddot);
+          }
+          acc[pass][i] = acc[pass][i] * rprev[mr] + dot;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- partials
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass)
+#pragma unroll 4
+    for (uint32_t i = 0; i < kAcc; ++i) {
+      const uint32_t o = (pass * kAcc + i) * 256U + tid;
+      if (o < outputs) {
+        const uint32_t mr = o / hd, d = o % hd;
+        const uint32_t row = mr / group, head = kvh * group + mr % group;
+        const size_t pidx = (static_cast<size_t>(row) * a.max_splits + split) * a.q_heads + head;
+        part.outputs[pidx * hd + d] = acc[pass][i];
+        if (d == 0U) { part.maxima[pidx] = rmax[mr]; part.sums[pidx] = rsum[mr]; }
+      }
+    }
+}
+
+// --------------------------------------- Q4H tensor-core attention (head_dim 128)
+// CTA = (kv head, split), 4 warps.  QK^T and P.V are INT8 m16n8k32 MMAs whose B
+// operands are built straight from the packed nibbles in global memory: a code c
+// sits in the byte's high half as 16*c (one shift/mask per 8 codes) and the factor
+// 1/16 is folded into the score / output scale (exact power of two).  The k-slot
+// order inside an MMA is free as long as A and B agree, so even/odd codes of a
+// word feed the two halves of the k dimension without any shuffling.
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                       uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+attention_q4h_mma_kernel(AttentionArgs a, Partials part) {
+  constexpr uint32_t HD = 128;
+  __shared__ __align__(16) int8_t qs[32][HD + 16];  // +16: rows land on different banks
+  __shared__ float S[32][33];
+  __shared__ __align__(16) uint32_t Pq[32][8];      // 32 int8 probabilities per row
+  __shared__ float rmax[32], rsum[32], rprev[32], rpscale[32], rqscale[32];
+  __shared__ float kscale[32], vscale[32];
+  const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
+  const uint32_t g = lane >> 2U, t = lane & 3U;
+  const uint32_t kvh = blockIdx.x, split = blockIdx.y;
+  const uint32_t group = a.q_heads / a.kv_heads;
+  const uint32_t MR = a.rows * group;
+  const uint32_t first_ctx = *a.first_position + a.position_offset + 1U;
+  const uint32_t total = first_ctx + a.rows - 1U;
+  const uint32_t first = split * a.split_tokens;
+  if (first >= total) return;
+  const uint32_t last = min(total, first + a.split_tokens);
+  const uint32_t pt = a.page_tokens;
+  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
+  const float inv_sqrt = 1.0F / sqrtf(static_cast<float>(HD));
+
+  // INT8 queries, one warp per matrix row
+  for (uint32_t mr = warp; mr < 32U; mr += 4U) {
+    float vals[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    if (mr < MR) {
+      const uint32_t row = mr / group, head = kvh * group + mr % group;
+      const float4 q4 = *reinterpret_cast<const float4*>(
+          a.query + static_cast<size_t>(row) * a.query_row_stride + static_cast<size_t>(head) * HD + lane * 4U);
+      vals[0] = q4.x; vals[1] = q4.y; vals[2] = q4.z; vals[3] = q4.w;
+    }
+    float m = fmaxf(fmaxf(fabsf(vals[0]), fabsf(vals[1])), fmaxf(fabsf(vals[2]), fabsf(vals[3])));
+    m = warp_max(m);
+    const float sc = fmaxf(m / 127.0F, 0x1p-24F);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int q = mr < MR ? max(-127, min(127, __float2int_rn(vals[i] / sc))) : 0;
+      packed |= (static_cast<uint32_t>(q) & 0xffU) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(&qs[mr][lane * 4U]) = packed;
+    if (lane == 0U) { rqscale[mr] = mr < MR ? sc : 0.0F; rmax[mr] = kNegInf; rsum[mr] = 0.0F; }
+  }
+  __syncthreads();
+  const uint32_t mt = warp >> 1U, half = warp & 1U;
+  // A fragments of this warp's 16 query rows for the four 32-dim k-steps
+  uint32_t qa[4][4];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    const uint2 lo = *reinterpret_cast<const uint2*>(&qs[16U * mt + g][32 * ks + 8 * t]);
+    const uint2 hi = *reinterpret_cast<const uint2*>(&qs[16U * mt + g + 8U][32 * ks + 8 * t]);
+    qa[ks][0] = __byte_perm(lo.x, lo.y, 0x6420);  // even dims -> k slots 4t..4t+3
+    qa[ks][1] = __byte_perm(hi.x, hi.y, 0x6420);
+    qa[ks][2] = __byte_perm(lo.x, lo.y, 0x7531);  // odd dims -> k slots 16+4t..
+    qa[ks][3] = __byte_perm(hi.x, hi.y, 0x7531);
+  }
+  float out[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[j][i] = 0.0F;
+
+  for (uint32_t t0 = first; t0 < last; t0 += 32U) {
+    const uint32_t n = min(32U, last - t0);
+    // every key of the tile lies in one page (page_tokens % 32 == 0, t0 % 32 == 0)
+    const uint8_t* layer = a.page_table[t0 / pt] + a.layer_offset;
+    const uint32_t slot0 = t0 % pt;
+    const uint8_t* kcodes = layer + (static_cast<size_t>(kvh) * pt + slot0) * (HD / 2U);
+    const uint8_t* vcodes = layer + records * (HD / 2U) + records * 2U +
+                            (static_cast<size_t>(kvh) * pt + slot0) * (HD / 2U);
+    if (tid < 64U) {
+      const uint32_t j = tid & 31U;
+      const uint8_t* base = tid < 32U ? layer + records * (HD / 2U)
+                                      : layer + records * (HD / 2U) * 2U + records * 2U;
+      const float sc = __half2float(reinterpret_cast<const __half*>(base)[static_cast<size_t>(kvh) * pt + slot0 + j]);
+      (tid < 32U ? kscale : vscale)[j] = j < n ? sc : 0.0F;
+    }
+    // V words of this warp's dim half for the 8 keys this lane feeds into P.V
+    uint32_t vw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t key = (i < 4 ? 4U * t + i : 16U + 4U * t + (i - 4));
+      vw[i] = *reinterpret_cast<const uint32_t*>(vcodes + key * (HD / 2U) + 4U * (g + 8U * half));
+    }
+    // ---- S = Q K^T for keys 16*half + {0..15}
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const uint32_t key = 16U * half + 8U * nt + g;
+      int c[4] = {0, 0, 0, 0};
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(kcodes + key * (HD / 2U));
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t w = kw[4 * ks + t];
+        mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], (w << 4U) & 0xf0f0f0f0U, w & 0xf0f0f0f0U);
+      }
+      const uint32_t col = 16U * half + 8U * nt + 2U * t;
+      S[16U * mt + g][col] = static_cast<float>(c[0]) * 0.0625F;
+      S[16U * mt + g][col + 1U] = static_cast<float>(c[1]) * 0.0625F;
+      S[16U * mt + g + 8U][col] = static_cast<float>(c[2]) * 0.0625F;
+      S[16U * mt + g + 8U][col + 1U] = static_cast<float>(c[3]) * 0.0625F;
+    }
+    __syncthreads();
+    // ---- online softmax: warp w owns rows 8w..8w+7, lane = key
+#pragma unroll 1
+    for (uint32_t i = 0; i < 8U; ++i) {
+      const uint32_t mr = 8U * warp + i;
+      const bool active = mr < MR;
+      const uint32_t ctx = first_ctx + (active ? mr / group : 0U);
+      const bool visible = active && lane < n && t0 + lane < ctx;
+      const float score = visible ? S[mr][lane] * rqscale[mr] * kscale[lane] * inv_sqrt : kNegInf;
+      const float tmax = warp_max(score);
+      const float old = rmax[mr];
+      const float next = fmaxf(old, tmax);
+      const float prev = old == kNegInf ? 0.0F : expf(old - next);
+      const float p = visible ? expf(score - next) : 0.0F;
+      const float tsum = static_cast<float>(warp_sum_f64(static_cast<double>(p)));
+      const float w = visible ? p * vscale[lane] : 0.0F;
+      const float wmax = warp_max(w);
+      const float pscale = fmaxf(wmax / 127.0F, 0x1p-24F);
+      reinterpret_cast<int8_t*>(&Pq[mr][0])[lane] =
+          static_cast<int8_t>(max(0, min(127, __float2int_rn(w / pscale))));
+      if (lane == 0U && active) {
+        rsum[mr] = rsum[mr] * prev + tsum;
+        rmax[mr] = next;
+        rprev[mr] = prev;
+        rpscale[mr] = pscale * 0.0625F;  // V bytes carry 16*code
+      }
+    }
+    __syncthreads();
+    // ---- O += P V for dims 64*half + 8*chunk + j, chunk = B column
+    {
+      const uint32_t pa0 = Pq[16U * mt + g][t], pa1 = Pq[16U * mt + g + 8U][t];
+      const uint32_t pa2 = Pq[16U * mt + g][4U + t], pa3 = Pq[16U * mt + g + 8U][4U + t];
+      uint32_t bl[2][4], bh[2][4];  // [key set][dim pair index]: 4x4 byte transposes
+#pragma unroll
+      for (int set = 0; set < 2; ++set) {
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          lo[i] = (vw[4 * set + i] << 4U) & 0xf0f0f0f0U;  // dims 0,2,4,6 of the chunk
+          hi[i] = vw[4 * set + i] & 0xf0f0f0f0U;          // dims 1,3,5,7
+        }
+        uint32_t x0 = __byte_perm(lo[0], lo[1], 0x5140), x1 = __byte_perm(lo[2], lo[3], 0x5140);
+        uint32_t x2 = __byte_perm(lo[0], lo[1], 0x7362), x3 = __byte_perm(lo[2], lo[3], 0x7362);
+        bl[set][0] = __byte_perm(x0, x1, 0x5410); bl[set][1] = __byte_perm(x0, x1, 0x7632);
+        bl[set][2] = __byte_perm(x2, x3, 0x5410); bl[set][3] = __byte_perm(x2, x3, 0x7632);
+        x0 = __byte_perm(hi[0], hi[1], 0x5140); x1 = __byte_perm(hi[2], hi[3], 0x5140);
+        x2 = __byte_perm(hi[0], hi[1], 0x7362); x3 = __byte_perm(hi[2], hi[3], 0x7362);
+        bh[set][0] = __byte_perm(x0, x1, 0x5410); bh[set][1] = __byte_perm(x0, x1, 0x7632);
+        bh[set][2] = __byte_perm(x2, x3, 0x5410); bh[set][3] = __byte_perm(x2, x3, 0x7632);
+      }
+      const float prev_lo = rprev[16U * mt + g], prev_hi = rprev[16U * mt + g + 8U];
+      const float ps_lo = rpscale[16U * mt + g], ps_hi = rpscale[16U * mt + g + 8U];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // dim offset j inside the chunk: even -> bl[j/2], odd -> bh[j/2]
+        int c[4] = {0, 0, 0, 0};
+        const uint32_t b0 = (j & 1) ? bh[0][j >> 1] : bl[0][j >> 1];
+        const uint32_t b1 = (j & 1) ? bh[1][j >> 1] : bl[1][j >> 1];
+        mma_s8(c, pa0, pa1, pa2, pa3, b0, b1);
+        out[j][0] = out[j][0] * prev_lo + static_cast<float>(c[0]) * ps_lo;
+        out[j][1] = out[j][1] * prev_lo + static_cast<float>(c[1]) * ps_lo;
+        out[j][2] = out[j][2] * prev_hi + static_cast<float>(c[2]) * ps_hi;
+        out[j][3] = out[j][3] * prev_hi + static_cast<float>(c[3]) * ps_hi;
+      }
+    }
+    __syncthreads();
+  }
+  // ---- partials: C column n = 2t + e is B column (chunk) n -> dim 64*half + 8*n + j
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t mr = 16U * mt + g + (i >= 2 ? 8U : 0U);
+      if (mr >= MR) continue;
+      const uint32_t chunk = 2U * t + (i & 1U);
+      const uint32_t d = 64U * half + 8U * chunk + j;
+      const uint32_t row = mr / group, head = kvh * group + mr % group;
+      const size_t pidx = (static_cast<size_t>(row) * a.max_splits + split) * a.q_heads + head;
+      part.outputs[pidx * HD + d] = out[j][i];
+      if (d == 0U) { part.maxima[pidx] = rmax[mr]; part.sums[pidx] = rsum[mr]; }
+    }
+}
+
+// grid (q_heads, rows), block head_dim.
+__global__ void attention_combine_kernel(AttentionArgs a, Partials part) {
+  __shared__ float gmax, gsum;
+  const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
+  const uint32_t ctx = *a.first_position + a.position_offset + 1U + row;
+  const uint32_t active = (ctx + a.split_tokens - 1U) / a.split_tokens;
+  const size_t base = static_cast<size_t>(row) * a.max_splits * a.q_heads + head;
+  if (d == 0U) {
+    float m = kNegInf;
+    for (uint32_t s = 0; s < active; ++s) m = fmaxf(m, part.maxima[base + static_cast<size_t>(s) * a.q_heads]);
+    float sum = 0.0F;
+    for (uint32_t s = 0; s < active; ++s) {
+      const size_t p = base + static_cast<size_t>(s) * a.q_heads;
+      sum += part.sums[p] * expf(part.maxima[p] - m);
+    }
+    gmax = m;
+    gsum = sum;
+  }
+  __syncthreads();
+  float result = 0.0F;
+  for (uint32_t s = 0; s < active; ++s) {
+    const size_t p = base + static_cast<size_t>(s) * a.q_heads;
+    result += part.outputs[p * hd + d] * expf(part.maxima[p] - gmax);
+  }
+  a.out[(static_cast<size_t>(row) * a.q_heads + head) * hd + d] = actv(result / gsum, a.bf16);
+}
+
+int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
+  const uint32_t group = a.kv_heads ? a.q_heads / a.kv_heads : 0U;
+  const uint32_t MR = a.rows * group;
+  if (!a.rows || !group || a.q_heads % a.kv_heads || a.head_dim % 32U || a.head_dim > 256U ||
+      a.split_tokens % 32U || !a.split_tokens || a.page_tokens % 32U || !a.max_splits || MR > 64U)
+    return fail(QLLM_INVALID_ARGUMENT, "unsupported attention geometry");
+  const Partials part = partials_of(a);
+  const dim3 grid(a.kv_heads, a.max_splits);
+  if (a.impl == 1) {
+    if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 32U || a.query_row_stride % 4U)
+      return fail(QLLM_INVALID_ARGUMENT, "tensor-core attention needs Q4H, head_dim 128, rows*group <= 32");
+    attention_q4h_mma_kernel<<<grid, 128, 0, stream>>>(a, part);
+  } else {
+    const size_t smem = (static_cast<size_t>(MR) * a.head_dim + 32U * (a.head_dim + 1U) +
+                         2U * MR * 33U + 5U * MR + 64U) * sizeof(float);
+    auto set = [&](auto kernel) {
+      return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem));
+    };
+    cudaError_t e;
+    switch (a.encoding) {
+      case QLLM_KV_Q4H:
+        e = set(attention_scalar_kernel<QLLM_KV_Q4H>);
+        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_Q4H><<<grid, 256, smem, stream>>>(a, part);
+        break;
+      case QLLM_KV_Q8:
+        e = set(attention_scalar_kernel<QLLM_KV_Q8>);
+        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_Q8><<<grid, 256, smem, stream>>>(a, part);
+        break;
+      case QLLM_KV_F16:
+        e = set(attention_scalar_kernel<QLLM_KV_F16>);
+        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_F16><<<grid, 256, smem, stream>>>(a, part);
+        break;
+      default:
+        return fail(QLLM_INVALID_ARGUMENT, "unknown KV encoding");
+    }
+    if (e != cudaSuccess) return check_cuda(e, "attention shared memory opt-in");
+  }
+  attention_combine_kernel<<<dim3(a.q_heads, a.rows), a.head_dim, 0, stream>>>(a, part);
+  count_launch(2);
+  return check_launch("attention");
+}
+
+// ------------------------------------------------------- synthetic cache fill
+__device__ __forceinline__ uint32_t hash32(uint64_t x) {
+  x ^= x >> 33U; x *= 0xff51afd7ed558ccdULL; x ^= x >> 33U; x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33U;
+  return static_cast<uint32_t>(x);
+}
+// One thread per (token, kv head, K|V): writes a record with pseudo-random codes and a
+// scale near 0.2 (K and V magnitudes of a random-init decoder).
+__global__ void fill_synthetic_kv_kernel(uint8_t* const* page_table, size_t layer_offset,
+                                         uint32_t enc, uint32_t pt, uint32_t kv, uint32_t hd,
+                                         uint32_t first, uint32_t count, uint64_t seed) {
+  const uint64_t item = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (item >= static_cast<uint64_t>(count) * kv * 2U) return;
+  const uint32_t which = item & 1U;
+  const uint32_t h = (item >> 1U) % kv;
+  const uint32_t pos = first + static_cast<uint32_t>((item >> 1U) / kv);
+  uint8_t* layer = page_table[pos / pt] + layer_offset;
+  const size_t records = static_cast<size_t>(pt) * kv;
+  const uint32_t slot = pos % pt;
+  const uint64_t key = seed ^ (static_cast<uint64_t>(pos) << 20U) ^ (static_cast<uint64_t>(h) << 4U) ^ which;
+  const __half scale = __float2half_rn(0.1F + 0.2F * static_cast<float>(hash32(key) & 0xffffU) / 65536.0F);
+  if (enc == QLLM_KV_Q4H) {
+    const size_t rec = static_cast<size_t>(h) * pt + slot;
+    uint8_t* codes = layer + (which ? records * (hd / 2U) + records * 2U : 0U) + rec * (hd / 2U);
+    uint8_t* sc = layer + records * (hd / 2U) + (which ? records * (hd / 2U) + records * 2U : 0U);
+    reinterpret_cast<__half*>(sc)[rec] = scale;
+    for (uint32_t d = 0; d < hd / 2U; ++d) {
+      const uint32_t r = hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U);
+      int lo = static_cast<int>(r % 15U) - 7, hi = static_cast<int>((r >> 8U) % 15U) - 7;
+      codes[d] = static_cast<uint8_t>((lo & 15) | ((hi & 15) << 4));
+    }
+  } else if (enc == QLLM_KV_Q8) {
+    const size_t rec = static_cast<size_t>(slot) * kv + h;
+    uint8_t* r8 = layer + (which ? records * (hd + 2U) : 0U) + rec * (hd + 2U);
+    *reinterpret_cast<__half*>(r8 + hd) = __float2half_rn(__half2float(scale) / 16.0F);
+    for (uint32_t d = 0; d < hd; ++d)
+      r8[d] = static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U) % 255U) - 127));
+  } else {
+    const size_t rec = static_cast<size_t>(slot) * kv + h;
+    __half* r16 = reinterpret_cast<__half*>(layer + (which ? records * hd * 2U : 0U)) + rec * hd;
+    for (uint32_t d = 0; d < hd; ++d)
+      r16[d] = __float2half_rn((static_cast<float>(hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U) & 0xffffU) / 32768.0F - 1.0F) * 1.4F);
+  }
+}
+
+int launch_fill_synthetic_kv(uint8_t* const* page_table, size_t layer_offset, uint32_t encoding,
+                             uint32_t page_tokens, uint32_t kv_heads, uint32_t head_dim,
+                             uint32_t first, uint32_t count, uint64_t seed, cudaStream_t stream) {
+  const uint64_t items = static_cast<uint64_t>(count) * kv_heads * 2U;
+  if (!items) return 0;
+  fill_synthetic_kv_kernel<<<static_cast<unsigned>((items + 127U) / 128U), 128, 0, stream>>>(
+      page_table, layer_offset, encoding, page_tokens, kv_heads, head_dim, first, count, seed);
+  count_launch();
+  return check_launch("fill_synthetic_kv");
+}
+
+}  // namespace qllm

@@ -1,0 +1,779 @@
+// Host side of the B200 provider: the exact-decode subset of
+// expert::runtime::IOperationProvider (runtime/include/expert/runtime/program_executor.hpp:244-370)
+// over the kernel layer.  Control flow follows DenseFp4Provider::execute_exact_decode,
+// run_target, run_mtp, extend_mtp_rollout and synchronize_exact_decode_batch
+// (runtime/tools/dense_fp4_provider.cpp:11139-11318, 8529-8635, 8681-8852, 11011-11137),
+// re-arranged so that one step is a fixed launch sequence driven by device-resident
+// state: verify -> accept/rollback kernel -> draft passes, with one host read at the end.
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "gemv_mma.h"
+#include "kernels.h"
+
+namespace qllm {
+
+namespace {
+thread_local std::string g_error;
+unsigned long long g_launches = 0;
+}  // namespace
+
+void set_error(const std::string& message) { g_error = message; }
+int fail(int status, const std::string& message) {
+  g_error = message;
+  return status;
+}
+int check_cuda(cudaError_t error, const char* what) {
+  if (error == cudaSuccess) return 0;
+  return fail(QLLM_INTERNAL, std::string(what) + ": " + cudaGetErrorString(error));
+}
+int check_launch(const char* what) { return check_cuda(cudaPeekAtLastError(), what); }
+void count_launch(unsigned launches) { g_launches += launches; }
+unsigned long long launches_counted() { return g_launches; }
+
+struct Error : std::runtime_error {
+  int status;
+  Error(int s, const std::string& m) : std::runtime_error(m), status(s) {}
+};
+static void ok(int rc) {
+  if (rc) throw Error(rc, g_error);
+}
+static void cu(cudaError_t e, const char* what) { ok(check_cuda(e, what)); }
+
+template <typename T>
+struct DeviceBuffer {
+  T* p = nullptr;
+  size_t n = 0;
+  void alloc(size_t count, const char* what) {
+    release();
+    if (!count) return;
+    cu(cudaMalloc(&p, count * sizeof(T)), what);
+    n = count;
+  }
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    n = 0;
+  }
+  ~DeviceBuffer() { release(); }
+};
+
+struct Matrix {
+  qllm_matrix m{};           // device pointers
+  MmaWeights mma;            // tensor map + re-tiled scales for the tcgen05 kernel
+};
+struct Block {
+  const float* input_norm = nullptr;
+  const float* post_norm = nullptr;
+  Matrix qkv, o, gate_up, down;
+};
+
+}  // namespace qllm
+
+using namespace qllm;
+
+struct qllm_request_state {
+  uint8_t* slab = nullptr;          // page storage
+  uint8_t** page_table = nullptr;   // device array of page pointers
+  uint32_t pages = 0;
+  StepState* state = nullptr;       // device
+  qllm_exact_result* results = nullptr;  // device ring
+  float* retained_hidden = nullptr; // [kMaxRows, hidden] rows of the last prefill chunk
+  float* mtp_last_hidden = nullptr; // [hidden]
+  // host mirror of the invocation stream invariants
+  uint32_t mtp_length = 0;
+  uint32_t synchronized_token = 0;
+  bool draft_valid = false;
+  uint32_t draft_count = 0;
+  uint32_t retained_rows = 0;
+  uint32_t retained_first = 0;
+  uint32_t ring_cursor = 0;  // host mirror of StepState::step_index
+  bool request_bound = false;
+  qllm_request request{};
+  cudaGraphExec_t step_graph = nullptr;
+  uint32_t graph_splits = 0, graph_mtp_splits = 0;
+  int graph_sampled = -1, graph_gemv = -1;
+};
+
+struct qllm_provider {
+  static constexpr uint32_t kMaxRows = 8;      // kMaximumWorkspaceRows of the microbatch paths
+  static constexpr uint32_t kResultRing = 64;
+  qllm_config cfg{};
+  int device = 0;
+  bool borrowed = false;
+  cudaStream_t stream = nullptr;
+  std::mutex mutex;
+  std::vector<void*> owned;          // uploads
+  const uint16_t* embedding = nullptr;
+  std::vector<Block> layers;
+  const float* final_norm = nullptr;
+  Matrix head;
+  const float* mtp_embedding_norm = nullptr;
+  const float* mtp_hidden_norm = nullptr;
+  const float* mtp_draft_norm = nullptr;
+  Matrix mtp_fusion;
+  Block mtp_block;
+  DeviceBuffer<float> inv_freq;
+  std::vector<size_t> layer_off;
+  size_t page_bytes = 0;
+  // workspaces (rows <= kMaxRows)
+  DeviceBuffer<float> hidden, residual, normalized, qkv, attn, gate_up, inter, logits, xq, fused;
+  DeviceBuffer<float> mtp_emb, mtp_emb_norm, mtp_hid_norm, draft_logits;
+  DeviceBuffer<uint8_t> attn_ws, topk_ws, gemv_ws;
+  DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
+  DeviceBuffer<float> top_values;
+  uint32_t max_splits = 0;
+  int graph_mode = 0;
+  int gemv_impl = 0;
+  int attention_impl = 1;
+  uint32_t last_rows = 0;
+
+  // ---------------------------------------------------------------- weights
+  template <typename T>
+  const T* bring(const T* src, size_t count, bool on_device) {
+    if (!src) throw Error(QLLM_INVALID_ARGUMENT, "missing tensor");
+    if (on_device) return src;
+    void* d = nullptr;
+    cu(cudaMalloc(&d, count * sizeof(T)), "tensor upload allocation");
+    owned.push_back(d);
+    cu(cudaMemcpy(d, src, count * sizeof(T), cudaMemcpyHostToDevice), "tensor upload");
+    return static_cast<const T*>(d);
+  }
+  Matrix bring(const qllm_matrix& m, bool on_device, uint32_t rows, uint32_t cols, const char* name) {
+    if (m.rows != rows || m.cols != cols || cols % 16U || !(m.weight_scale > 0.0F) ||
+        !(m.input_scale > 0.0F))
+      throw Error(QLLM_INVALID_ARGUMENT, std::string("native NVFP4 matrix geometry is invalid: ") + name);
+    Matrix out;
+    out.m = m;
+    out.m.codes = bring(m.codes, static_cast<size_t>(rows) * cols / 2U, on_device);
+    out.m.scales = bring(m.scales, static_cast<size_t>(rows) * cols / 16U, on_device);
+    ok(out.mma.prepare(out.m, stream));
+    return out;
+  }
+  Block bring(const qllm_block& b, bool on_device) {
+    const auto& c = cfg;
+    Block out;
+    out.input_norm = bring(b.input_norm, c.hidden, on_device);
+    out.post_norm = bring(b.post_norm, c.hidden, on_device);
+    out.qkv = bring(b.qkv, on_device, (c.q_heads + 2U * c.kv_heads) * c.head_dim, c.hidden, "qkv");
+    out.o = bring(b.o, on_device, c.hidden, c.q_heads * c.head_dim, "o");
+    out.gate_up = bring(b.gate_up, on_device, 2U * c.ffn, c.hidden, "gate_up");
+    out.down = bring(b.down, on_device, c.hidden, c.ffn, "down");
+    return out;
+  }
+
+  void create(const qllm_config& config, const qllm_weights& w, bool on_device, int dev) {
+    cfg = config;
+    const auto& c = cfg;
+    if (!c.layers || !c.hidden || !c.kv_heads || !c.q_heads || c.q_heads % c.kv_heads ||
+        c.head_dim % 32U || c.head_dim > 256U || c.hidden % 16U || c.ffn % 16U || !c.page_tokens ||
+        c.page_tokens % 32U || !c.draft_depth || c.draft_depth > 4U || !c.split_tokens ||
+        c.split_tokens % 32U || c.draft_vocab > c.vocab || !c.draft_vocab || !c.max_context ||
+        c.kv_encoding > 2U || c.mtp_kv_encoding > 2U || c.rotary_dim > c.head_dim || c.rotary_dim % 2U ||
+        kMaxRows * (c.q_heads / c.kv_heads) > 64U)
+      throw Error(QLLM_INVALID_ARGUMENT, "provider does not support this model geometry");
+    device = dev;
+    borrowed = on_device;
+    cu(cudaSetDevice(device), "select device");
+    cu(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "create stream");
+    embedding = bring(w.embedding, static_cast<size_t>(c.vocab) * c.hidden, on_device);
+    for (uint32_t l = 0; l < c.layers; ++l) layers.push_back(bring(w.layers[l], on_device));
+    final_norm = bring(w.final_norm, c.hidden, on_device);
+    head = bring(w.head, on_device, c.vocab, c.hidden, "head");
+    mtp_embedding_norm = bring(w.mtp_embedding_norm, c.hidden, on_device);
+    mtp_hidden_norm = bring(w.mtp_hidden_norm, c.hidden, on_device);
+    mtp_draft_norm = bring(w.mtp_draft_norm, c.hidden, on_device);
+    mtp_fusion = bring(w.mtp_fusion, on_device, c.hidden, 2U * c.hidden, "fusion");
+    mtp_block = bring(w.mtp_block, on_device);
+
+    std::vector<float> inv(c.rotary_dim / 2U);
+    for (uint32_t p = 0; p < inv.size(); ++p)
+      inv[p] = std::pow(c.rope_theta, -2.0F * static_cast<float>(p) / static_cast<float>(c.rotary_dim));
+    inv_freq.alloc(inv.size() ? inv.size() : 1, "rope table");
+    if (!inv.empty())
+      cu(cudaMemcpy(inv_freq.p, inv.data(), inv.size() * sizeof(float), cudaMemcpyHostToDevice), "rope table");
+
+    size_t off = 0;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+      layer_off.push_back(off);
+      off += kv_layer_bytes(c.kv_encoding, c.page_tokens, c.kv_heads, c.head_dim);
+    }
+    layer_off.push_back(off);
+    off += kv_layer_bytes(c.mtp_kv_encoding, c.page_tokens, c.kv_heads, c.head_dim);
+    page_bytes = (off + 255U) & ~static_cast<size_t>(255U);
+
+    const uint32_t R = kMaxRows;
+    const uint32_t qkv_w = (c.q_heads + 2U * c.kv_heads) * c.head_dim;
+    hidden.alloc(static_cast<size_t>(R) * c.hidden, "hidden");
+    residual.alloc(static_cast<size_t>(R) * c.hidden, "residual");
+    normalized.alloc(static_cast<size_t>(R) * c.hidden, "normalized");
+    qkv.alloc(static_cast<size_t>(R) * qkv_w, "qkv");
+    attn.alloc(static_cast<size_t>(R) * c.q_heads * c.head_dim, "attention");
+    gate_up.alloc(static_cast<size_t>(R) * 2U * c.ffn, "gate_up");
+    inter.alloc(static_cast<size_t>(R) * c.ffn, "intermediate");
+    logits.alloc(static_cast<size_t>(R) * c.vocab, "logits");
+    const uint32_t widest = std::max(std::max(2U * c.hidden, c.ffn), c.q_heads * c.head_dim);
+    xq.alloc(static_cast<size_t>(R) * widest, "quantised activations");
+    fused.alloc(static_cast<size_t>(R) * 2U * c.hidden, "fusion input");
+    mtp_emb.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding");
+    mtp_emb_norm.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding norm");
+    mtp_hid_norm.alloc(static_cast<size_t>(R) * c.hidden, "draft hidden norm");
+    draft_logits.alloc(c.draft_vocab, "draft logits");
+    // the page pool keeps a few slots of slack past max_context for speculative rows
+    max_splits = (c.max_context + 2U * kMaxRows + c.split_tokens - 1U) / c.split_tokens;
+    attn_ws.alloc(attention_workspace_bytes(R, c.q_heads, c.head_dim, max_splits), "attention partials");
+    topk_ws.alloc(topk_workspace_bytes(R, c.vocab, 64), "top-k partials");
+    const uint32_t most_rows = std::max(std::max(c.vocab, 2U * c.ffn), qkv_w);
+    gemv_ws.alloc(gemv_mma_workspace_bytes(R, most_rows, widest), "GEMV workspace");
+    argmax_out.alloc(R, "argmax");
+    top_tokens.alloc(static_cast<size_t>(R) * 64U, "top-k tokens");
+    top_values.alloc(static_cast<size_t>(R) * 64U, "top-k values");
+    tokens_dev.alloc(R, "token upload");
+    first_token_dev.alloc(1, "first token");
+    verify_hidden.alloc(static_cast<size_t>(R) * c.hidden, "verify hidden rows");
+    cu(cudaStreamSynchronize(stream), "provider set-up");
+  }
+
+  ~qllm_provider() {
+    for (void* p : owned) cudaFree(p);
+    if (stream) cudaStreamDestroy(stream);
+  }
+
+  // ------------------------------------------------------------------ ops
+  // y[rows, row_count] = bf16(fakequant(x) . W[first_row..]^T)
+  void project(const Matrix& w, const float* x, float* y, uint32_t rows, uint32_t first_row = 0,
+               uint32_t row_count = 0) {
+    if (!row_count) row_count = w.m.rows;
+    if (gemv_impl == 1) {
+      ok(launch_gemv_mma(w.mma, w.m, first_row, row_count, x, y, rows, gemv_ws.p, gemv_ws.n, stream));
+    } else {
+      ok(launch_act_quant_i8(x, xq.p, rows, w.m.cols, w.m.input_scale, stream));
+      ok(launch_gemv_simt(w.m, first_row, row_count, xq.p, rows, y, rows, stream));
+    }
+  }
+
+  // One transformer block over `rows` rows held in hidden: attention sub-block
+  // (run_full_attention + residual add) then FFN (run_ffn), pre-norm / ABI 1.
+  void block(const Block& b, uint32_t rows, uint32_t enc, size_t layer_offset,
+             qllm_request_state& st, const uint32_t* first_position, uint32_t position_offset,
+             uint32_t rotary_offset, uint32_t splits) {
+    const auto& c = cfg;
+    const bool bf = c.activation_bf16 != 0U;
+    const uint32_t qkv_w = (c.q_heads + 2U * c.kv_heads) * c.head_dim;
+    cu(cudaMemcpyAsync(residual.p, hidden.p, static_cast<size_t>(rows) * c.hidden * sizeof(float),
+                       cudaMemcpyDeviceToDevice, stream), "retain attention residual");
+    ok(launch_rms_norm(hidden.p, b.input_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
+    project(b.qkv, normalized.p, qkv.p, rows);
+    RopeStoreArgs rs{qkv.p, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
+                     first_position, position_offset, rotary_offset, st.page_table, layer_offset,
+                     c.page_tokens, enc, bf};
+    ok(launch_rope_kv_store(rs, stream));
+    AttentionArgs at{};
+    at.encoding = enc;
+    at.page_table = st.page_table;
+    at.layer_offset = layer_offset;
+    at.page_tokens = c.page_tokens;
+    at.query = qkv.p;
+    at.query_row_stride = qkv_w;
+    at.rows = rows;
+    at.first_position = first_position;
+    at.position_offset = position_offset;
+    at.q_heads = c.q_heads;
+    at.kv_heads = c.kv_heads;
+    at.head_dim = c.head_dim;
+    at.split_tokens = c.split_tokens;
+    at.max_splits = splits;
+    at.bf16 = bf;
+    at.workspace = attn_ws.p;
+    at.out = attn.p;
+    at.impl = (attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
+               rows * (c.q_heads / c.kv_heads) <= 32U) ? 1 : 0;
+    ok(launch_attention(at, stream));
+    project(b.o, attn.p, hidden.p, rows);
+    ok(launch_add(hidden.p, residual.p, static_cast<uint64_t>(rows) * c.hidden, bf, stream));
+    cu(cudaMemcpyAsync(residual.p, hidden.p, static_cast<size_t>(rows) * c.hidden * sizeof(float),
+                       cudaMemcpyDeviceToDevice, stream), "retain FFN residual");
+    ok(launch_rms_norm(hidden.p, b.post_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
+    project(b.gate_up, normalized.p, gate_up.p, rows);
+    ok(launch_silu_product(gate_up.p, inter.p, rows, c.ffn, bf, stream));
+    project(b.down, inter.p, hidden.p, rows);
+    ok(launch_add(hidden.p, residual.p, static_cast<uint64_t>(rows) * c.hidden, bf, stream));
+  }
+
+  uint32_t splits_for(uint32_t tokens) const {
+    return std::min(max_splits, (tokens + cfg.split_tokens - 1U) / cfg.split_tokens);
+  }
+
+  // run_target: tokens (device) at positions *first_position + r.
+  void run_target(qllm_request_state& st, const uint32_t* tokens, uint32_t rows,
+                  const uint32_t* first_position, uint32_t splits, bool with_head) {
+    const auto& c = cfg;
+    ok(launch_embedding(embedding, tokens, hidden.p, rows, c.hidden, c.vocab, stream));
+    for (uint32_t l = 0; l < c.layers; ++l)
+      block(layers[l], rows, c.kv_encoding, layer_off[l], st, first_position, 0U, 0U, splits);
+    last_rows = rows;
+    if (with_head) {
+      ok(launch_rms_norm(hidden.p, final_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
+      project(head, normalized.p, logits.p, rows);
+    }
+  }
+
+  // Candidate selection of `rows` logit rows for the sampler.
+  void select_candidates(const float* values, uint32_t rows, uint32_t count, uint32_t stride,
+                         bool sampled, uint32_t top_k) {
+    if (sampled)
+      ok(launch_topk(values, rows, count, stride, top_k, top_values.p, top_tokens.p, topk_ws.p, stream));
+    else
+      ok(launch_argmax(values, rows, count, stride, argmax_out.p, stream));
+  }
+
+  // run_mtp over `rows` rows: tokens (device), previous hidden rows (device),
+  // cache position of row r = *first_position + position_offset + r.
+  // When `select_row` is set the draft head runs on that row (device index).
+  void run_mtp(qllm_request_state& st, const uint32_t* tokens, const float* previous_hidden,
+               uint32_t rows, const uint32_t* first_position, uint32_t position_offset,
+               uint32_t splits, bool produce, const uint32_t* select_row, bool sampled,
+               uint32_t top_k) {
+    const auto& c = cfg;
+    ok(launch_embedding(embedding, tokens, mtp_emb.p, rows, c.hidden, c.vocab, stream));
+    // [norm(embedding) | norm(previous hidden)] written straight into the fusion input
+    ok(launch_rms_norm(mtp_emb.p, mtp_embedding_norm, fused.p, rows, c.hidden, c.hidden, 2U * c.hidden, c.eps, nullptr, stream));
+    ok(launch_rms_norm(previous_hidden, mtp_hidden_norm, fused.p + c.hidden, rows, c.hidden, c.hidden, 2U * c.hidden, c.eps, nullptr, stream));
+    project(mtp_fusion, fused.p, hidden.p, rows);
+    block(mtp_block, rows, c.mtp_kv_encoding, layer_off[c.layers], st, first_position,
+          position_offset, 1U, splits);
+    if (!produce) return;
+    ok(launch_copy_rows(st.mtp_last_hidden, c.hidden, hidden.p, c.hidden, 1, c.hidden, select_row, stream));
+    ok(launch_rms_norm(st.mtp_last_hidden, mtp_draft_norm, normalized.p, 1, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
+    project(head, normalized.p, draft_logits.p, 1, 0, c.draft_vocab);
+    select_candidates(draft_logits.p, 1, c.draft_vocab, c.draft_vocab, sampled, top_k);
+  }
+
+  // Draft passes after the first: chained on the draft block's own last hidden.
+  void rollout(qllm_request_state& st, uint32_t splits, bool sampled, uint32_t top_k) {
+    const auto& c = cfg;
+    for (uint32_t i = 1; i < c.draft_depth; ++i) {
+      run_mtp(st, &st.state->verify_tokens[i], st.mtp_last_hidden, 1, &st.state->new_position,
+              i - 1U, splits, true, nullptr, sampled, top_k);
+      DraftSampleArgs ds{st.state, argmax_out.p, top_values.p, top_tokens.p,
+                         i | (i + 1U == c.draft_depth ? 0x80000000U : 0U), 0U};
+      ok(launch_draft_sample(ds, stream));
+    }
+  }
+
+  // The launch sequence of one speculative step (captured into a graph when enabled).
+  void enqueue_step(qllm_request_state& st, uint32_t splits, uint32_t mtp_splits, bool sampled,
+                    uint32_t top_k) {
+    const auto& c = cfg;
+    const uint32_t R = c.draft_depth + 1U;
+    StepState* s = st.state;
+    run_target(st, s->verify_tokens, R, &s->position, splits, true);
+    select_candidates(logits.p, R, c.vocab, c.vocab, sampled, top_k);
+    AcceptArgs aa{s, argmax_out.p, top_values.p, top_tokens.p, st.results, kResultRing};
+    ok(launch_accept(aa, stream));
+    // first draft pass: accepted drafts + selected token against the target's hidden rows;
+    // rows past accepted+1 are padding whose cache records are overwritten before any read
+    run_mtp(st, s->mtp_tokens, hidden_rows_for_mtp(), R, &s->position, 0U, mtp_splits, true,
+            &s->accepted, sampled, top_k);
+    DraftSampleArgs ds{s, argmax_out.p, top_values.p, top_tokens.p,
+                       0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 0U};
+    ok(launch_draft_sample(ds, stream));
+    rollout(st, mtp_splits, sampled, top_k);
+  }
+
+  // run_mtp reuses `hidden` as its working buffer, so the verify rows are parked first.
+  DeviceBuffer<float> verify_hidden;
+  const float* hidden_rows_for_mtp() {
+    const auto& c = cfg;
+    cu(cudaMemcpyAsync(verify_hidden.p, hidden.p, static_cast<size_t>(last_rows) * c.hidden * sizeof(float),
+                       cudaMemcpyDeviceToDevice, stream), "park verify hidden rows");
+    return verify_hidden.p;
+  }
+
+  void bind_request(qllm_request_state& st, const qllm_request& rq) {
+    if (rq.sampling_temperature_ppm > 2000000U ||
+        (rq.sampling_temperature_ppm != 0U &&
+         (rq.sampling_top_k == 0U || rq.sampling_top_k > 64U || rq.sampling_top_k > cfg.draft_vocab ||
+          rq.sampling_top_p_ppm == 0U || rq.sampling_top_p_ppm > 1000000U ||
+          rq.sampling_min_p_ppm > 1000000U)))
+      throw Error(QLLM_INVALID_ARGUMENT, "sampled exact decode requires bounded nonzero top-k");
+    if (rq.reserved_context_tokens > cfg.max_context)
+      throw Error(QLLM_INVALID_ARGUMENT, "request context exceeds the provider's max_context");
+    if (st.request_bound && !std::memcmp(&st.request, &rq, sizeof(rq))) return;
+    StepState head{};
+    head.seed = rq.sampling_seed;
+    head.temperature_ppm = rq.sampling_temperature_ppm;
+    head.top_p_ppm = rq.sampling_top_p_ppm;
+    head.top_k = rq.sampling_top_k;
+    head.min_p_ppm = rq.sampling_min_p_ppm;
+    head.context_limit = rq.reserved_context_tokens;
+    head.draft_depth = cfg.draft_depth;
+    cu(cudaMemcpyAsync(st.state, &head, offsetof(StepState, position), cudaMemcpyHostToDevice, stream),
+       "bind request parameters");
+    st.request = rq;
+    st.request_bound = true;
+  }
+
+  template <typename T>
+  void poke(T* device_field, const T& value) {
+    cu(cudaMemcpyAsync(device_field, &value, sizeof(T), cudaMemcpyHostToDevice, stream), "state update");
+  }
+};
+
+// ------------------------------------------------------------------- C ABI
+namespace {
+
+template <typename F>
+int guarded(F&& body) {
+  try {
+    body();
+    return QLLM_OK;
+  } catch (const Error& e) {
+    return fail(e.status, e.what());
+  } catch (const std::exception& e) {
+    return fail(QLLM_INTERNAL, e.what());
+  }
+}
+
+void check_device_error(qllm_provider& p, qllm_request_state& st) {
+  uint32_t error = 0;
+  cu(cudaMemcpyAsync(&error, &st.state->error, sizeof(error), cudaMemcpyDeviceToHost, p.stream), "read step status");
+  cu(cudaStreamSynchronize(p.stream), "step");
+  if (error) throw Error(QLLM_INTERNAL, "exact MTP step failed on the device (code " + std::to_string(error) + ")");
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* qllm_last_error(void) { return g_error.c_str(); }
+const char* qllm_capability_name(void) { return "decode.mtp.dense-full-attention.nvfp4-block16.exact.v1"; }
+uint32_t qllm_capability_abi(void) { return 2U; }
+
+int qllm_provider_create(const qllm_config* config, const qllm_weights* weights,
+                         int weights_on_device, int device, qllm_provider** out) {
+  if (!config || !weights || !out) return fail(QLLM_INVALID_ARGUMENT, "null provider argument");
+  *out = nullptr;
+  auto p = std::make_unique<qllm_provider>();
+  const int rc = guarded([&] { p->create(*config, *weights, weights_on_device != 0, device); });
+  if (rc) return rc;
+  *out = p.release();
+  return QLLM_OK;
+}
+
+void qllm_provider_destroy(qllm_provider* p) { delete p; }
+
+int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** out) {
+  if (!p || !out) return fail(QLLM_INVALID_ARGUMENT, "null request-state argument");
+  *out = nullptr;
+  auto st = std::make_unique<qllm_request_state>();
+  const int rc = guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    st->pages = (c.max_context + 2U * qllm_provider::kMaxRows + c.page_tokens - 1U) / c.page_tokens;
+    cu(cudaMalloc(&st->slab, static_cast<size_t>(st->pages) * p->page_bytes), "KV page pool");
+    cu(cudaMemsetAsync(st->slab, 0, static_cast<size_t>(st->pages) * p->page_bytes, p->stream), "clear KV pages");
+    std::vector<uint8_t*> table(st->pages);
+    for (uint32_t i = 0; i < st->pages; ++i) table[i] = st->slab + static_cast<size_t>(i) * p->page_bytes;
+    cu(cudaMalloc(&st->page_table, st->pages * sizeof(uint8_t*)), "page table");
+    cu(cudaMemcpyAsync(st->page_table, table.data(), st->pages * sizeof(uint8_t*), cudaMemcpyHostToDevice, p->stream), "page table");
+    cu(cudaMalloc(&st->state, sizeof(StepState)), "step state");
+    cu(cudaMemsetAsync(st->state, 0, sizeof(StepState), p->stream), "step state");
+    cu(cudaMalloc(&st->results, qllm_provider::kResultRing * sizeof(qllm_exact_result)), "result ring");
+    cu(cudaMalloc(&st->retained_hidden, static_cast<size_t>(qllm_provider::kMaxRows) * c.hidden * sizeof(float)), "retained hidden");
+    cu(cudaMalloc(&st->mtp_last_hidden, c.hidden * sizeof(float)), "draft hidden");
+    cu(cudaStreamSynchronize(p->stream), "request state set-up");
+  });
+  if (rc) {
+    qllm_provider_destroy_request_state(p, st.release());
+    return rc;
+  }
+  *out = st.release();
+  return QLLM_OK;
+}
+
+void qllm_provider_destroy_request_state(qllm_provider* p, qllm_request_state* st) {
+  if (!st) return;
+  if (p) cudaSetDevice(p->device);
+  if (st->step_graph) cudaGraphExecDestroy(st->step_graph);
+  cudaFree(st->slab);
+  cudaFree(st->page_table);
+  cudaFree(st->state);
+  cudaFree(st->results);
+  cudaFree(st->retained_hidden);
+  cudaFree(st->mtp_last_hidden);
+  delete st;
+}
+
+int qllm_provider_prefill_chunk(qllm_provider* p, qllm_request_state* st, const uint32_t* tokens,
+                                uint32_t count, uint32_t first_position) {
+  if (!p || !st || !tokens) return fail(QLLM_INVALID_ARGUMENT, "null prefill argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    if (!count || count > qllm_provider::kMaxRows || first_position + count > c.max_context)
+      throw Error(QLLM_INVALID_ARGUMENT, "invalid target-model microbatch");
+    for (uint32_t r = 0; r < count; ++r)
+      if (tokens[r] >= c.vocab) throw Error(QLLM_INVALID_ARGUMENT, "target token exceeds vocabulary");
+    cu(cudaMemcpyAsync(p->tokens_dev.p, tokens, count * sizeof(uint32_t), cudaMemcpyHostToDevice, p->stream), "upload embedding token batch");
+    p->poke(&st->state->position, first_position);
+    p->run_target(*st, p->tokens_dev.p, count, &st->state->position, p->splits_for(first_position + count), true);
+    cu(cudaMemcpyAsync(st->retained_hidden, p->hidden.p, static_cast<size_t>(count) * c.hidden * sizeof(float),
+                       cudaMemcpyDeviceToDevice, p->stream), "retain target hidden rows");
+    cu(cudaStreamSynchronize(p->stream), "prefill chunk");
+    st->retained_rows = count;
+    st->retained_first = first_position;
+  });
+}
+
+int qllm_provider_first_token(qllm_provider* p, qllm_request_state* st, const qllm_request* rq,
+                              uint32_t sample_position, uint32_t* token) {
+  if (!p || !st || !rq || !token) return fail(QLLM_INVALID_ARGUMENT, "null first-token argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    if (!st->retained_rows) throw Error(QLLM_INVALID_ARGUMENT, "no prefill rows retained");
+    p->bind_request(*st, *rq);
+    const bool sampled = rq->sampling_temperature_ppm != 0U;
+    const float* row = p->logits.p + static_cast<size_t>(st->retained_rows - 1U) * c.vocab;
+    p->select_candidates(row, 1, c.vocab, c.vocab, sampled, rq->sampling_top_k);
+    ok(launch_first_token(st->state, p->argmax_out.p, p->top_values.p, p->top_tokens.p, sample_position,
+                          p->first_token_dev.p, p->stream));
+    cu(cudaMemcpyAsync(token, p->first_token_dev.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, p->stream), "copy first token");
+    check_device_error(*p, *st);
+  });
+}
+
+int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_state* st,
+                                                 const qllm_request* rq, const uint32_t* next_tokens,
+                                                 uint32_t count, uint32_t first_target_position,
+                                                 int produce_final_draft) {
+  if (!p || !st || !rq || !next_tokens) return fail(QLLM_INVALID_ARGUMENT, "null synchronization argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    if (!count || count > qllm_provider::kMaxRows || count != st->retained_rows ||
+        first_target_position != st->retained_first || st->mtp_length != first_target_position ||
+        first_target_position + count + 1U > c.max_context)
+      throw Error(QLLM_INVALID_ARGUMENT, "MTP synchronization stream is invalid");
+    for (uint32_t r = 0; r < count; ++r)
+      if (next_tokens[r] >= c.vocab) throw Error(QLLM_INVALID_ARGUMENT, "MTP synchronization stream is invalid");
+    p->bind_request(*st, *rq);
+    const bool sampled = rq->sampling_temperature_ppm != 0U;
+    const bool produce = produce_final_draft != 0;
+    if (produce && (rq->reserved_context_tokens > c.max_context ||
+                    first_target_position + count + 1U >= rq->reserved_context_tokens))
+      throw Error(QLLM_INVALID_ARGUMENT, "MTP rollout root exceeds context");
+    st->draft_valid = false;
+    st->synchronized_token = next_tokens[count - 1U];
+    cu(cudaMemcpyAsync(p->tokens_dev.p, next_tokens, count * sizeof(uint32_t), cudaMemcpyHostToDevice, p->stream), "upload MTP token batch");
+    StepState* s = st->state;
+    p->poke(&s->position, first_target_position);
+    p->poke(&s->new_position, first_target_position + count);
+    p->poke(&s->accepted, count - 1U);
+    p->poke(&s->next_token, st->synchronized_token);
+    p->poke(&s->draft_count, 0U);
+    const uint32_t splits = p->splits_for(first_target_position + count + c.draft_depth);
+    p->run_mtp(*st, p->tokens_dev.p, st->retained_hidden, count, &s->position, 0U, splits, produce,
+               &s->accepted, sampled, rq->sampling_top_k);
+    if (produce) {
+      DraftSampleArgs ds{s, p->argmax_out.p, p->top_values.p, p->top_tokens.p,
+                         0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 1U};
+      ok(launch_draft_sample(ds, p->stream));
+      p->rollout(*st, splits, sampled, rq->sampling_top_k);
+      uint32_t drafts = 0;
+      cu(cudaMemcpyAsync(&drafts, &s->draft_count, sizeof(drafts), cudaMemcpyDeviceToHost, p->stream), "read draft count");
+      check_device_error(*p, *st);
+      st->draft_count = drafts;
+      st->draft_valid = drafts != 0U;
+    } else {
+      p->poke(&s->position, first_target_position + count);
+      cu(cudaStreamSynchronize(p->stream), "MTP synchronization");
+    }
+    st->mtp_length = first_target_position + count;
+    st->retained_rows = 0;
+  });
+}
+
+static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_request* rq,
+                      uint32_t context_limit, uint32_t steps, qllm_exact_result* results) {
+  const auto& c = p->cfg;
+  const uint32_t R = c.draft_depth + 1U;
+  if (!steps || steps > qllm_provider::kResultRing)
+    throw Error(QLLM_INVALID_ARGUMENT, "step count exceeds the result ring");
+  // every enqueued step may advance by up to R positions and writes R speculative rows
+  const uint32_t reach = st->mtp_length + steps * R + 2U * c.draft_depth + 2U;
+  if (reach >= context_limit)
+    throw Error(QLLM_INVALID_ARGUMENT, "multi-draft MTP state is invalid: too close to the context limit");
+  const bool sampled = rq->sampling_temperature_ppm != 0U;
+  const uint32_t splits = p->splits_for(st->mtp_length + steps * R + R);
+  const uint32_t mtp_splits = splits;
+  StepState* s = st->state;
+  const uint32_t ring_start = st->ring_cursor;
+  if (p->graph_mode) {
+    if (!st->step_graph || st->graph_splits != splits || st->graph_sampled != static_cast<int>(sampled) ||
+        st->graph_gemv != p->gemv_impl) {
+      if (st->step_graph) { cudaGraphExecDestroy(st->step_graph); st->step_graph = nullptr; }
+      cudaGraph_t graph = nullptr;
+      cu(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeThreadLocal), "begin step capture");
+      try {
+        p->enqueue_step(*st, splits, mtp_splits, sampled, rq->sampling_top_k);
+      } catch (...) {
+        cudaStreamEndCapture(p->stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        throw;
+      }
+      cu(cudaStreamEndCapture(p->stream, &graph), "end step capture");
+      const cudaError_t e = cudaGraphInstantiate(&st->step_graph, graph, 0);
+      cudaGraphDestroy(graph);
+      cu(e, "instantiate step graph");
+      st->graph_splits = splits;
+      st->graph_sampled = sampled;
+      st->graph_gemv = p->gemv_impl;
+    }
+    for (uint32_t i = 0; i < steps; ++i) cu(cudaGraphLaunch(st->step_graph, p->stream), "launch step graph");
+  } else {
+    for (uint32_t i = 0; i < steps; ++i) p->enqueue_step(*st, splits, mtp_splits, sampled, rq->sampling_top_k);
+  }
+  std::vector<qllm_exact_result> ring(qllm_provider::kResultRing);
+  cu(cudaMemcpyAsync(ring.data(), st->results, ring.size() * sizeof(qllm_exact_result), cudaMemcpyDeviceToHost, p->stream), "read step results");
+  uint32_t drafts = 0;
+  cu(cudaMemcpyAsync(&drafts, &s->draft_count, sizeof(drafts), cudaMemcpyDeviceToHost, p->stream), "read draft count");
+  check_device_error(*p, *st);
+  st->ring_cursor += steps;
+  for (uint32_t i = 0; i < steps; ++i) {
+    results[i] = ring[(ring_start + i) % qllm_provider::kResultRing];
+    st->mtp_length += results[i].positions_advanced;
+    st->synchronized_token = results[i].next_token;
+  }
+  st->draft_count = drafts;
+  st->draft_valid = drafts != 0U;
+}
+
+int qllm_provider_execute_exact_decode(qllm_provider* p, qllm_request_state* st,
+                                       const qllm_request* rq, uint32_t guaranteed_token,
+                                       uint32_t position, uint32_t context_limit,
+                                       qllm_exact_result* result) {
+  if (!p || !st || !rq || !result) return fail(QLLM_INVALID_ARGUMENT, "null exact-decode argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    if (!st->draft_valid || guaranteed_token != st->synchronized_token || position != st->mtp_length ||
+        position + 1U >= context_limit || context_limit > p->cfg.max_context ||
+        context_limit != rq->reserved_context_tokens)
+      throw Error(QLLM_INVALID_ARGUMENT, "exact MTP invocation stream is invalid");
+    p->bind_request(*st, *rq);
+    run_steps(p, st, rq, context_limit, 1U, result);
+  });
+}
+
+int qllm_provider_execute_exact_decode_steps(qllm_provider* p, qllm_request_state* st,
+                                             const qllm_request* rq, uint32_t context_limit,
+                                             uint32_t steps, qllm_exact_result* results) {
+  if (!p || !st || !rq || !results) return fail(QLLM_INVALID_ARGUMENT, "null exact-decode argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    if (!st->draft_valid || context_limit > p->cfg.max_context || context_limit != rq->reserved_context_tokens)
+      throw Error(QLLM_INVALID_ARGUMENT, "exact MTP invocation stream is invalid");
+    p->bind_request(*st, *rq);
+    run_steps(p, st, rq, context_limit, steps, results);
+  });
+}
+
+int qllm_provider_telemetry(qllm_provider* p, qllm_request_state* st, uint64_t* out, uint32_t count) {
+  if (!p || !st || !out || count < 8U) return fail(QLLM_INVALID_ARGUMENT, "telemetry needs 8 slots");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    cu(cudaStreamSynchronize(p->stream), "sync");
+    StepState host;
+    cu(cudaMemcpy(&host, st->state, offsetof(StepState, drafts), cudaMemcpyDeviceToHost), "read counters");
+    std::memset(out, 0, count * sizeof(uint64_t));
+    out[0] = host.exact_calls;
+    out[1] = host.accepted_drafts;
+    for (int i = 0; i < 5; ++i) out[2 + i] = host.accepted_depth_calls[i];
+    out[7] = launches_counted();
+  });
+}
+
+int qllm_provider_set_graph_mode(qllm_provider* p, int enabled) {
+  if (!p) return fail(QLLM_INVALID_ARGUMENT, "null provider");
+  p->graph_mode = enabled != 0;
+  return QLLM_OK;
+}
+int qllm_provider_set_gemv_impl(qllm_provider* p, int impl) {
+  if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
+  p->gemv_impl = impl;
+  return QLLM_OK;
+}
+
+int qllm_provider_read_logits(qllm_provider* p, float* out, uint32_t rows) {
+  if (!p || !out || rows > qllm_provider::kMaxRows) return fail(QLLM_INVALID_ARGUMENT, "invalid logits read");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    cu(cudaStreamSynchronize(p->stream), "sync");
+    cu(cudaMemcpy(out, p->logits.p, static_cast<size_t>(rows) * p->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost), "read logits");
+  });
+}
+int qllm_provider_read_hidden(qllm_provider* p, qllm_request_state* st, int which, float* out, uint32_t rows) {
+  if (!p || !st || !out || rows > qllm_provider::kMaxRows) return fail(QLLM_INVALID_ARGUMENT, "invalid hidden read");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    cu(cudaStreamSynchronize(p->stream), "sync");
+    const float* src = which ? p->verify_hidden.p : st->retained_hidden;
+    cu(cudaMemcpy(out, src, static_cast<size_t>(rows) * p->cfg.hidden * sizeof(float), cudaMemcpyDeviceToHost), "read hidden");
+  });
+}
+int qllm_provider_read_drafts(qllm_provider* p, qllm_request_state* st, uint32_t* tokens, uint32_t* count) {
+  if (!p || !st || !tokens || !count) return fail(QLLM_INVALID_ARGUMENT, "invalid drafts read");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    cu(cudaStreamSynchronize(p->stream), "sync");
+    StepState host;
+    cu(cudaMemcpy(&host, st->state, offsetof(StepState, drafts), cudaMemcpyDeviceToHost), "read drafts");
+    *count = host.draft_count;
+    for (uint32_t i = 0; i < host.draft_count && i < 4U; ++i) tokens[i] = host.verify_tokens[i + 1U];
+  });
+}
+size_t qllm_provider_page_bytes(qllm_provider* p) { return p ? p->page_bytes : 0; }
+size_t qllm_provider_layer_offset(qllm_provider* p, uint32_t layer) {
+  return p && layer < p->layer_off.size() ? p->layer_off[layer] : 0;
+}
+int qllm_provider_read_page(qllm_provider* p, qllm_request_state* st, uint32_t page, uint8_t* out) {
+  if (!p || !st || !out || page >= st->pages) return fail(QLLM_INVALID_ARGUMENT, "invalid page read");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    cu(cudaStreamSynchronize(p->stream), "sync");
+    cu(cudaMemcpy(out, st->slab + static_cast<size_t>(page) * p->page_bytes, p->page_bytes, cudaMemcpyDeviceToHost), "read page");
+  });
+}
+
+int qllm_provider_fill_synthetic_kv(qllm_provider* p, qllm_request_state* st, uint32_t first,
+                                    uint32_t count, uint64_t seed) {
+  if (!p || !st) return fail(QLLM_INVALID_ARGUMENT, "null synthetic-fill argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    if (first != st->mtp_length || first + count > c.max_context)
+      throw Error(QLLM_INVALID_ARGUMENT, "synthetic cache fill must extend the cached prefix");
+    for (uint32_t l = 0; l <= c.layers; ++l)
+      ok(launch_fill_synthetic_kv(st->page_table, p->layer_off[l], l < c.layers ? c.kv_encoding : c.mtp_kv_encoding,
+                                  c.page_tokens, c.kv_heads, c.head_dim, first, count,
+                                  seed + 0x9e3779b97f4a7c15ULL * (l + 1U), p->stream));
+    cu(cudaStreamSynchronize(p->stream), "synthetic cache fill");
+    st->mtp_length = first + count;
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,262 @@
+"""GPU parity of each kernel launcher against the CPU oracle, through the C ABI.
+Bit-exact where the arithmetic is integer/byte work (NVFP4 codes, Q4H/Q8/F16
+records, top-k, sampler decisions); tolerance where the accumulation order is
+free (GEMV: at most one BF16 step on a small fraction; attention: 2e-3 abs of a
+unit-scale output, the reference's own gates are 2e-4..2e-3)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import binding as ob
+from tests import synth
+from tests.gpu_util import bf16_ulps, dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def L():
+    import torch
+    assert torch.cuda.is_available()
+    from quantum_llm_b200 import lib
+    return lib.load()
+
+
+def _check(L, rc):
+    assert rc >= 0, L.qllm_last_error().decode()
+    return rc
+
+
+def _sync():
+    import torch
+    torch.cuda.synchronize()
+
+
+def test_fake_quant_is_bit_exact(L):
+    import torch
+    rng = np.random.default_rng(0)
+    x = (rng.normal(0, 1, (7, 512)) * rng.choice([1e-3, 1, 30], (7, 1))).astype(np.float32)
+    x[0, :16] = 0
+    want = np.empty_like(x)
+    ob.lib().qo_nvfp4_fake_quant(ob._ptr(x), 7, 512, np.float32(336.0), ob._ptr(want))
+    dx = dev(x); out = torch.empty_like(dx)
+    _check(L, L.qllm_k_nvfp4_fake_quant(dx.data_ptr(), out.data_ptr(), 7, 512, 336.0, None)); _sync()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_weight_quantiser_is_bit_exact(L):
+    import torch
+    rng = np.random.default_rng(1)
+    w = rng.normal(0, 0.02, (96, 256)).astype(np.float32)
+    w[3, 32:48] = 0
+    g = np.float32(448 * 6) / np.abs(w).max()
+    codes, scales = ob.quantize_weights(w, g)
+    dw = dev(w)
+    dc = torch.empty((96, 128), dtype=torch.uint8, device="cuda"); ds = torch.empty((96, 16), dtype=torch.uint8, device="cuda")
+    _check(L, L.qllm_k_nvfp4_quantize_weights(dw.data_ptr(), 96, 256, float(g), dc.data_ptr(), ds.data_ptr(), None)); _sync()
+    assert np.array_equal(dc.cpu().numpy(), codes) and np.array_equal(ds.cpu().numpy(), scales)
+
+
+def _assert_gemv(got, want, impl):
+    """CUDA-core kernel: block terms are exact and summed in double on both sides, so the
+    BF16 results are identical.  Tensor-core kernel: the hardware accumulates in FP32, so a
+    result may land one BF16 step away (or differ by rounding noise next to zero)."""
+    if impl == 0:
+        assert np.array_equal(got, want)
+        return
+    close = (bf16_ulps(got, want) <= 1) | (np.abs(got - want) <= 1e-3 * np.sqrt((want ** 2).mean()))
+    assert close.all()
+    assert (got != want).mean() < 0.01
+
+
+@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("rows,cols,batch", [(256, 256, 5), (1024, 1024, 5), (384, 2048, 1), (4096, 512, 8), (640, 1024, 40)])
+def test_nvfp4_gemv_matches_oracle(L, impl, rows, cols, batch):
+    import torch
+    from quantum_llm_b200 import lib
+    rng = np.random.default_rng(rows + cols + batch)
+    m = synth.SynthMatrix(rng.normal(0, 0.02, (rows, cols)).astype(np.float32))
+    x = rng.normal(0, 1, (batch, cols)).astype(np.float32)
+    want = ob.gemv(m.oracle(), x)
+    dc, ds, dx = dev(m.codes), dev(m.scales), dev(x)
+    y = torch.empty((batch, rows), dtype=torch.float32, device="cuda")
+    ws_bytes = L.qllm_k_nvfp4_gemv_workspace_bytes(batch, rows, cols)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    cm = lib.Matrix(dc.data_ptr(), ds.data_ptr(), float(m.weight_scale), float(m.input_scale), rows, cols)
+    _check(L, L.qllm_k_nvfp4_gemv(C.byref(cm), 0, rows, dx.data_ptr(), y.data_ptr(), batch, ws.data_ptr(), ws_bytes, impl, None)); _sync()
+    got = y.cpu().numpy()
+    _assert_gemv(got, want, impl)
+    # prefix of the rows (the draft head reads the first draft_vocab rows)
+    part = rows // 2
+    _check(L, L.qllm_k_nvfp4_gemv(C.byref(cm), 0, part, dx.data_ptr(), y.data_ptr(), batch, ws.data_ptr(), ws_bytes, impl, None)); _sync()
+    got = y.cpu().numpy().reshape(-1)[:batch * part].reshape(batch, part)
+    _assert_gemv(got, want[:, :part], impl)
+
+
+def test_rms_norm_add_silu(L):
+    import torch
+    rng = np.random.default_rng(2)
+    x = rng.normal(0, 2, (5, 1024)).astype(np.float32); w = rng.normal(1, 0.1, 1024).astype(np.float32)
+    want = np.empty_like(x)
+    ob.lib().qo_rmsnorm(ob._ptr(x), ob._ptr(w), ob._ptr(want), 5, 1024, np.float32(1e-6))
+    dx, dw = dev(x), dev(w); out = torch.empty_like(dx)
+    _check(L, L.qllm_k_rms_norm(dx.data_ptr(), dw.data_ptr(), out.data_ptr(), 5, 1024, 1e-6, None)); _sync()
+    assert np.abs(out.cpu().numpy() - want).max() < 1e-5
+    gu = rng.normal(0, 1.5, (5, 2 * 768)).astype(np.float32)
+    dg = dev(gu); so = torch.empty((5, 768), dtype=torch.float32, device="cuda")
+    _check(L, L.qllm_k_silu_product(dg.data_ptr(), so.data_ptr(), 5, 768, 1, None)); _sync()
+    g, u = gu[:, :768], gu[:, 768:]
+    a = torch.from_numpy(g / (1 + np.exp(-g))).to(torch.bfloat16).float().numpy()
+    ref = torch.from_numpy(a * u).to(torch.bfloat16).float().numpy()
+    assert bf16_ulps(so.cpu().numpy(), ref).max() <= 1
+    a1 = dev(x.copy()); b1 = dev(want)
+    _check(L, L.qllm_k_add(a1.data_ptr(), b1.data_ptr(), x.size, 1, None)); _sync()
+    assert np.array_equal(a1.cpu().numpy(), torch.from_numpy(x + want).to(torch.bfloat16).float().numpy())
+
+
+def _pages(enc, page_tokens, kv, hd, count, layers=2):
+    layer_bytes = ob.lib().qo_kv_layer_bytes(enc, page_tokens, kv, hd)
+    return layer_bytes, [np.zeros(layer_bytes * layers, np.uint8) for _ in range(count)]
+
+
+def _ptr_table(arrays):
+    t = (C.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+    return t
+
+
+@pytest.mark.parametrize("enc", [ob.KV_Q4H, ob.KV_Q8, ob.KV_F16])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_rope_and_kv_store_bytes(L, enc, hd):
+    """RoPE output within rounding of the oracle; K/V record bytes bit-exact when both
+    sides quantise the same rotated rows (empty, all-zero and saturating rows included)."""
+    import torch
+    rng = np.random.default_rng(enc * 10 + hd)
+    qh, kv, pt, rows, first = 4, 2, 64, 5, 61  # rows straddle a page boundary
+    width = (qh + 2 * kv) * hd
+    qkv = (rng.normal(0, 1.4, (rows, width))).astype(np.float32)
+    qkv = torch.from_numpy(qkv).to(torch.bfloat16).float().numpy()
+    qkv[1, qh * hd:(qh + 1) * hd] = 0          # an all-zero key head
+    qkv[2, (qh + kv) * hd] = 3e4               # a dominant value element
+    positions = np.arange(first, first + rows, dtype=np.uint32)
+    # oracle: rotate q and k heads, then store
+    want = qkv.copy()
+    qk = np.ascontiguousarray(want[:, :(qh + kv) * hd])
+    ob.lib().qo_rope(ob._ptr(qk), rows, qh + kv, hd, hd, np.float32(1e6), ob._ptr(positions), 1)
+    want[:, :(qh + kv) * hd] = qk
+    layer_bytes, pages = _pages(enc, pt, kv, hd, 3)
+    table = _ptr_table(pages)
+    off = layer_bytes  # second layer of the page
+    k_rows = np.ascontiguousarray(want[:, qh * hd:(qh + kv) * hd]); v_rows = np.ascontiguousarray(want[:, (qh + kv) * hd:])
+    ob.lib().qo_kv_store(enc, table, off, pt, kv, hd, ob._ptr(k_rows), ob._ptr(v_rows), rows, kv * hd, first)
+    # device
+    dq = dev(qkv)
+    inv = np.power(np.float32(1e6), -2.0 * np.arange(hd // 2, dtype=np.float32) / np.float32(hd)).astype(np.float32)
+    dinv = dev(inv); dpos = dev(np.array([first], np.uint32))
+    dpages = [torch.zeros(layer_bytes * 2, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    dtable = dev(np.array([p.data_ptr() for p in dpages], np.uint64))
+    _check(L, L.qllm_k_rope_kv_store(dq.data_ptr(), rows, qh, kv, hd, hd, dinv.data_ptr(), dpos.data_ptr(), 0, 0,
+                                     dtable.data_ptr(), off, pt, enc, 1, None)); _sync()
+    got = dq.cpu().numpy()
+    assert bf16_ulps(got[:, :(qh + kv) * hd], want[:, :(qh + kv) * hd]).max() <= 1
+    assert (got[:, :(qh + kv) * hd] != want[:, :(qh + kv) * hd]).mean() < 0.01
+    # second pass: store the oracle's rotated rows unchanged (rotary_dim 0) -> bytes must be identical
+    dq2 = dev(want)
+    for p in dpages:
+        p.zero_()
+    _check(L, L.qllm_k_rope_kv_store(dq2.data_ptr(), rows, qh, kv, hd, 0, dinv.data_ptr(), dpos.data_ptr(), 0, 0,
+                                     dtable.data_ptr(), off, pt, enc, 1, None)); _sync()
+    for i in range(3):
+        assert np.array_equal(dpages[i].cpu().numpy(), pages[i]), f"page {i} differs"
+
+
+def _filled_cache(enc, hd, kv, pt, tokens, rng, layers=1):
+    layer_bytes, pages = _pages(enc, pt, kv, hd, (tokens + pt - 1) // pt, layers)
+    table = _ptr_table(pages)
+    k = rng.normal(0, 1.0, (tokens, kv * hd)).astype(np.float32)
+    v = rng.normal(0, 1.0, (tokens, kv * hd)).astype(np.float32)
+    ob.lib().qo_kv_store(enc, table, 0, pt, kv, hd, ob._ptr(k), ob._ptr(v), tokens, kv * hd, 0)
+    return layer_bytes, pages, table
+
+
+@pytest.mark.parametrize("enc,impl,qh,kv,hd", [
+    (ob.KV_Q4H, 0, 10, 2, 128), (ob.KV_Q4H, 1, 10, 2, 128), (ob.KV_Q4H, 1, 8, 8, 128),
+    (ob.KV_Q4H, 0, 12, 2, 256),  # the reference's own smoke geometry: head_dim 256, group 6
+    (ob.KV_Q8, 0, 10, 2, 128), (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128)])
+@pytest.mark.parametrize("ctx,rows", [(8, 5), (300, 5), (1500, 5), (1027, 1), (64, 4)])
+def test_attention_matches_oracle(L, enc, impl, qh, kv, hd, ctx, rows):
+    import torch
+    if hd == 256 and rows * (qh // kv) > 32:
+        rows = 5
+    rng = np.random.default_rng(ctx * 7 + rows + enc)
+    pt, split = 256, 256
+    tokens = ctx + rows - 1
+    layer_bytes, pages, table = _filled_cache(enc, hd, kv, pt, tokens, rng)
+    q = rng.normal(0, 1.0, (rows, qh * hd)).astype(np.float32)
+    want = np.empty((rows, qh * hd), np.float32)
+    ob.lib().qo_attention(enc, table, 0, pt, ob._ptr(q), qh * hd, rows, ctx, qh, kv, hd, split, 1, ob._ptr(want))
+    dq = dev(q); dpages = [dev(p) for p in pages]
+    dtable = dev(np.array([p.data_ptr() for p in dpages], np.uint64))
+    dpos = dev(np.array([ctx - 1], np.uint32))
+    max_splits = (tokens + split - 1) // split + 1
+    ws = torch.empty(L.qllm_k_attention_workspace_bytes(rows, qh, hd, max_splits), dtype=torch.uint8, device="cuda")
+    out = torch.empty((rows, qh * hd), dtype=torch.float32, device="cuda")
+    _check(L, L.qllm_k_attention(enc, dtable.data_ptr(), 0, pt, dq.data_ptr(), qh * hd, rows, dpos.data_ptr(), 0,
+                                 qh, kv, hd, split, max_splits, 1, ws.data_ptr(), out.data_ptr(), impl, None)); _sync()
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    # outputs are BF16-rounded: equal up to one BF16 step (exp() differs in the last place
+    # between the device and the host library); in practice almost all are identical
+    close = (bf16_ulps(got, want) <= 1) | (np.abs(got - want) < 2e-4)
+    assert close.all(), np.abs(got - want).max()
+    assert (got != want).mean() < 0.02
+
+
+def test_argmax_and_topk_are_exact(L):
+    import torch
+    rng = np.random.default_rng(9)
+    rows, count = 5, 151936
+    v = rng.normal(0, 1.5, (rows, count)).astype(np.float32)
+    v = torch.from_numpy(v).to(torch.bfloat16).float().numpy()   # many exact ties
+    v[0, 100] = v[0, 90000] = v[0].max() + 1                       # tie for the maximum -> lower id wins
+    v[1, 5] = np.nan
+    dv = dev(v)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    _check(L, L.qllm_k_argmax(dv.data_ptr(), rows, count, count, out.data_ptr(), None)); _sync()
+    want = [ob.lib().qo_argmax(ob._ptr(np.ascontiguousarray(np.nan_to_num(v[r], nan=-3e38))), count) for r in range(rows)]
+    assert list(out.cpu().numpy().astype(np.uint32)) == want and want[0] == 100
+    for k in (1, 20, 64):
+        ws = torch.empty(L.qllm_k_topk_workspace_bytes(rows, count, k), dtype=torch.uint8, device="cuda")
+        tv = torch.empty((rows, k), dtype=torch.float32, device="cuda"); tt = torch.empty((rows, k), dtype=torch.int32, device="cuda")
+        _check(L, L.qllm_k_topk(dv.data_ptr(), rows, count, count, k, tv.data_ptr(), tt.data_ptr(), ws.data_ptr(), None)); _sync()
+        for r in range(rows):
+            wv = np.empty(k, np.float32); wt = np.empty(k, np.uint32)
+            ob.lib().qo_topk(ob._ptr(np.ascontiguousarray(v[r])), count, k, ob._ptr(wv), ob._ptr(wt))
+            assert np.array_equal(tt[r].cpu().numpy().astype(np.uint32), wt)
+            assert np.array_equal(tv[r].cpu().numpy(), wv)
+
+
+def test_device_sampler_matches_reference_vectors(L, golden_dir):
+    import json, os
+    cases = json.load(open(os.path.join(golden_dir, "sampler_cases.json")))
+    for seed, pos, stream, index, want in cases["counter_uniform"][:16]:
+        out = C.c_double(0)
+        _check(L, L.qllm_k_counter_uniform_host(seed, pos, stream, index, C.byref(out)))
+        assert out.value == want
+    for case in cases["distributions"][:24]:
+        logits = np.array(case["logits"], np.float32); tokens = np.array(case["tokens"], np.uint32)
+        ot = np.empty(64, np.uint32); op = np.empty(64, np.float64)
+        n = _check(L, L.qllm_k_make_distribution_host(logits.ctypes.data, tokens.ctypes.data, len(tokens),
+                                                      case["temperature_ppm"], case["top_p_ppm"], case["min_p_ppm"],
+                                                      ot.ctypes.data, op.ctypes.data))
+        assert list(ot[:n]) == case["out_tokens"]
+        assert np.allclose(op[:n], case["out_probabilities"], rtol=1e-14, atol=0)
+    agree = 0
+    for case in cases["rejections"][:80]:
+        tt = np.array(case["target"][0], np.uint32); tp = np.array(case["target"][1], np.float64)
+        dt = np.array(case["draft"][0], np.uint32); dp = np.array(case["draft"][1], np.float64)
+        token = C.c_uint32(0)
+        r = _check(L, L.qllm_k_rejection_sample_host(case["proposal"], tt.ctypes.data, tp.ctypes.data, len(tt),
+                                                     dt.ctypes.data, dp.ctypes.data, len(dt), case["ua"], case["uc"], C.byref(token)))
+        agree += (r, token.value) == (case["accepted"], case["token"])
+    assert agree == 80

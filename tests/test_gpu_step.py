@@ -1,0 +1,214 @@
+"""Whole-step parity on the tiny configuration (2 layers, hidden 256, 4q/2kv heads,
+head_dim 64, FFN 1024, vocab 4096; prompt of 128 seeded ids, 64 generated tokens):
+the CUDA provider against the CPU oracle through the provider C ABI."""
+import numpy as np
+import pytest
+
+from oracle import binding as ob
+from tests import synth
+from tests.gpu_util import provider_from_synth, request_pair
+from tests.test_oracle_step import echo_model
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_MAX_ABS, LOGIT_REL_RMS = 2e-2, 1e-3   # the stated F16-KV parity tolerance
+
+
+def run_gpu(model, prompt, temperature, generate, graph=False, gemv_impl=0, seed=1234):
+    """Decode `generate` tokens on the CUDA provider.  Returns the token stream (first token
+    onwards), {position: logits row whose inputs are emitted tokens}, and the provider."""
+    prq, _ = request_pair(seed=seed, temperature_ppm=temperature, context_limit=model.cfg["max_context"])
+    p = provider_from_synth(model)
+    p.set_graph_mode(graph)
+    p.set_gemv_impl(gemv_impl)
+    st = p.create_request_state()
+    first = p.prefill(st, prq, prompt, chunk_rows=5)
+    drafts = [int(t) for t in p.read_drafts(st)]
+    stream, rows, pos, tok, steps, accepted = [first], {}, len(prompt), first, 0, 0
+    while len(stream) < generate + 1:
+        r = p.execute_exact_decode(st, prq, tok, pos, prq.reserved_context_tokens)
+        assert r.emitted_tokens[0] == tok and r.positions_advanced == len(r.emitted_tokens)
+        logits = p.read_logits(5)
+        for i in range(r.positions_advanced):
+            rows[pos + i] = logits[i]
+        stream += r.emitted_tokens[1:] + [r.next_token]
+        pos += r.positions_advanced
+        tok = r.next_token
+        steps += 1
+        accepted += r.positions_advanced - 1
+    return dict(stream=stream, rows=rows, drafts=drafts, steps=steps, accepted=accepted, provider=p, state=st)
+
+
+def run_cpu(model, prompt, temperature, generate, seed=1234):
+    _, orq = request_pair(seed=seed, temperature_ppm=temperature, context_limit=model.cfg["max_context"])
+    o = model.oracle_session()
+    first = o.prefill(prompt, 5, orq)
+    drafts = [int(t) for t in o.drafts()]
+    stream, rows, pos, tok, steps, accepted = [first], {}, len(prompt), first, 0, 0
+    while len(stream) < generate + 1:
+        r = o.execute_exact_decode(orq, tok, pos)
+        logits = o.last_logits(5)
+        for i in range(r.positions_advanced):
+            rows[pos + i] = logits[i]
+        stream += list(r.emitted[1:r.emitted_count]) + [r.next_token]
+        pos += r.positions_advanced
+        tok = r.next_token
+        steps += 1
+        accepted += r.positions_advanced - 1
+    return dict(stream=stream, rows=rows, drafts=drafts, steps=steps, accepted=accepted, oracle=o)
+
+
+def row_within_tolerance(a, b):
+    return (np.abs(a - b).max() <= LOGIT_MAX_ABS and
+            np.sqrt(((a - b) ** 2).mean()) / np.sqrt((b ** 2).mean()) <= LOGIT_REL_RMS)
+
+
+def compare(gpu, cpu, prompt_len):
+    """Common prefix of the two token streams, and how many of the logit rows fed by agreed
+    tokens are within the stated tolerance.  W4A4 activation quantisation makes the decoder
+    discontinuous: a last-place difference that crosses an E2M1/E4M3 rounding threshold moves
+    a whole row by ~1e-1, so single rows may fall outside while their neighbours are exact."""
+    n = 0
+    while n < min(len(gpu["stream"]), len(cpu["stream"])) and gpu["stream"][n] == cpu["stream"][n]:
+        n += 1
+    shared = [p for p in sorted(gpu["rows"]) if p in cpu["rows"] and p < prompt_len + n]
+    good = [p for p in shared if row_within_tolerance(gpu["rows"][p], cpu["rows"][p])]
+    exact = [p for p in shared if np.array_equal(gpu["rows"][p], cpu["rows"][p])]
+    tie = None
+    if n < min(len(gpu["stream"]), len(cpu["stream"])):
+        q = prompt_len + n - 1            # the row that chose the first differing token
+        if q in cpu["rows"]:
+            row = cpu["rows"][q]
+            tie = abs(float(row[cpu["stream"][n]]) - float(row[gpu["stream"][n]])) <= 2 * LOGIT_MAX_ABS
+    return dict(prefix=n, shared=len(shared), good=len(good), exact=len(exact), tie=tie)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_tiny_greedy_tokens_and_logits(graph):
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prompt = synth.prompt(4096, 128, 0)
+    gpu = run_gpu(model, prompt, 0, 64, graph=graph)
+    cpu = run_cpu(model, prompt, 0, 64)
+    c = compare(gpu, cpu, len(prompt))
+    print("greedy parity", c, "drafts", gpu["drafts"], cpu["drafts"])
+    assert gpu["stream"][0] == cpu["stream"][0]
+    assert c["shared"] >= 16 and c["good"] >= 0.9 * c["shared"]
+    if c["prefix"] < 65:
+        assert c["tie"] is not False or c["good"] < c["shared"], "streams differ without a tie or a threshold event"
+    t = gpu["provider"].telemetry(gpu["state"])
+    assert t["exact_calls"] == gpu["steps"] and t["kernel_launches"] > 0
+
+
+def test_greedy_stream_equals_plain_target_decoding_on_gpu():
+    # property that needs no oracle: speculative greedy output does not depend on the drafts,
+    # so a provider with a different draft block emits the same tokens
+    prompt = synth.prompt(4096, 64, 3)
+    model = synth.SynthModel(synth.TINY, seed=0)
+    a = run_gpu(model, prompt, 0, 32)
+    rng = np.random.default_rng(5)
+    model.mtp_fusion = synth.SynthMatrix(rng.normal(0, 0.02, (256, 512)).astype(np.float32))
+    b = run_gpu(model, prompt, 0, 32)
+    assert a["stream"][:33] == b["stream"][:33]
+
+
+def test_tiny_kv_pages_match_the_oracle():
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prompt = synth.prompt(4096, 128, 0)
+    gpu = run_gpu(model, prompt, 0, 4)
+    cpu = run_cpu(model, prompt, 0, 4)
+    p, st, o = gpu["provider"], gpu["state"], cpu["oracle"]
+    assert p.page_bytes() >= o.page(0).size
+    for layer in range(3):
+        assert p.layer_offset(layer) == o.layer_offset(layer)
+    cfg = model.cfg
+    pt, kv, hd = cfg["page_tokens"], cfg["kv_heads"], cfg["head_dim"]
+    same, total = 0, 0
+    for page in range(2):   # 128 prompt tokens = two 64-token pages
+        g = p.read_page(st, page)[:o.page(page).size]
+        c = o.page(page)
+        lo, hi = o.layer_offset(0), o.layer_offset(1)
+        # first layer: inputs are identical on both sides -> records are byte-identical
+        assert np.array_equal(g[lo:hi], c[lo:hi]) or (g[lo:hi] != c[lo:hi]).mean() < 1e-3
+        # later layers: identical except rows hit by a quantisation-threshold event upstream
+        for layer in (1, 2):
+            lo, hi = o.layer_offset(layer), (o.layer_offset(layer + 1) if layer < 2 else o.page(page).size)
+            width = (hi - lo) // (2 * pt)
+            gr = g[lo:hi].reshape(2, pt, width)
+            cr = c[lo:hi].reshape(2, pt, width)
+            eq = (gr == cr).all(axis=(0, 2))
+            same += int(eq.sum())
+            total += pt
+    print("identical KV token records in layers 1..2:", same, "of", total)
+    assert same >= 0.5 * total
+
+
+def test_tiny_sampled_decisions():
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prompt = synth.prompt(4096, 128, 0)
+    gpu = run_gpu(model, prompt, 700000, 48, seed=77)
+    cpu = run_cpu(model, prompt, 700000, 48, seed=77)
+    c = compare(gpu, cpu, len(prompt))
+    print("sampled parity", c)
+    # every emitted token must come from the top-k support of the row that chose it
+    for pos, row in gpu["rows"].items():
+        tok = gpu["stream"][pos + 1 - len(prompt)]
+        assert (row > row[tok]).sum() < 20
+    assert c["shared"] >= 1 and c["good"] >= 0.9 * c["shared"]
+
+
+@pytest.mark.parametrize("temperature", [0, 700000])
+def test_echo_model_acceptance_lengths(temperature):
+    model = echo_model()
+    prompt = synth.prompt(4096, 64, 5)
+    gpu = run_gpu(model, prompt, temperature, 48, graph=True)
+    cpu = run_cpu(model, prompt, temperature, 48)
+    c = compare(gpu, cpu, len(prompt))
+    print("echo parity", c, "accepted gpu/cpu", gpu["accepted"], cpu["accepted"], "steps", gpu["steps"], cpu["steps"])
+    assert cpu["accepted"] > 0 and gpu["accepted"] > 0
+    assert gpu["steps"] < 48
+    t = gpu["provider"].telemetry(gpu["state"])
+    assert t["accepted_drafts"] == gpu["accepted"] and sum(t["accepted_depth_calls"]) == gpu["steps"]
+    if c["prefix"] >= 49:
+        assert gpu["accepted"] == cpu["accepted"] or temperature != 0
+
+
+def test_multi_step_enqueue_equals_single_steps():
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prompt = synth.prompt(4096, 64, 4)
+    outs = []
+    for batched in (False, True):
+        prq, _ = request_pair(context_limit=256)
+        p = provider_from_synth(model)
+        st = p.create_request_state()
+        first = p.prefill(st, prq, prompt)
+        toks, pos, tok = [], len(prompt), first
+        if batched:
+            for r in p.execute_exact_decode_steps(st, prq, 256, 6):
+                toks += r.emitted_tokens + [r.next_token]
+        else:
+            for _ in range(6):
+                r = p.execute_exact_decode(st, prq, tok, pos, 256)
+                toks += r.emitted_tokens + [r.next_token]
+                pos += r.positions_advanced
+                tok = r.next_token
+        outs.append(toks)
+    assert outs[0] == outs[1]
+
+
+def test_invalid_invocations_are_rejected():
+    from quantum_llm_b200 import QllmError
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prq, _ = request_pair(context_limit=256)
+    p = provider_from_synth(model)
+    st = p.create_request_state()
+    with pytest.raises(QllmError):                      # no draft yet
+        p.execute_exact_decode(st, prq, 1, 0, 256)
+    first = p.prefill(st, prq, synth.prompt(4096, 16, 0))
+    with pytest.raises(QllmError):                      # wrong guaranteed token
+        p.execute_exact_decode(st, prq, (first + 1) % 4096, 16, 256)
+    with pytest.raises(QllmError):                      # position != draft cache length
+        p.execute_exact_decode(st, prq, first, 17, 256)
+    with pytest.raises(QllmError):                      # context limit beyond max_context
+        p.execute_exact_decode(st, prq, first, 16, 100000)
+    r = p.execute_exact_decode(st, prq, first, 16, 256)
+    assert r.emitted_tokens[0] == first and r.positions_advanced == len(r.emitted_tokens)
