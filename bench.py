@@ -1,0 +1,361 @@
+"""Benchmark of the MTP-4 speculative decode step on B200.
+
+Workload (N=1): 27B-class dense target, NVFP4 weights, one stream, 32768 cached
+tokens, Q4H target cache + Q8 draft cache, 4 drafts per step.  One "step" is one
+execute_exact_decode: verify 5 rows, accept/rollback on the device, 4 draft passes.
+`value` is decode tok/s with everything resident in HBM (steps enqueued back to back,
+one read at the end); `e2e` is the same through the provider's per-step call with the
+invocation cursor uploaded and the result record read back every step.
+N>1 runs N independent replicas (one stream per GPU, data parallel, no collective).
+
+  python bench.py --gpus N --steps K --warmup W [--impl reference]
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONTEXT = 32768          # cached tokens when the timed region starts
+REAL_PREFILL = 40        # last prompt tokens run through the real prefill path
+METRIC = "decode_tok_per_s_mtp4_q4h_32k"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "0")))
+    ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline_sample(threads=None):
+    """Times the CPU oracle (a port of the reference's arithmetic) on a bounded sample of the
+    workload: the four NVFP4 GEMVs of ONE 27B-geometry layer at 5 rows plus the Q4H attention
+    of one layer over 2048 cached tokens, then scales by algorithmic bytes to a full step."""
+    import numpy as np
+    from oracle import binding as ob
+    threads = threads or os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    O = ob.lib()
+    rng = np.random.default_rng(0)
+    H, F, QH, KV, HD = 5120, 17408, 40, 8, 128
+    shapes = [((QH + 2 * KV) * HD, H), (H, QH * HD), (2 * F, H), (H, F)]
+    mats, sample_bytes = [], 0
+    for rows, cols in shapes:
+        codes = rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8)
+        scales = rng.integers(0x20, 0x48, (rows, cols // 16), dtype=np.uint8)
+        mats.append((ob.matrix(codes, scales, 1e-3, 336.0), codes, scales, rng.normal(0, 1, (5, cols)).astype(np.float32)))
+        sample_bytes += codes.size + scales.size
+    ctx, pt = 2048, 256
+    layer_bytes = O.qo_kv_layer_bytes(ob.KV_Q4H, pt, KV, HD)
+    pages = [rng.integers(0, 256, layer_bytes, dtype=np.uint8) for _ in range((ctx + 4 + pt - 1) // pt)]
+    table = (C.c_void_p * len(pages))(*[p.ctypes.data for p in pages])
+    k = rng.normal(0, 1, (ctx + 4, KV * HD)).astype(np.float32)
+    O.qo_kv_store(ob.KV_Q4H, table, 0, pt, KV, HD, ob._ptr(k), ob._ptr(k), ctx + 4, KV * HD, 0)
+    q = rng.normal(0, 1, (5, QH * HD)).astype(np.float32)
+    out = np.empty_like(q)
+    sample_bytes += (ctx + 4) * KV * (HD // 2 + 2) * 2
+    t0 = time.perf_counter()
+    for m, _, _, x in mats:
+        ob.gemv(m, x)
+    O.qo_attention(ob.KV_Q4H, table, 0, pt, ob._ptr(q), QH * HD, 5, ctx, QH, KV, HD, 512, 1, ob._ptr(out))
+    dt = time.perf_counter() - t0
+    return dt, sample_bytes, threads
+
+
+def timed_cpu_baseline(min_seconds=8.0):
+    reps, total, info = 0, 0.0, None
+    while total < min_seconds and reps < 12:
+        dt, sample_bytes, threads = cpu_baseline_sample()
+        total += dt
+        reps += 1
+        info = (sample_bytes, threads)
+    return total / reps, info[0], info[1], reps
+
+
+def reference_arm(args):
+    """Reference arm: the reference's host-side arithmetic for this path, timed on the
+    host cores.  The reference's provider itself needs a CUDA device and a compiled model
+    artifact, so its CPU implementation of the path is the oracle port (kind "port")."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from quantum_llm_b200.synthetic import DENSE_27B
+    cfg = DENSE_27B
+    # algorithmic bytes of a full step without touching a GPU
+    per_layer = sum(r * c * 9 // 16 for r, c in [((cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"], cfg["hidden"]),
+                                                  (cfg["hidden"], cfg["q_heads"] * cfg["head_dim"]),
+                                                  (2 * cfg["ffn"], cfg["hidden"]), (cfg["hidden"], cfg["ffn"])])
+    head = cfg["vocab"] * cfg["hidden"] * 9 // 16
+    kv = 2 * (cfg["head_dim"] // 2 + 2) * cfg["kv_heads"] * cfg["layers"] * args.context
+    draft = per_layer + 2 * cfg["hidden"] * cfg["hidden"] * 9 // 16 + cfg["draft_vocab"] * cfg["hidden"] * 9 // 16 \
+        + 2 * (cfg["head_dim"] + 2) * cfg["kv_heads"] * args.context
+    step_bytes = per_layer * cfg["layers"] + head + kv + 4 * draft
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, sample_bytes, threads = cpu_baseline_sample()
+        if i >= args.warmup:
+            times.append(dt)
+    dt = sum(times) / len(times)
+    step_s = dt * step_bytes / sample_bytes
+    value = 1.0 / step_s   # accepted length 1.0 on random-init weights: one token per step
+    sample = ("one 27B-geometry layer (4 NVFP4 GEMVs, 5 rows) + Q4H attention over 2048 tokens, "
+              "scaled by algorithmic bytes to a full step")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
+            "config": {"workload": "27B dense, 1 stream, 32768 ctx, Q4H KV, MTP-4 (CPU port of the reference arithmetic)"},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def gemv_kernel_leg(model, provider, gemv_impl, rows=5, repeats=3):
+    """Average duration of the dominant kernel (gate/up NVFP4 GEMV, 34816x5120, 5 rows) over
+    all layers' weights back to back (6.4 GB, far beyond L2), timed with CUDA events on the
+    launching stream."""
+    import torch
+    from quantum_llm_b200 import lib as ql
+    L = ql.load()
+    dev = model.device
+    mats = [b.m["gate_up"] for b in model.layers]
+    rows_w, cols = mats[0].rows, mats[0].cols
+    x = torch.randn((rows, cols), device=dev, dtype=torch.float32)
+    y = torch.empty((rows, rows_w), device=dev, dtype=torch.float32)
+    ws_bytes = L.qllm_k_nvfp4_gemv_workspace_bytes(rows, rows_w, cols)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    cms = [m.c() for m in mats]
+    best = None
+    with torch.cuda.stream(stream):
+        for rep in range(repeats + 1):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for cm in cms:
+                ql.check(L.qllm_k_nvfp4_gemv(C.byref(cm), 0, rows_w, x.data_ptr(), y.data_ptr(), rows, ws.data_ptr(),
+                                            ws_bytes, gemv_impl, C.c_void_p(stream.cuda_stream)))
+            stop.record(stream)
+            stop.synchronize()
+            ms = start.elapsed_time(stop) / len(cms)
+            if rep > 0:
+                best = ms if best is None else min(best, ms)
+    algorithmic = mats[0].nbytes() + rows * cols * 4 + rows * rows_w * 4
+    return best, algorithmic
+
+
+def ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    from quantum_llm_b200 import build as qbuild
+    if local == 0:
+        qbuild.build()
+    if world > 1:
+        dist.barrier()
+    from quantum_llm_b200.provider import RequestParameters
+    from quantum_llm_b200.synthetic import DENSE_27B, DeviceModel
+
+    cfg = dict(DENSE_27B)
+    if args.small:
+        cfg["layers"] = 4
+    context = args.context
+    cfg["max_context"] = context + 1024
+    steps_total = args.warmup + 2 * args.steps + 8
+    assert context + 5 * steps_total + 16 < cfg["max_context"], "too many steps for the context reserve"
+    model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
+    provider = model.provider()
+    provider.set_gemv_impl(args.gemv_impl)
+    state = provider.create_request_state()
+    request = RequestParameters(sampling_seed=1 + rank, sampling_temperature_ppm=0,
+                                reserved_context_tokens=cfg["max_context"])
+    # prompt: seeded uniform ids; the first context-REAL_PREFILL positions are represented by
+    # seeded synthetic cache records, the tail goes through the real prefill + draft priming
+    prompt = np.random.default_rng(1 + rank).integers(0, cfg["vocab"], context, dtype=np.uint32)
+    synthetic = context - REAL_PREFILL
+    provider.fill_synthetic_kv(state, 0, synthetic, seed=1234 + rank)
+    first = provider.prefill(state, request, prompt[synthetic:], first_position=synthetic, chunk_rows=5)
+    provider.set_graph_mode(True)
+
+    stream = torch.cuda.ExternalStream(provider.stream(), device=f"cuda:{local}")
+    position, token = context, first
+    launches0 = provider.telemetry(state)["kernel_launches"]
+    provider.set_graph_mode(False)
+    r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
+    launches_per_step = provider.telemetry(state)["kernel_launches"] - launches0
+    position += r.positions_advanced
+    token = r.next_token
+    provider.set_graph_mode(True)
+    for _ in range(max(args.warmup, 3)):
+        r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
+        position += r.positions_advanced
+        token = r.next_token
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: steps enqueued back to back, device-resident, one read per batch of 32
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tokens_a, accepted_a = 0, 0
+    with ClockSampler(local) as clocks:
+        start.record(stream)
+        done = 0
+        while done < args.steps:
+            n = min(32, args.steps - done)
+            for r in provider.execute_exact_decode_steps(state, request, cfg["max_context"], n):
+                tokens_a += r.positions_advanced
+                accepted_a += r.positions_advanced - 1
+                position += r.positions_advanced
+                token = r.next_token
+            done += n
+        stop.record(stream)
+        stop.synchronize()
+        barrier()
+    ms_value = start.elapsed_time(stop)
+    # ---- e2e: one provider call per step, cursor uploaded and result read back every step
+    barrier()
+    tokens_b = 0
+    start.record(stream)
+    for _ in range(args.steps):
+        r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
+        tokens_b += r.positions_advanced
+        position += r.positions_advanced
+        token = r.next_token
+    stop.record(stream)
+    stop.synchronize()
+    barrier()
+    ms_e2e = start.elapsed_time(stop)
+
+    stats = torch.tensor([ms_value, ms_e2e], dtype=torch.float64, device=f"cuda:{local}")
+    totals = torch.tensor([tokens_a, tokens_b, accepted_a], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    ms_value, ms_e2e = (float(x) for x in stats.cpu())
+    tokens_a, tokens_b, accepted_a = (float(x) for x in totals.cpu())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if peaks else "fallback"
+    kernel_ms, kernel_bytes = gemv_kernel_leg(model, provider, args.gemv_impl)
+    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+    step_bytes, verify_bytes = model.step_bytes(context)
+    ms_per_step = ms_value / args.steps
+    step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+    value = tokens_a / (ms_value * 1e-3)
+    e2e = tokens_b / (ms_e2e * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
+        "config": {"workload": "27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936), 1 stream/GPU, "
+                               f"{context} cached tokens, Q4H target KV + Q8 draft KV, MTP-4, greedy",
+                   "layers": cfg["layers"], "parallelism": f"dp{world} replicas",
+                   "l2_policy": "inputs larger than L2 (16 GB streamed per step)",
+                   "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",
+                   "gemv_impl": "tcgen05" if args.gemv_impl == 1 else "dp4a"},
+        "accepted_len_per_step": tokens_a / (args.steps * world),
+        "tok_s_if_all_drafts_accepted": 5.0 * args.steps * world / (ms_value * 1e-3),
+        "step_algorithmic_gb": step_bytes / 1e9, "step_gbs": step_gbs, "step_frac_of_hbm": step_gbs / hbm_peak,
+        "roofline": {"bound": "hbm", "kernel": "nvfp4_gemv gate_up 34816x5120 M=5", "achieved": achieved,
+                     "peak": hbm_peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": None, "kernel_ms": kernel_ms},
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 56,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "clocks": clocks.summary(),
+    }
+    if not args.no_cpu_baseline and world >= 1:
+        dt, sample_bytes, threads, reps = timed_cpu_baseline()
+        cpu_step = dt * step_bytes / sample_bytes
+        line["cpu_baseline"] = {"value": 1.0 / cpu_step, "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": f"one layer's 4 NVFP4 GEMVs at 5 rows + Q4H attention over 2048 tokens "
+                                          f"({reps} repetitions, {dt:.2f} s each), scaled by algorithmic bytes to a step"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        reference_arm(a)
+    else:
+        ours(a)

@@ -164,6 +164,8 @@ int qllm_provider_execute_exact_decode_steps(qllm_provider* provider, qllm_reque
  * out[7]=kernel launches enqueued since creation. */
 int qllm_provider_telemetry(qllm_provider* provider, qllm_request_state* state, uint64_t* out,
                             uint32_t count);
+/* The cudaStream_t every call of this provider launches on (for event timing). */
+void* qllm_provider_stream(qllm_provider* provider);
 /* 0 = launch kernels one by one, 1 = replay the captured CUDA graph of the step. */
 int qllm_provider_set_graph_mode(qllm_provider* provider, int enabled);
 /* GEMV implementation: 0 = CUDA-core kernel, 1 = tcgen05 block-scaled MMA kernel. */

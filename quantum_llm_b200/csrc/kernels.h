@@ -105,12 +105,19 @@ struct StepState {
   unsigned long long exact_calls, accepted_drafts, accepted_depth_calls[5];
   DraftDistribution drafts[4];
 };
+// One ring entry per step: the result the caller reads plus the state summary the host
+// mirror needs, so that one small device-to-host copy ends a step.
+struct StepRecord {
+  qllm_exact_result result;
+  uint32_t draft_count;  // proposals ready for the next step
+  uint32_t error;        // StepState::error after the step
+};
 struct AcceptArgs {
   StepState* state;
   const uint32_t* argmax_tokens;  // [rows] (greedy)
   const float* top_values;        // [rows, top_k] (sampling)
   const uint32_t* top_tokens;
-  qllm_exact_result* results;     // device ring [results_capacity]
+  StepRecord* results;            // device ring [results_capacity]
   uint32_t results_capacity;
 };
 int launch_accept(const AcceptArgs& a, cudaStream_t stream);
@@ -121,6 +128,8 @@ struct DraftSampleArgs {
   const uint32_t* top_tokens;
   uint32_t pass;                  // 0 = first draft pass of a step, 1.. = chained passes
   uint32_t from_sync;             // 1: called from a synchronisation batch (position is final)
+  StepRecord* results;            // ring of the acceptance kernel (may be null)
+  uint32_t results_capacity;
 };
 int launch_draft_sample(const DraftSampleArgs& a, cudaStream_t stream);
 int launch_first_token(StepState* state, const uint32_t* argmax_token, const float* top_values,

@@ -152,13 +152,17 @@ __global__ void accept_kernel(AcceptArgs a) {
   StepState* s = a.state;
   const uint32_t proposals = s->draft_count;
   const uint32_t position = s->position;
-  qllm_exact_result* result = a.results + (s->step_index % a.results_capacity);
+  StepRecord* record = a.results + (s->step_index % a.results_capacity);
+  qllm_exact_result* result = &record->result;
+  record->draft_count = 0U;
+  record->error = s->error;
   s->step_index += 1U;
   result->emitted_count = 0U;
   result->positions_advanced = 0U;
   if (s->error != 0U || proposals == 0U || proposals > 4U ||
       position + proposals >= s->context_limit) {
     if (s->error == 0U) s->error = 1U;  // invalid multi-draft state
+    record->error = s->error;
     return;
   }
   DeviceDist target;
@@ -249,6 +253,11 @@ __global__ void draft_sample_kernel(DraftSampleArgs a, uint32_t commit) {
   if (commit) {
     s->verify_tokens[0] = s->next_token;
     s->position = s->new_position;
+    if (a.results != nullptr && !a.from_sync) {
+      StepRecord* record = a.results + ((s->step_index - 1U) % a.results_capacity);
+      record->draft_count = s->draft_count;
+      record->error = s->error;
+    }
   }
 }
 

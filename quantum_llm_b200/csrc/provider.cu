@@ -83,7 +83,8 @@ struct qllm_request_state {
   uint8_t** page_table = nullptr;   // device array of page pointers
   uint32_t pages = 0;
   StepState* state = nullptr;       // device
-  qllm_exact_result* results = nullptr;  // device ring
+  StepRecord* results = nullptr;    // device ring
+  StepRecord* host_records = nullptr;  // pinned landing area of the ring
   float* retained_hidden = nullptr; // [kMaxRows, hidden] rows of the last prefill chunk
   float* mtp_last_hidden = nullptr; // [hidden]
   // host mirror of the invocation stream invariants
@@ -356,13 +357,15 @@ struct qllm_provider {
   }
 
   // Draft passes after the first: chained on the draft block's own last hidden.
-  void rollout(qllm_request_state& st, uint32_t splits, bool sampled, uint32_t top_k) {
+  void rollout(qllm_request_state& st, uint32_t splits, bool sampled, uint32_t top_k,
+               bool from_sync = false) {
     const auto& c = cfg;
     for (uint32_t i = 1; i < c.draft_depth; ++i) {
       run_mtp(st, &st.state->verify_tokens[i], st.mtp_last_hidden, 1, &st.state->new_position,
               i - 1U, splits, true, nullptr, sampled, top_k);
       DraftSampleArgs ds{st.state, argmax_out.p, top_values.p, top_tokens.p,
-                         i | (i + 1U == c.draft_depth ? 0x80000000U : 0U), 0U};
+                         i | (i + 1U == c.draft_depth ? 0x80000000U : 0U), from_sync ? 1U : 0U,
+                         st.results, kResultRing};
       ok(launch_draft_sample(ds, stream));
     }
   }
@@ -382,7 +385,7 @@ struct qllm_provider {
     run_mtp(st, s->mtp_tokens, hidden_rows_for_mtp(), R, &s->position, 0U, mtp_splits, true,
             &s->accepted, sampled, top_k);
     DraftSampleArgs ds{s, argmax_out.p, top_values.p, top_tokens.p,
-                       0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 0U};
+                       0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 0U, st.results, kResultRing};
     ok(launch_draft_sample(ds, stream));
     rollout(st, mtp_splits, sampled, top_k);
   }
@@ -486,7 +489,9 @@ int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** ou
     cu(cudaMemcpyAsync(st->page_table, table.data(), st->pages * sizeof(uint8_t*), cudaMemcpyHostToDevice, p->stream), "page table");
     cu(cudaMalloc(&st->state, sizeof(StepState)), "step state");
     cu(cudaMemsetAsync(st->state, 0, sizeof(StepState), p->stream), "step state");
-    cu(cudaMalloc(&st->results, qllm_provider::kResultRing * sizeof(qllm_exact_result)), "result ring");
+    cu(cudaMalloc(&st->results, qllm_provider::kResultRing * sizeof(StepRecord)), "result ring");
+    cu(cudaMemsetAsync(st->results, 0, qllm_provider::kResultRing * sizeof(StepRecord), p->stream), "result ring");
+    cu(cudaMallocHost(&st->host_records, qllm_provider::kResultRing * sizeof(StepRecord)), "pinned result ring");
     cu(cudaMalloc(&st->retained_hidden, static_cast<size_t>(qllm_provider::kMaxRows) * c.hidden * sizeof(float)), "retained hidden");
     cu(cudaMalloc(&st->mtp_last_hidden, c.hidden * sizeof(float)), "draft hidden");
     cu(cudaStreamSynchronize(p->stream), "request state set-up");
@@ -507,6 +512,7 @@ void qllm_provider_destroy_request_state(qllm_provider* p, qllm_request_state* s
   cudaFree(st->page_table);
   cudaFree(st->state);
   cudaFree(st->results);
+  if (st->host_records) cudaFreeHost(st->host_records);
   cudaFree(st->retained_hidden);
   cudaFree(st->mtp_last_hidden);
   delete st;
@@ -588,9 +594,10 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
                &s->accepted, sampled, rq->sampling_top_k);
     if (produce) {
       DraftSampleArgs ds{s, p->argmax_out.p, p->top_values.p, p->top_tokens.p,
-                         0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 1U};
+                         0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 1U, st->results,
+                         qllm_provider::kResultRing};
       ok(launch_draft_sample(ds, p->stream));
-      p->rollout(*st, splits, sampled, rq->sampling_top_k);
+      p->rollout(*st, splits, sampled, rq->sampling_top_k, true);
       uint32_t drafts = 0;
       cu(cudaMemcpyAsync(&drafts, &s->draft_count, sizeof(drafts), cudaMemcpyDeviceToHost, p->stream), "read draft count");
       check_device_error(*p, *st);
@@ -616,7 +623,10 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
   if (reach >= context_limit)
     throw Error(QLLM_INVALID_ARGUMENT, "multi-draft MTP state is invalid: too close to the context limit");
   const bool sampled = rq->sampling_temperature_ppm != 0U;
-  const uint32_t splits = p->splits_for(st->mtp_length + steps * R + R);
+  // the split count is part of the captured graph: size it for a fixed horizon so that
+  // single-step and batched calls share one graph until the context crosses a split
+  const uint32_t horizon = std::max(steps, 32U);
+  const uint32_t splits = p->splits_for(st->mtp_length + horizon * R + R);
   const uint32_t mtp_splits = splits;
   StepState* s = st->state;
   const uint32_t ring_start = st->ring_cursor;
@@ -645,14 +655,23 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
   } else {
     for (uint32_t i = 0; i < steps; ++i) p->enqueue_step(*st, splits, mtp_splits, sampled, rq->sampling_top_k);
   }
-  std::vector<qllm_exact_result> ring(qllm_provider::kResultRing);
-  cu(cudaMemcpyAsync(ring.data(), st->results, ring.size() * sizeof(qllm_exact_result), cudaMemcpyDeviceToHost, p->stream), "read step results");
-  uint32_t drafts = 0;
-  cu(cudaMemcpyAsync(&drafts, &s->draft_count, sizeof(drafts), cudaMemcpyDeviceToHost, p->stream), "read draft count");
-  check_device_error(*p, *st);
+  // one copy when the records are contiguous in the ring, two when they wrap
+  const uint32_t cap = qllm_provider::kResultRing;
+  const uint32_t begin = ring_start % cap;
+  const uint32_t head_count = std::min(steps, cap - begin);
+  cu(cudaMemcpyAsync(st->host_records + begin, st->results + begin, head_count * sizeof(StepRecord),
+                     cudaMemcpyDeviceToHost, p->stream), "read step results");
+  if (head_count < steps)
+    cu(cudaMemcpyAsync(st->host_records, st->results, (steps - head_count) * sizeof(StepRecord),
+                       cudaMemcpyDeviceToHost, p->stream), "read step results");
+  cu(cudaStreamSynchronize(p->stream), "step");
+  const StepRecord& last = st->host_records[(ring_start + steps - 1U) % cap];
+  if (last.error)
+    throw Error(QLLM_INTERNAL, "exact MTP step failed on the device (code " + std::to_string(last.error) + ")");
+  const uint32_t drafts = last.draft_count;
   st->ring_cursor += steps;
   for (uint32_t i = 0; i < steps; ++i) {
-    results[i] = ring[(ring_start + i) % qllm_provider::kResultRing];
+    results[i] = st->host_records[(ring_start + i) % cap].result;
     st->mtp_length += results[i].positions_advanced;
     st->synchronized_token = results[i].next_token;
   }
@@ -673,6 +692,14 @@ int qllm_provider_execute_exact_decode(qllm_provider* p, qllm_request_state* st,
         context_limit != rq->reserved_context_tokens)
       throw Error(QLLM_INVALID_ARGUMENT, "exact MTP invocation stream is invalid");
     p->bind_request(*st, *rq);
+    // the invocation's position, proposal count and guaranteed token travel to the device
+    // cursor with the call (they equal what the previous step left there)
+    const uint32_t cursor[3] = {position, st->draft_count, guaranteed_token};
+    static_assert(offsetof(StepState, draft_count) == offsetof(StepState, position) + 4U &&
+                      offsetof(StepState, verify_tokens) == offsetof(StepState, position) + 8U,
+                  "cursor fields must be adjacent");
+    cu(cudaMemcpyAsync(&st->state->position, cursor, sizeof(cursor), cudaMemcpyHostToDevice, p->stream),
+       "upload invocation cursor");
     run_steps(p, st, rq, context_limit, 1U, result);
   });
 }
@@ -705,6 +732,8 @@ int qllm_provider_telemetry(qllm_provider* p, qllm_request_state* st, uint64_t* 
     out[7] = launches_counted();
   });
 }
+
+void* qllm_provider_stream(qllm_provider* p) { return p ? static_cast<void*>(p->stream) : nullptr; }
 
 int qllm_provider_set_graph_mode(qllm_provider* p, int enabled) {
   if (!p) return fail(QLLM_INVALID_ARGUMENT, "null provider");

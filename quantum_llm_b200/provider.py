@@ -151,6 +151,10 @@ class Nvfp4MtpProvider:
         return first_token
 
     # -- settings / inspection ---------------------------------------------------
+    def stream(self):
+        """The provider's cudaStream_t as an integer handle."""
+        return int(self.L.qllm_provider_stream(self.h) or 0)
+
     def set_graph_mode(self, enabled):
         _l.check(self.L.qllm_provider_set_graph_mode(self.h, int(enabled)))
 

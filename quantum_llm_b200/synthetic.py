@@ -1,0 +1,140 @@
+"""Seeded random-init models built directly in device memory, for benchmarks and
+large-shape property tests.  Weights are N(0, 0.02) quantised to NVFP4 by the
+library's own device quantiser (per-tensor scale 448*6/absmax); the draft block is
+the last target block plus N(0, 0.004).  torch is used for device memory and the
+random generator only.
+"""
+import ctypes as C
+
+import torch
+
+from . import lib as _l
+from .provider import Nvfp4MtpProvider
+
+INPUT_SCALE = 448.0 * 6.0 / 8.0
+
+# 27B-class dense target of the headline benchmark (64 layers, hidden 5120, 40q/8kv,
+# head_dim 128, FFN 17408, vocab 151936), Q4H target cache, Q8 draft cache.
+DENSE_27B = dict(layers=64, hidden=5120, q_heads=40, kv_heads=8, head_dim=128, ffn=17408, vocab=151936,
+                 draft_vocab=65536, rotary_dim=128, rope_theta=1e6, eps=1e-6, page_tokens=256,
+                 kv_encoding=_l.KV_Q4H, mtp_kv_encoding=_l.KV_Q8, activation_bf16=1, draft_depth=4,
+                 max_context=33792, split_tokens=512)
+
+
+class DeviceMatrix:
+    def __init__(self, codes, scales, weight_scale, rows, cols):
+        self.codes, self.scales, self.weight_scale, self.rows, self.cols = codes, scales, weight_scale, rows, cols
+
+    def c(self):
+        return _l.Matrix(self.codes.data_ptr(), self.scales.data_ptr(), self.weight_scale, INPUT_SCALE,
+                         self.rows, self.cols)
+
+    def nbytes(self):
+        return self.codes.numel() + self.scales.numel()
+
+
+def _random_rows(rows, cols, seed, device, std=0.02, base_seed=None, noise=0.0):
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed if base_seed is None else base_seed)
+    w = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * std
+    if base_seed is not None:
+        gen.manual_seed(seed)
+        w += torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * noise
+    return w
+
+
+def quantize(w):
+    """fp32 device tensor [rows, cols] -> DeviceMatrix (library quantiser)."""
+    L = _l.load()
+    rows, cols = w.shape
+    divisor = float(448.0 * 6.0 / w.abs().max().item())
+    codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device=w.device)
+    stream = torch.cuda.current_stream(w.device).cuda_stream
+    _l.check(L.qllm_k_nvfp4_quantize_weights(w.data_ptr(), rows, cols, divisor, codes.data_ptr(), scales.data_ptr(),
+                                              C.c_void_p(stream)))
+    torch.cuda.current_stream(w.device).synchronize()
+    weight_scale = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(divisor, dtype=torch.float32))
+    return DeviceMatrix(codes, scales, weight_scale, rows, cols)
+
+
+class DeviceBlock:
+    SHAPES = ("qkv", "o", "gate_up", "down")
+
+    def __init__(self, cfg, seed, device, base_seed=None):
+        H, F = cfg["hidden"], cfg["ffn"]
+        qkv_rows = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"]
+        shapes = dict(qkv=(qkv_rows, H), o=(H, cfg["q_heads"] * cfg["head_dim"]), gate_up=(2 * F, H), down=(H, F))
+        self.m = {}
+        for i, name in enumerate(self.SHAPES):
+            rows, cols = shapes[name]
+            w = _random_rows(rows, cols, seed * 16 + i, device,
+                             base_seed=None if base_seed is None else base_seed * 16 + i, noise=0.004)
+            self.m[name] = quantize(w)
+            del w
+        self.input_norm = torch.ones(H, dtype=torch.float32, device=device)
+        self.post_norm = torch.ones(H, dtype=torch.float32, device=device)
+
+    def c(self):
+        return _l.Block(self.input_norm.data_ptr(), self.m["qkv"].c(), self.m["o"].c(), self.post_norm.data_ptr(),
+                        self.m["gate_up"].c(), self.m["down"].c())
+
+    def nbytes(self):
+        return sum(x.nbytes() for x in self.m.values())
+
+
+class DeviceModel:
+    def __init__(self, cfg, seed=0, device="cuda:0"):
+        self.cfg = dict(cfg)
+        self.device = torch.device(device)
+        H, V = cfg["hidden"], cfg["vocab"]
+        with torch.cuda.device(self.device):
+            gen = torch.Generator(device=self.device)
+            gen.manual_seed(seed * 1000 + 1)
+            self.embedding = (torch.randn((V, H), generator=gen, device=self.device, dtype=torch.float32) * 0.02
+                              ).to(torch.bfloat16)
+            self.layers = [DeviceBlock(cfg, seed * 1000 + 10 + l, self.device) for l in range(cfg["layers"])]
+            self.final_norm = torch.ones(H, dtype=torch.float32, device=self.device)
+            self.head = quantize(_random_rows(V, H, seed * 1000 + 2, self.device))
+            self.mtp_norms = [torch.ones(H, dtype=torch.float32, device=self.device) for _ in range(3)]
+            self.mtp_fusion = quantize(_random_rows(H, 2 * H, seed * 1000 + 3, self.device))
+            self.mtp_block = DeviceBlock(cfg, seed * 1000 + 4, self.device,
+                                         base_seed=seed * 1000 + 10 + cfg["layers"] - 1)
+            torch.cuda.empty_cache()
+
+    def config(self):
+        c = _l.Config()
+        for k, v in self.cfg.items():
+            setattr(c, k, v)
+        return c
+
+    def provider(self):
+        blocks = (_l.Block * len(self.layers))(*[b.c() for b in self.layers])
+        w = _l.Weights(self.embedding.data_ptr(), blocks, self.final_norm.data_ptr(), self.head.c(),
+                       self.mtp_norms[0].data_ptr(), self.mtp_norms[1].data_ptr(), self.mtp_fusion.c(),
+                       self.mtp_block.c(), self.mtp_norms[2].data_ptr())
+        return Nvfp4MtpProvider(self.config(), w, weights_on_device=True, device=self.device.index or 0,
+                                keepalive=(self, blocks))
+
+    # ---- algorithmic bytes (weights streamed once per pass; scales included)
+    def verify_weight_bytes(self):
+        return sum(b.nbytes() for b in self.layers) + self.head.nbytes()
+
+    def draft_pass_weight_bytes(self):
+        V, H = self.cfg["draft_vocab"], self.cfg["hidden"]
+        return self.mtp_block.nbytes() + self.mtp_fusion.nbytes() + V * H // 2 + V * H // 16
+
+    def kv_bytes_per_token(self):
+        L = _l.load()
+        c = self.cfg
+        target = L.qllm_k_kv_layer_bytes(c["kv_encoding"], c["page_tokens"], c["kv_heads"], c["head_dim"])
+        draft = L.qllm_k_kv_layer_bytes(c["mtp_kv_encoding"], c["page_tokens"], c["kv_heads"], c["head_dim"])
+        return target * c["layers"] // c["page_tokens"], draft // c["page_tokens"]
+
+    def step_bytes(self, context):
+        """Algorithmic bytes of one MTP-4 step at `context` cached tokens: one verify pass
+        (all layer weights + head + target cache) and draft_depth draft passes."""
+        target_kv, draft_kv = self.kv_bytes_per_token()
+        verify = self.verify_weight_bytes() + target_kv * context
+        draft = self.draft_pass_weight_bytes() + draft_kv * context
+        return verify + self.cfg["draft_depth"] * draft, verify
