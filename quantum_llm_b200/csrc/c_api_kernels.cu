@@ -1,4 +1,6 @@
 // extern "C" forms of the kernel launchers declared in include/qllm_b200.h.
+#include <string>
+
 #include "common.cuh"
 #include "gemv_mma.h"
 #include "kernels.h"
@@ -53,9 +55,18 @@ int qllm_k_nvfp4_gemv(const qllm_matrix* m, uint32_t first_row, uint32_t row_cou
     MmaWeights w;
     int rc = w.prepare(*m, s);
     if (rc) return rc;
+    if (!w.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+    rc = check_cuda(cudaMemsetAsync(workspace, 0, sizeof(uint32_t), s), "clear GEMV status word");
+    if (rc) return rc;
     rc = launch_gemv_mma(w, *m, first_row, row_count, x, y, batch, workspace, workspace_bytes, s);
     if (rc) return rc;
-    return check_cuda(cudaStreamSynchronize(s), "native NVFP4 tensor-core GEMV");
+    uint32_t status = 0;
+    rc = check_cuda(cudaMemcpyAsync(&status, workspace, sizeof(status), cudaMemcpyDeviceToHost, s), "read GEMV status");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamSynchronize(s), "native NVFP4 tensor-core GEMV");
+    if (rc) return rc;
+    if (status) return fail(QLLM_INTERNAL, "tensor-core GEMV pipeline wait ran out (status " + std::to_string(status) + ")");
+    return 0;
   }
   return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
 }

@@ -71,7 +71,10 @@ struct AttentionArgs {
   void* workspace;
   float* out;                 // [rows, q_heads*head_dim]
   int impl;                   // 0 scalar, 1 tensor-core (Q4H)
+  uint32_t* error;            // optional device status word (set when a pipeline wait runs out)
 };
+int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
+                                   uint32_t* error, cudaStream_t stream);
 size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                                  uint32_t max_splits);
 int launch_attention(const AttentionArgs& a, cudaStream_t stream);

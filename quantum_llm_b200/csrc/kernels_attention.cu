@@ -6,8 +6,6 @@
 //   Q4H: [K codes kv*pt*hd/2][K scales f16 kv*pt][V codes][V scales], record = kv_head*pt + pos%pt
 //   Q8 : [K records pt*kv*(hd+2)][V records], record = (pos%pt)*kv + kv_head, int8[hd] + f16 scale
 //   F16: [K pt*kv*hd f16][V ...], token-major
-#include <mma.h>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -355,205 +353,6 @@ attention_scalar_kernel(AttentionArgs a, Partials part) {
     }
 }
 
-// --------------------------------------- Q4H tensor-core attention (head_dim 128)
-// CTA = (kv head, split), 4 warps.  QK^T and P.V are INT8 m16n8k32 MMAs whose B
-// operands are built straight from the packed nibbles in global memory: a code c
-// sits in the byte's high half as 16*c (one shift/mask per 8 codes) and the factor
-// 1/16 is folded into the score / output scale (exact power of two).  The k-slot
-// order inside an MMA is free as long as A and B agree, so even/odd codes of a
-// word feed the two halves of the k dimension without any shuffling.
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                       uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};\n"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__global__ void __launch_bounds__(128)
-attention_q4h_mma_kernel(AttentionArgs a, Partials part) {
-  constexpr uint32_t HD = 128;
-  __shared__ __align__(16) int8_t qs[32][HD + 16];  // +16: rows land on different banks
-  __shared__ float S[32][33];
-  __shared__ __align__(16) uint32_t Pq[32][8];      // 32 int8 probabilities per row
-  __shared__ float rmax[32], rsum[32], rprev[32], rpscale[32], rqscale[32];
-  __shared__ float kscale[32], vscale[32];
-  const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
-  const uint32_t g = lane >> 2U, t = lane & 3U;
-  const uint32_t kvh = blockIdx.x, split = blockIdx.y;
-  const uint32_t group = a.q_heads / a.kv_heads;
-  const uint32_t MR = a.rows * group;
-  const uint32_t first_ctx = *a.first_position + a.position_offset + 1U;
-  const uint32_t total = first_ctx + a.rows - 1U;
-  const uint32_t first = split * a.split_tokens;
-  if (first >= total) return;
-  const uint32_t last = min(total, first + a.split_tokens);
-  const uint32_t pt = a.page_tokens;
-  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
-  const float inv_sqrt = 1.0F / sqrtf(static_cast<float>(HD));
-
-  // INT8 queries, one warp per matrix row
-  for (uint32_t mr = warp; mr < 32U; mr += 4U) {
-    float vals[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-    if (mr < MR) {
-      const uint32_t row = mr / group, head = kvh * group + mr % group;
-      const float4 q4 = *reinterpret_cast<const float4*>(
-          a.query + static_cast<size_t>(row) * a.query_row_stride + static_cast<size_t>(head) * HD + lane * 4U);
-      vals[0] = q4.x; vals[1] = q4.y; vals[2] = q4.z; vals[3] = q4.w;
-    }
-    float m = fmaxf(fmaxf(fabsf(vals[0]), fabsf(vals[1])), fmaxf(fabsf(vals[2]), fabsf(vals[3])));
-    m = warp_max(m);
-    const float sc = fmaxf(m / 127.0F, 0x1p-24F);
-    uint32_t packed = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int q = mr < MR ? max(-127, min(127, __float2int_rn(vals[i] / sc))) : 0;
-      packed |= (static_cast<uint32_t>(q) & 0xffU) << (8 * i);
-    }
-    *reinterpret_cast<uint32_t*>(&qs[mr][lane * 4U]) = packed;
-    if (lane == 0U) { rqscale[mr] = mr < MR ? sc : 0.0F; rmax[mr] = kNegInf; rsum[mr] = 0.0F; }
-  }
-  __syncthreads();
-  const uint32_t mt = warp >> 1U, half = warp & 1U;
-  // A fragments of this warp's 16 query rows for the four 32-dim k-steps
-  uint32_t qa[4][4];
-#pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    const uint2 lo = *reinterpret_cast<const uint2*>(&qs[16U * mt + g][32 * ks + 8 * t]);
-    const uint2 hi = *reinterpret_cast<const uint2*>(&qs[16U * mt + g + 8U][32 * ks + 8 * t]);
-    qa[ks][0] = __byte_perm(lo.x, lo.y, 0x6420);  // even dims -> k slots 4t..4t+3
-    qa[ks][1] = __byte_perm(hi.x, hi.y, 0x6420);
-    qa[ks][2] = __byte_perm(lo.x, lo.y, 0x7531);  // odd dims -> k slots 16+4t..
-    qa[ks][3] = __byte_perm(hi.x, hi.y, 0x7531);
-  }
-  float out[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) out[j][i] = 0.0F;
-
-  for (uint32_t t0 = first; t0 < last; t0 += 32U) {
-    const uint32_t n = min(32U, last - t0);
-    // every key of the tile lies in one page (page_tokens % 32 == 0, t0 % 32 == 0)
-    const uint8_t* layer = a.page_table[t0 / pt] + a.layer_offset;
-    const uint32_t slot0 = t0 % pt;
-    const uint8_t* kcodes = layer + (static_cast<size_t>(kvh) * pt + slot0) * (HD / 2U);
-    const uint8_t* vcodes = layer + records * (HD / 2U) + records * 2U +
-                            (static_cast<size_t>(kvh) * pt + slot0) * (HD / 2U);
-    if (tid < 64U) {
-      const uint32_t j = tid & 31U;
-      const uint8_t* base = tid < 32U ? layer + records * (HD / 2U)
-                                      : layer + records * (HD / 2U) * 2U + records * 2U;
-      const float sc = __half2float(reinterpret_cast<const __half*>(base)[static_cast<size_t>(kvh) * pt + slot0 + j]);
-      (tid < 32U ? kscale : vscale)[j] = j < n ? sc : 0.0F;
-    }
-    // V words of this warp's dim half for the 8 keys this lane feeds into P.V
-    uint32_t vw[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t key = (i < 4 ? 4U * t + i : 16U + 4U * t + (i - 4));
-      vw[i] = *reinterpret_cast<const uint32_t*>(vcodes + key * (HD / 2U) + 4U * (g + 8U * half));
-    }
-    // ---- S = Q K^T for keys 16*half + {0..15}
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const uint32_t key = 16U * half + 8U * nt + g;
-      int c[4] = {0, 0, 0, 0};
-      const uint32_t* kw = reinterpret_cast<const uint32_t*>(kcodes + key * (HD / 2U));
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t w = kw[4 * ks + t];
-        mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], (w << 4U) & 0xf0f0f0f0U, w & 0xf0f0f0f0U);
-      }
-      const uint32_t col = 16U * half + 8U * nt + 2U * t;
-      S[16U * mt + g][col] = static_cast<float>(c[0]) * 0.0625F;
-      S[16U * mt + g][col + 1U] = static_cast<float>(c[1]) * 0.0625F;
-      S[16U * mt + g + 8U][col] = static_cast<float>(c[2]) * 0.0625F;
-      S[16U * mt + g + 8U][col + 1U] = static_cast<float>(c[3]) * 0.0625F;
-    }
-    __syncthreads();
-    // ---- online softmax: warp w owns rows 8w..8w+7, lane = key
-#pragma unroll 1
-    for (uint32_t i = 0; i < 8U; ++i) {
-      const uint32_t mr = 8U * warp + i;
-      const bool active = mr < MR;
-      const uint32_t ctx = first_ctx + (active ? mr / group : 0U);
-      const bool visible = active && lane < n && t0 + lane < ctx;
-      const float score = visible ? S[mr][lane] * rqscale[mr] * kscale[lane] * inv_sqrt : kNegInf;
-      const float tmax = warp_max(score);
-      const float old = rmax[mr];
-      const float next = fmaxf(old, tmax);
-      const float prev = old == kNegInf ? 0.0F : expf(old - next);
-      const float p = visible ? expf(score - next) : 0.0F;
-      const float tsum = static_cast<float>(warp_sum_f64(static_cast<double>(p)));
-      const float w = visible ? p * vscale[lane] : 0.0F;
-      const float wmax = warp_max(w);
-      const float pscale = fmaxf(wmax / 127.0F, 0x1p-24F);
-      reinterpret_cast<int8_t*>(&Pq[mr][0])[lane] =
-          static_cast<int8_t>(max(0, min(127, __float2int_rn(w / pscale))));
-      if (lane == 0U && active) {
-        rsum[mr] = rsum[mr] * prev + tsum;
-        rmax[mr] = next;
-        rprev[mr] = prev;
-        rpscale[mr] = pscale * 0.0625F;  // V bytes carry 16*code
-      }
-    }
-    __syncthreads();
-    // ---- O += P V for dims 64*half + 8*chunk + j, chunk = B column
-    {
-      const uint32_t pa0 = Pq[16U * mt + g][t], pa1 = Pq[16U * mt + g + 8U][t];
-      const uint32_t pa2 = Pq[16U * mt + g][4U + t], pa3 = Pq[16U * mt + g + 8U][4U + t];
-      uint32_t bl[2][4], bh[2][4];  // [key set][dim pair index]: 4x4 byte transposes
-#pragma unroll
-      for (int set = 0; set < 2; ++set) {
-        uint32_t lo[4], hi[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          lo[i] = (vw[4 * set + i] << 4U) & 0xf0f0f0f0U;  // dims 0,2,4,6 of the chunk
-          hi[i] = vw[4 * set + i] & 0xf0f0f0f0U;          // dims 1,3,5,7
-        }
-        uint32_t x0 = __byte_perm(lo[0], lo[1], 0x5140), x1 = __byte_perm(lo[2], lo[3], 0x5140);
-        uint32_t x2 = __byte_perm(lo[0], lo[1], 0x7362), x3 = __byte_perm(lo[2], lo[3], 0x7362);
-        bl[set][0] = __byte_perm(x0, x1, 0x5410); bl[set][1] = __byte_perm(x0, x1, 0x7632);
-        bl[set][2] = __byte_perm(x2, x3, 0x5410); bl[set][3] = __byte_perm(x2, x3, 0x7632);
-        x0 = __byte_perm(hi[0], hi[1], 0x5140); x1 = __byte_perm(hi[2], hi[3], 0x5140);
-        x2 = __byte_perm(hi[0], hi[1], 0x7362); x3 = __byte_perm(hi[2], hi[3], 0x7362);
-        bh[set][0] = __byte_perm(x0, x1, 0x5410); bh[set][1] = __byte_perm(x0, x1, 0x7632);
-        bh[set][2] = __byte_perm(x2, x3, 0x5410); bh[set][3] = __byte_perm(x2, x3, 0x7632);
-      }
-      const float prev_lo = rprev[16U * mt + g], prev_hi = rprev[16U * mt + g + 8U];
-      const float ps_lo = rpscale[16U * mt + g], ps_hi = rpscale[16U * mt + g + 8U];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {  // dim offset j inside the chunk: even -> bl[j/2], odd -> bh[j/2]
-        int c[4] = {0, 0, 0, 0};
-        const uint32_t b0 = (j & 1) ? bh[0][j >> 1] : bl[0][j >> 1];
-        const uint32_t b1 = (j & 1) ? bh[1][j >> 1] : bl[1][j >> 1];
-        mma_s8(c, pa0, pa1, pa2, pa3, b0, b1);
-        out[j][0] = out[j][0] * prev_lo + static_cast<float>(c[0]) * ps_lo;
-        out[j][1] = out[j][1] * prev_lo + static_cast<float>(c[1]) * ps_lo;
-        out[j][2] = out[j][2] * prev_hi + static_cast<float>(c[2]) * ps_hi;
-        out[j][3] = out[j][3] * prev_hi + static_cast<float>(c[3]) * ps_hi;
-      }
-    }
-    __syncthreads();
-  }
-  // ---- partials: C column n = 2t + e is B column (chunk) n -> dim 64*half + 8*n + j
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t mr = 16U * mt + g + (i >= 2 ? 8U : 0U);
-      if (mr >= MR) continue;
-      const uint32_t chunk = 2U * t + (i & 1U);
-      const uint32_t d = 64U * half + 8U * chunk + j;
-      const uint32_t row = mr / group, head = kvh * group + mr % group;
-      const size_t pidx = (static_cast<size_t>(row) * a.max_splits + split) * a.q_heads + head;
-      part.outputs[pidx * HD + d] = out[j][i];
-      if (d == 0U) { part.maxima[pidx] = rmax[mr]; part.sums[pidx] = rsum[mr]; }
-    }
-}
-
 // grid (q_heads, rows), block head_dim.
 __global__ void attention_combine_kernel(AttentionArgs a, Partials part) {
   __shared__ float gmax, gsum;
@@ -590,9 +389,12 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   const Partials part = partials_of(a);
   const dim3 grid(a.kv_heads, a.max_splits);
   if (a.impl == 1) {
-    if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 32U || a.query_row_stride % 4U)
-      return fail(QLLM_INVALID_ARGUMENT, "tensor-core attention needs Q4H, head_dim 128, rows*group <= 32");
-    attention_q4h_mma_kernel<<<grid, 128, 0, stream>>>(a, part);
+    if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 32U || a.query_row_stride % 4U ||
+        a.page_tokens % 64U || a.split_tokens % 64U)
+      return fail(QLLM_INVALID_ARGUMENT,
+                  "tensor-core attention needs Q4H, head_dim 128, rows*group <= 32, 64-token aligned pages and splits");
+    const int rc = launch_attention_q4h_pipelined(a, part.maxima, part.sums, part.outputs, a.error, stream);
+    if (rc) return rc;
   } else {
     const size_t smem = (static_cast<size_t>(MR) * a.head_dim + 32U * (a.head_dim + 1U) +
                          2U * MR * 33U + 5U * MR + 64U) * sizeof(float);
