@@ -208,6 +208,17 @@ size_t qllm_k_nvfp4_gemv_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t
 int qllm_k_nvfp4_gemv(const qllm_matrix* matrix, uint32_t first_row, uint32_t row_count,
                       const float* x, float* y, uint32_t batch, void* workspace,
                       size_t workspace_bytes, int impl, void* stream);
+/* Load-time preparation of one matrix (the provider does this once per tensor when it binds
+ * the weights, cf. ensure_tensor, dense_fp4_provider.cpp:3486-3677): builds the TMA descriptor
+ * and the re-tiled block scales the tensor-core GEMV reads.  The matrix memory must outlive
+ * the handle.  qllm_k_nvfp4_gemv_prepared is qllm_k_nvfp4_gemv without that per-call work
+ * and without a final synchronisation. */
+typedef struct qllm_prepared_matrix qllm_prepared_matrix;
+int qllm_k_matrix_prepare(const qllm_matrix* matrix, void* stream, qllm_prepared_matrix** out);
+void qllm_k_matrix_release(qllm_prepared_matrix* prepared);
+int qllm_k_nvfp4_gemv_prepared(const qllm_prepared_matrix* prepared, const float* x, float* y,
+                               uint32_t batch, void* workspace, size_t workspace_bytes, int impl,
+                               void* stream);
 /* Harness-owned weight quantiser on the device (formula of transformer_kernels.cu:1960-1967
  * applied to weight rows); w is fp32 [rows, cols]. */
 int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols,

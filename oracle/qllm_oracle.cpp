@@ -451,7 +451,8 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
               const uint8_t* vc = layer + records * (hd / 2U) + records * 2U + rec * (hd / 2U);
               dot += pq[j] * nibble_s4(vc[d / 2U], d & 1U);
             }
-            acc[d] += static_cast<float>(dot) * pscale;
+            // one fused multiply-add, as the reference's `results * prev + acc * scale` compiles to
+            acc[d] = std::fma(static_cast<float>(dot), pscale, acc[d]);
           }
         } else {
           std::vector<double> tdot(hd, 0.0);
@@ -488,14 +489,17 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
     const uint32_t active = (ctx + split_tokens - 1U) / split_tokens;
     float gmax = kNegInf;
     for (uint32_t s = 0; s < active; ++s) gmax = std::fmax(gmax, pmax[s]);
-    float gsum = 0.0F;
-    for (uint32_t s = 0; s < active; ++s) gsum += psum[s] * std::exp(pmax[s] - gmax);
+    // split terms are FP32 products; their sums are formed in double so that the merge does
+    // not depend on the order in which splits are visited
+    double gsum_d = 0.0;
+    for (uint32_t s = 0; s < active; ++s) gsum_d += static_cast<double>(psum[s] * std::exp(pmax[s] - gmax));
+    const float gsum = static_cast<float>(gsum_d);
     float* o = out + (static_cast<size_t>(row) * qh + head) * hd;
     for (uint32_t d = 0; d < hd; ++d) {
-      float result = 0.0F;
+      double result = 0.0;
       for (uint32_t s = 0; s < active; ++s)
-        result += pout[static_cast<size_t>(s) * hd + d] * std::exp(pmax[s] - gmax);
-      o[d] = act(result / gsum, bf16);
+        result += static_cast<double>(pout[static_cast<size_t>(s) * hd + d] * std::exp(pmax[s] - gmax));
+      o[d] = act(static_cast<float>(result) / gsum, bf16);
     }
   }
 }

@@ -71,6 +71,42 @@ int qllm_k_nvfp4_gemv(const qllm_matrix* m, uint32_t first_row, uint32_t row_cou
   return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
 }
 
+struct qllm_prepared_matrix {
+  qllm_matrix m;
+  MmaWeights mma;
+};
+
+int qllm_k_matrix_prepare(const qllm_matrix* m, void* stream, qllm_prepared_matrix** out) {
+  if (!m || !out || !m->codes || !m->scales || !m->rows || !m->cols || m->cols % 16U)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 matrix");
+  auto* p = new qllm_prepared_matrix;
+  p->m = *m;
+  const int rc = p->mma.prepare(*m, static_cast<cudaStream_t>(stream));
+  if (rc) {
+    delete p;
+    return rc;
+  }
+  *out = p;
+  return 0;
+}
+
+void qllm_k_matrix_release(qllm_prepared_matrix* p) { delete p; }
+
+int qllm_k_nvfp4_gemv_prepared(const qllm_prepared_matrix* p, const float* x, float* y, uint32_t batch,
+                               void* workspace, size_t workspace_bytes, int impl, void* stream) {
+  if (!p || !x || !y || !workspace || !batch) return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 GEMV");
+  if (workspace_bytes < qllm_k_nvfp4_gemv_workspace_bytes(batch, p->m.rows, p->m.cols))
+    return fail(QLLM_INVALID_ARGUMENT, "native NVFP4 GEMV workspace is too small");
+  auto s = static_cast<cudaStream_t>(stream);
+  if (impl == 0) {
+    int rc = launch_act_quant_i8(x, workspace, batch, p->m.cols, p->m.input_scale, s);
+    if (rc) return rc;
+    return launch_gemv_simt(p->m, 0U, p->m.rows, workspace, batch, y, batch, s);
+  }
+  if (impl != 1 || !p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+  return launch_gemv_mma(p->mma, p->m, 0U, p->m.rows, x, y, batch, workspace, workspace_bytes, s);
+}
+
 int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols, float global_scale,
                                   uint8_t* codes, uint8_t* scales, void* stream) {
   if (!w || !codes || !scales || !rows || !cols || cols % 16U || !(global_scale > 0.0F))

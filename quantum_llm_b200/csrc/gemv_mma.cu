@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "fused.h"
 #include "gemv_mma.h"
 
 namespace qllm {
@@ -292,7 +293,7 @@ struct GemvMmaParams {
   uint32_t* error;
   uint32_t first_tile, row_count, batch, n_pad;
   uint32_t k_chunks, k_atoms, split, stages;
-  float out_scale;              // weight_scale / input_scale applied as two operations
+  uint32_t raw;                 // 1: always write raw partials (the consumer applies the scale)
   float weight_scale, input_scale;
 };
 
@@ -418,14 +419,14 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
           const uint32_t col = n_tile * 128U + c0 + j;
           if (col >= p.batch) continue;
           const float acc = __uint_as_float(v[j]);
-          if (p.split == 1U)
+          if (p.split == 1U && !p.raw)
             p.y[static_cast<size_t>(col) * p.row_count + row] = bf16r(acc * p.weight_scale / p.input_scale);
           else
             p.partials[(static_cast<size_t>(blockIdx.y) * p.batch + col) * p.row_count + row] = acc;
         }
       }
     }
-  } else if (tid == 0U) {
+  } else if (tid == 0U && p.error != nullptr) {
     atomicExch(p.error, 100U);  // a pipeline wait ran out: results of this launch are invalid
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -443,6 +444,10 @@ __global__ void gemv_mma_finalize_kernel(const float* __restrict__ partials, flo
   for (uint32_t s = 0; s < split; ++s) sum += partials[static_cast<uint64_t>(s) * count + i];
   y[i] = bf16r(sum * weight_scale / input_scale);
 }
+
+int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
+             const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
+             uint32_t* split_out, cudaStream_t stream);
 
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
@@ -464,6 +469,35 @@ int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_ro
   count_launch();
   int rc = check_launch("act_quant_mma");
   if (rc) return rc;
+  rc = mma_core(w, m, first_row, row_count, batch, ws.codes, ws.atoms, ws.partials, y, ws.error, false, nullptr,
+                stream);
+  if (rc) return rc;
+  if (split > 1U) {
+    const uint64_t count = static_cast<uint64_t>(batch) * row_count;
+    gemv_mma_finalize_kernel<<<static_cast<unsigned>((count + 255U) / 256U), 256, 0, stream>>>(
+        ws.partials, y, count, split, m.weight_scale, m.input_scale);
+    count_launch();
+    rc = check_launch("gemv_mma_finalize");
+  }
+  return rc;
+}
+
+// Tensor-core GEMV over an operand that is already quantised (codes + atoms).  With `raw`
+// the result is left as split-K partials for the consumer; otherwise split == 1 writes y.
+int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
+             const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
+             uint32_t* split_out, cudaStream_t stream) {
+  const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
+  const uint32_t k_chunks = m.cols / kTileK;
+  const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
+  const uint32_t split = pick_split(row_tiles, n_tiles, k_chunks);
+  if (split_out) *split_out = split;
+  MmaWorkspace ws{};
+  ws.codes = const_cast<uint8_t*>(codes);
+  ws.atoms = const_cast<uint8_t*>(atoms);
+  ws.partials = partials;
+  ws.error = error;
+  int rc = 0;
   CUtensorMap act_map;
   rc = make_codes_map(&act_map, ws.codes, n_pad, m.cols / 2U, std::min(n_pad, 128U));
   if (rc) return rc;
@@ -493,19 +527,66 @@ int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_ro
   p.k_atoms = m.cols / 64U;
   p.split = split;
   p.stages = stages;
+  p.raw = raw ? 1U : 0U;
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
   nvfp4_gemv_mma_kernel<<<dim3(row_tiles, split, n_tiles), 128, smem, stream>>>(w.codes_map, act_map, p);
   count_launch();
-  rc = check_launch("nvfp4_gemv_mma");
-  if (rc) return rc;
-  if (split > 1U) {
-    const uint64_t count = static_cast<uint64_t>(batch) * row_count;
-    gemv_mma_finalize_kernel<<<static_cast<unsigned>((count + 255U) / 256U), 256, 0, stream>>>(
-        ws.partials, y, count, split, m.weight_scale, m.input_scale);
-    count_launch();
-    rc = check_launch("gemv_mma_finalize");
+  return check_launch("nvfp4_gemv_mma");
+}
+
+// ---- operand buffers and the implementation-neutral GEMV core ---------------------------
+size_t quant_buffer_bytes(uint32_t max_rows, uint32_t max_cols) {
+  const size_t simt = act_quant_bytes(max_rows, max_cols);
+  const size_t mma = align_up(static_cast<size_t>(128U) * (max_cols / 2U), 1024) +
+                     align_up(static_cast<size_t>(max_cols / 64U + 1U) * kAtomBytes, 1024);
+  return std::max(simt, mma) + 1024U;
+}
+
+QuantSink make_sink(int gemv_impl, void* quant_buffer, uint32_t rows, uint32_t cols, float g) {
+  QuantSink s{};
+  s.kind = gemv_impl;
+  s.cols = cols;
+  s.g = g;
+  uint8_t* base = static_cast<uint8_t*>(quant_buffer);
+  if (gemv_impl == 0) {
+    const size_t values = (static_cast<size_t>(rows) * cols + 15U) & ~static_cast<size_t>(15U);
+    s.xi8 = reinterpret_cast<int8_t*>(base);
+    s.xscale = reinterpret_cast<float*>(base + values);
+  } else {
+    s.codes = base;
+    s.atoms = base + align_up(static_cast<size_t>(128U) * (cols / 2U), 1024);
   }
+  return s;
+}
+
+size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
+  if (cols % kTileK) return static_cast<size_t>(batch) * rows;
+  const uint32_t row_tiles = (rows + kTileRows - 1U) / kTileRows;
+  return static_cast<size_t>(pick_split(row_tiles, 1U, cols / kTileK)) * batch * rows;
+}
+
+int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
+                     uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
+                     float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream) {
+  out->n = row_count;
+  out->batch = batch;
+  out->weight_scale = m.weight_scale;
+  out->input_scale = m.input_scale;
+  if (gemv_impl == 1 && w.ready && first_row % kTileRows == 0U && batch <= 128U) {
+    const QuantSink s = make_sink(1, quant_buffer, batch, m.cols, m.input_scale);
+    uint32_t split = 1;
+    const int rc = mma_core(w, m, first_row, row_count, batch, s.codes, s.atoms, partials, nullptr, error, true,
+                            &split, stream);
+    out->data = partials;
+    out->split = split;
+    return rc;
+  }
+  if (gemv_impl == 1)
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, first row % 128, rows <= 128)");
+  const int rc = launch_gemv_simt(m, first_row, row_count, quant_buffer, batch, final_out, batch, stream);
+  out->data = final_out;
+  out->split = 0U;
   return rc;
 }
 

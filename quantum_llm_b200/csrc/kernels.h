@@ -72,6 +72,7 @@ struct AttentionArgs {
   float* out;                 // [rows, q_heads*head_dim]
   int impl;                   // 0 scalar, 1 tensor-core (Q4H)
   uint32_t* error;            // optional device status word (set when a pipeline wait runs out)
+  bool skip_combine;          // leave the per-split partials in the workspace (merged by the caller)
 };
 int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
                                    uint32_t* error, cudaStream_t stream);
@@ -133,6 +134,7 @@ struct DraftSampleArgs {
   uint32_t from_sync;             // 1: called from a synchronisation batch (position is final)
   StepRecord* results;            // ring of the acceptance kernel (may be null)
   uint32_t results_capacity;
+  const uint32_t* kernel_error;   // status word of the pipelined kernels, folded into the state
 };
 int launch_draft_sample(const DraftSampleArgs& a, cudaStream_t stream);
 int launch_first_token(StepState* state, const uint32_t* argmax_token, const float* top_values,

@@ -7,6 +7,7 @@
 //   Q8 : [K records pt*kv*(hd+2)][V records], record = (pos%pt)*kv + kv_head, int8[hd] + f16 scale
 //   F16: [K pt*kv*hd f16][V ...], token-major
 #include "common.cuh"
+#include "fused.h"
 #include "kernels.h"
 
 namespace qllm {
@@ -33,7 +34,9 @@ __device__ __forceinline__ float block_max_small(float v, float* scratch) {
 }
 
 // grid (q_heads + kv_heads, rows), block head_dim threads.
-__global__ void rope_kv_store_kernel(RopeStoreArgs a) {
+// With `fused` the projections are read from the GEMV result `src` (final values or split-K
+// partials) and the rotated queries are written to q_out [rows, q_heads*head_dim].
+__global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, bool fused) {
   __shared__ float src[256];
   __shared__ float scratch[8];
   const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
@@ -41,8 +44,9 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a) {
   const uint32_t width = (a.q_heads + 2U * a.kv_heads) * hd;
   const uint32_t cache_position = *a.first_position + a.position_offset + row;
   const uint32_t rotary_position = cache_position + a.rotary_offset;
-  float* v = a.qkv + static_cast<size_t>(row) * width + static_cast<size_t>(head) * hd;
-  src[d] = actv(v[d], a.bf16);
+  float* v = fused ? (head < a.q_heads ? q_out + (static_cast<size_t>(row) * a.q_heads + head) * hd : nullptr)
+                   : a.qkv + static_cast<size_t>(row) * width + static_cast<size_t>(head) * hd;
+  src[d] = actv(fused ? gemv_value(src_out, row, head * hd + d) : v[d], a.bf16);
   __syncthreads();
   float result = src[d];
   if (d < a.rotary_dim) {
@@ -53,14 +57,15 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a) {
     result = src[d] * actv(cosf(angle), a.bf16) + other * actv(sinf(angle), a.bf16);
   }
   result = actv(result, a.bf16);
-  v[d] = result;
+  if (v) v[d] = result;
   if (head < a.q_heads) return;
 
   // K head: quantise and store the K record and the V record of the same kv head
   const uint32_t kvh = head - a.q_heads;
   const float key = result;
-  const float value = a.qkv[static_cast<size_t>(row) * width +
-                            static_cast<size_t>(a.q_heads + a.kv_heads + kvh) * hd + d];
+  const float value = fused ? gemv_value(src_out, row, (a.q_heads + a.kv_heads + kvh) * hd + d)
+                            : a.qkv[static_cast<size_t>(row) * width +
+                                    static_cast<size_t>(a.q_heads + a.kv_heads + kvh) * hd + d];
   const uint32_t pt = a.page_tokens;
   uint8_t* layer = a.page_table[cache_position / pt] + a.layer_offset;
   const size_t records = static_cast<size_t>(pt) * a.kv_heads;
@@ -119,7 +124,16 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a) {
 int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream) {
   if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
-  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a);
+  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a, GemvOut{}, nullptr, false);
+  count_launch();
+  return check_launch("rope_kv_store");
+}
+
+int launch_rope_kv_store_fused(const RopeStoreFusedArgs& f, cudaStream_t stream) {
+  const RopeStoreArgs& a = f.base;
+  if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U || !f.q_out)
+    return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
+  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a, f.qkv, f.q_out, true);
   count_launch();
   return check_launch("rope_kv_store");
 }
@@ -320,18 +334,16 @@ attention_scalar_kernel(AttentionArgs a, Partials part) {
         const uint32_t o = (pass * kAcc + i) * 256U + tid;
         if (o < outputs) {
           const uint32_t mr = o / hd, d = o % hd;
-          float dot;
           if (ENC == QLLM_KV_Q4H) {
             float idot = 0.0F;  // integer-valued terms: exact in FP32
             for (uint32_t j = 0; j < 32U; ++j) idot += P[mr * 33U + j] * tile[j * (hd + 1U) + d];
-            dot = idot * rpscale[mr];
+            acc[pass][i] = fmaf(idot, rpscale[mr], acc[pass][i] * rprev[mr]);
           } else {
             double ddot = 0.0;
             for (uint32_t j = 0; j < 32U; ++j)
               ddot += static_cast<double>(P[mr * 33U + j] * tile[j * (hd + 1U) + d]);
-            dot = static_cast<float>(ddot);
+            acc[pass][i] = acc[pass][i] * rprev[mr] + static_cast<float>(ddot);
           }
-          acc[pass][i] = acc[pass][i] * rprev[mr] + dot;
         }
       }
     }
@@ -421,9 +433,22 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
     }
     if (e != cudaSuccess) return check_cuda(e, "attention shared memory opt-in");
   }
-  attention_combine_kernel<<<dim3(a.q_heads, a.rows), a.head_dim, 0, stream>>>(a, part);
-  count_launch(2);
-  return check_launch("attention");
+  count_launch();
+  if (a.skip_combine) return check_launch("attention");  // the caller merges the splits itself
+  CombineArgs c{};
+  c.maxima = part.maxima;
+  c.sums = part.sums;
+  c.outputs = part.outputs;
+  c.first_position = a.first_position;
+  c.position_offset = a.position_offset;
+  c.q_heads = a.q_heads;
+  c.head_dim = a.head_dim;
+  c.split_tokens = a.split_tokens;
+  c.max_splits = a.max_splits;
+  c.bf16 = a.bf16;
+  c.out = a.out;
+  c.sink = no_sink();
+  return launch_combine_quant(c, a.rows, stream);
 }
 
 // ------------------------------------------------------- synthetic cache fill

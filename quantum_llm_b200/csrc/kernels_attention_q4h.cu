@@ -158,7 +158,8 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
     qa[ks][3] = __byte_perm(hi.x, hi.y, 0x7531);
   }
   const uint32_t row_lo = 16U * warp + g, row_hi = row_lo + 8U;
-  const float qs_lo = qscale_s[row_lo], qs_hi = qscale_s[row_hi];
+  // K bytes carry 16*code: the exact factor 1/16 rides on the query scale
+  const float qs_lo = qscale_s[row_lo] * 0.0625F, qs_hi = qscale_s[row_hi] * 0.0625F;
   const uint32_t ctx_lo = row_lo < MR ? first_ctx + row_lo / group : 0U;
   const uint32_t ctx_hi = row_hi < MR ? first_ctx + row_hi / group : 0U;
   float m_lo = kNegInf, m_hi = kNegInf, sum_lo = 0.0F, sum_hi = 0.0F;
@@ -203,9 +204,9 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
             const uint32_t tok = t0 - kb + key;
             const bool in = tok < last;
             sc_lo[2 * nt + e] = (in && tok < ctx_lo)
-                ? static_cast<float>(cfrag[e]) * 0.0625F * qs_lo * ksc * inv_sqrt : kNegInf;
+                ? static_cast<float>(cfrag[e]) * qs_lo * ksc * inv_sqrt : kNegInf;
             sc_hi[2 * nt + e] = (in && tok < ctx_hi)
-                ? static_cast<float>(cfrag[2 + e]) * 0.0625F * qs_hi * ksc * inv_sqrt : kNegInf;
+                ? static_cast<float>(cfrag[2 + e]) * qs_hi * ksc * inv_sqrt : kNegInf;
           }
         }
         // ---- online softmax per row (a row's 32 keys live in the 4 lanes of a quad)
@@ -281,10 +282,13 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
             const uint32_t b0 = (j & 1) ? bh[0][j >> 1] : bl[0][j >> 1];
             const uint32_t b1 = (j & 1) ? bh[1][j >> 1] : bl[1][j >> 1];
             mma_s8(cfrag, pa[0], pa[1], pa[2], pa[3], b0, b1);
-            out[h][j][0] = out[h][j][0] * prev_lo + static_cast<float>(cfrag[0]) * psl;
-            out[h][j][1] = out[h][j][1] * prev_lo + static_cast<float>(cfrag[1]) * psl;
-            out[h][j][2] = out[h][j][2] * prev_hi + static_cast<float>(cfrag[2]) * psh;
-            out[h][j][3] = out[h][j][3] * prev_hi + static_cast<float>(cfrag[3]) * psh;
+            // x * 1.0f is x: the rescale is skipped once the running maximum has settled
+            if (prev_lo != 1.0F) { out[h][j][0] *= prev_lo; out[h][j][1] *= prev_lo; }
+            if (prev_hi != 1.0F) { out[h][j][2] *= prev_hi; out[h][j][3] *= prev_hi; }
+            out[h][j][0] = fmaf(static_cast<float>(cfrag[0]), psl, out[h][j][0]);
+            out[h][j][1] = fmaf(static_cast<float>(cfrag[1]), psl, out[h][j][1]);
+            out[h][j][2] = fmaf(static_cast<float>(cfrag[2]), psh, out[h][j][2]);
+            out[h][j][3] = fmaf(static_cast<float>(cfrag[3]), psh, out[h][j][3]);
           }
         }
       }

@@ -400,9 +400,28 @@ argmax_kernel(const float* __restrict__ values, uint32_t count, uint32_t row_str
   const float* v = values + static_cast<size_t>(blockIdx.x) * row_stride;
   float best = kNegInf;
   uint32_t index = 0xffffffffU;
-  for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
-    const float x = v[i];
-    if (better(x, i, best, index)) { best = x; index = i; }
+  if ((reinterpret_cast<uintptr_t>(v) & 15U) == 0U) {
+    // 16-byte loads, four in flight per thread
+    const float4* v4 = reinterpret_cast<const float4*>(v);
+    const uint32_t n4 = count / 4U;
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 x = __ldg(v4 + i);
+      const uint32_t b = 4U * i;
+      if (better(x.x, b, best, index)) { best = x.x; index = b; }
+      if (better(x.y, b + 1U, best, index)) { best = x.y; index = b + 1U; }
+      if (better(x.z, b + 2U, best, index)) { best = x.z; index = b + 2U; }
+      if (better(x.w, b + 3U, best, index)) { best = x.w; index = b + 3U; }
+    }
+    for (uint32_t i = 4U * n4 + threadIdx.x; i < count; i += blockDim.x) {
+      const float x = v[i];
+      if (better(x, i, best, index)) { best = x; index = i; }
+    }
+  } else {
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+      const float x = v[i];
+      if (better(x, i, best, index)) { best = x; index = i; }
+    }
   }
   block_best(best, index, sv, si);
   if (threadIdx.x == 0U) out[blockIdx.x] = index;

@@ -251,6 +251,7 @@ __global__ void draft_sample_kernel(DraftSampleArgs a, uint32_t commit) {
     }
   }
   if (commit) {
+    if (a.kernel_error != nullptr && *a.kernel_error != 0U && s->error == 0U) s->error = *a.kernel_error;
     s->verify_tokens[0] = s->next_token;
     s->position = s->new_position;
     if (a.results != nullptr && !a.from_sync) {

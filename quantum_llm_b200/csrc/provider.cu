@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "gemv_mma.h"
+#include "fused.h"
 #include "kernels.h"
 
 namespace qllm {
@@ -124,9 +125,10 @@ struct qllm_provider {
   std::vector<size_t> layer_off;
   size_t page_bytes = 0;
   // workspaces (rows <= kMaxRows)
-  DeviceBuffer<float> hidden, residual, normalized, qkv, attn, gate_up, inter, logits, xq, fused;
-  DeviceBuffer<float> mtp_emb, mtp_emb_norm, mtp_hid_norm, draft_logits;
-  DeviceBuffer<uint8_t> attn_ws, topk_ws, gemv_ws;
+  DeviceBuffer<float> hidden, mtp_hidden, qkv, logits, mtp_emb, draft_logits;
+  DeviceBuffer<float> partial_buf, gemv_out;   // tensor-core split-K partials / CUDA-core results
+  DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
+  DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
   DeviceBuffer<float> top_values;
   uint32_t max_splits = 0;
@@ -212,32 +214,34 @@ struct qllm_provider {
     const uint32_t R = kMaxRows;
     const uint32_t qkv_w = (c.q_heads + 2U * c.kv_heads) * c.head_dim;
     hidden.alloc(static_cast<size_t>(R) * c.hidden, "hidden");
-    residual.alloc(static_cast<size_t>(R) * c.hidden, "residual");
-    normalized.alloc(static_cast<size_t>(R) * c.hidden, "normalized");
-    qkv.alloc(static_cast<size_t>(R) * qkv_w, "qkv");
-    attn.alloc(static_cast<size_t>(R) * c.q_heads * c.head_dim, "attention");
-    gate_up.alloc(static_cast<size_t>(R) * 2U * c.ffn, "gate_up");
-    inter.alloc(static_cast<size_t>(R) * c.ffn, "intermediate");
+    mtp_hidden.alloc(static_cast<size_t>(R) * c.hidden, "draft residual stream");
+    qkv.alloc(static_cast<size_t>(R) * qkv_w, "rotated queries");
     logits.alloc(static_cast<size_t>(R) * c.vocab, "logits");
     const uint32_t widest = std::max(std::max(2U * c.hidden, c.ffn), c.q_heads * c.head_dim);
-    xq.alloc(static_cast<size_t>(R) * widest, "quantised activations");
-    fused.alloc(static_cast<size_t>(R) * 2U * c.hidden, "fusion input");
+    quant_buf.alloc(quant_buffer_bytes(R, widest), "quantised GEMV operand");
+    size_t partial_floats = 0;
+    const uint32_t shapes[6][2] = {{qkv_w, c.hidden}, {c.hidden, c.q_heads * c.head_dim}, {2U * c.ffn, c.hidden},
+                                   {c.hidden, c.ffn}, {c.vocab, c.hidden}, {c.hidden, 2U * c.hidden}};
+    uint32_t most_outputs = 0;
+    for (const auto& s : shapes) {
+      partial_floats = std::max(partial_floats, gemv_partial_floats(R, s[0], s[1]));
+      most_outputs = std::max(most_outputs, s[0] == c.vocab ? 0U : s[0]);
+    }
+    partial_buf.alloc(partial_floats, "split-K partial sums");
+    gemv_out.alloc(static_cast<size_t>(R) * most_outputs, "GEMV results");
+    kernel_error.alloc(1, "kernel status word");
+    cu(cudaMemsetAsync(kernel_error.p, 0, sizeof(uint32_t), stream), "kernel status word");
     mtp_emb.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding");
-    mtp_emb_norm.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding norm");
-    mtp_hid_norm.alloc(static_cast<size_t>(R) * c.hidden, "draft hidden norm");
     draft_logits.alloc(c.draft_vocab, "draft logits");
     // the page pool keeps a few slots of slack past max_context for speculative rows
     max_splits = (c.max_context + 2U * kMaxRows + c.split_tokens - 1U) / c.split_tokens;
     attn_ws.alloc(attention_workspace_bytes(R, c.q_heads, c.head_dim, max_splits), "attention partials");
     topk_ws.alloc(topk_workspace_bytes(R, c.vocab, 64), "top-k partials");
-    const uint32_t most_rows = std::max(std::max(c.vocab, 2U * c.ffn), qkv_w);
-    gemv_ws.alloc(gemv_mma_workspace_bytes(R, most_rows, widest), "GEMV workspace");
     argmax_out.alloc(R, "argmax");
     top_tokens.alloc(static_cast<size_t>(R) * 64U, "top-k tokens");
     top_values.alloc(static_cast<size_t>(R) * 64U, "top-k values");
     tokens_dev.alloc(R, "token upload");
     first_token_dev.alloc(1, "first token");
-    verify_hidden.alloc(static_cast<size_t>(R) * c.hidden, "verify hidden rows");
     cu(cudaStreamSynchronize(stream), "provider set-up");
   }
 
@@ -247,34 +251,60 @@ struct qllm_provider {
   }
 
   // ------------------------------------------------------------------ ops
-  // y[rows, row_count] = bf16(fakequant(x) . W[first_row..]^T)
-  void project(const Matrix& w, const float* x, float* y, uint32_t rows, uint32_t first_row = 0,
-               uint32_t row_count = 0) {
+  // Every GEMV reads its operand from quant_buf (written by the producer kernel before it)
+  // and leaves its result either as final values (CUDA-core kernel) or as split-K partials
+  // (tensor-core kernel) that the consumer kernel sums and scales.
+  int impl_for(const Matrix& w) const { return gemv_impl == 1 && w.mma.ready ? 1 : 0; }
+  QuantSink sink_for(const Matrix& w, uint32_t rows) {
+    return make_sink(impl_for(w), quant_buf.p, rows, w.m.cols, w.m.input_scale);
+  }
+  GemvOut gemv(const Matrix& w, uint32_t rows, uint32_t row_count = 0, float* final_out = nullptr) {
     if (!row_count) row_count = w.m.rows;
-    if (gemv_impl == 1) {
-      ok(launch_gemv_mma(w.mma, w.m, first_row, row_count, x, y, rows, gemv_ws.p, gemv_ws.n, stream));
-    } else {
-      ok(launch_act_quant_i8(x, xq.p, rows, w.m.cols, w.m.input_scale, stream));
-      ok(launch_gemv_simt(w.m, first_row, row_count, xq.p, rows, y, rows, stream));
-    }
+    GemvOut o{};
+    ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
+                        final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream));
+    return o;
+  }
+  // x' = act(x + delta) stored to `store`; operand of `next` = quantised rmsnorm(x') * weight
+  void norm_quant(const float* x, uint32_t x_stride, const GemvOut* delta, float* store, const float* weight,
+                  const Matrix* next, uint32_t rows, uint32_t sink_block_offset = 0,
+                  const uint32_t* row_select = nullptr) {
+    const auto& c = cfg;
+    NormQuantArgs a{};
+    a.x = x;
+    a.x_stride = x_stride;
+    a.cols = c.hidden;
+    a.has_delta = delta != nullptr;
+    if (delta) a.delta = *delta;
+    a.bf16 = c.activation_bf16 != 0U;
+    a.store = store;
+    a.store_stride = c.hidden;
+    a.weight = weight;
+    a.eps = c.eps;
+    a.sink = next ? sink_for(*next, rows) : no_sink();
+    a.sink_block_offset = sink_block_offset;
+    a.row_select = row_select;
+    ok(launch_residual_norm_quant(a, rows, stream));
   }
 
   // One transformer block over `rows` rows held in hidden: attention sub-block
   // (run_full_attention + residual add) then FFN (run_ffn), pre-norm / ABI 1.
-  void block(const Block& b, uint32_t rows, uint32_t enc, size_t layer_offset,
-             qllm_request_state& st, const uint32_t* first_position, uint32_t position_offset,
-             uint32_t rotary_offset, uint32_t splits) {
+  // `h` holds the residual stream of the rows; `pending` is the GEMV result still to be added
+  // to it (null for the first block of a pass) and is replaced by this block's down projection.
+  void block(const Block& b, float* h, bool h_valid, GemvOut* pending, bool has_pending, uint32_t rows,
+             uint32_t enc, size_t layer_offset, qllm_request_state& st, const uint32_t* first_position,
+             uint32_t position_offset, uint32_t rotary_offset, uint32_t splits) {
     const auto& c = cfg;
     const bool bf = c.activation_bf16 != 0U;
-    const uint32_t qkv_w = (c.q_heads + 2U * c.kv_heads) * c.head_dim;
-    cu(cudaMemcpyAsync(residual.p, hidden.p, static_cast<size_t>(rows) * c.hidden * sizeof(float),
-                       cudaMemcpyDeviceToDevice, stream), "retain attention residual");
-    ok(launch_rms_norm(hidden.p, b.input_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
-    project(b.qkv, normalized.p, qkv.p, rows);
-    RopeStoreArgs rs{qkv.p, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
-                     first_position, position_offset, rotary_offset, st.page_table, layer_offset,
-                     c.page_tokens, enc, bf};
-    ok(launch_rope_kv_store(rs, stream));
+    norm_quant(h_valid ? h : nullptr, c.hidden, has_pending ? pending : nullptr, h, b.input_norm, &b.qkv, rows);
+    RopeStoreFusedArgs rs{};
+    rs.qkv = gemv(b.qkv, rows);
+    rs.q_out = qkv.p;
+    rs.base = RopeStoreArgs{nullptr, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
+                            first_position, position_offset, rotary_offset, st.page_table, layer_offset,
+                            c.page_tokens, enc, bf};
+    ok(launch_rope_kv_store_fused(rs, stream));
+    const uint32_t qkv_w = c.q_heads * c.head_dim;  // rotated queries only
     AttentionArgs at{};
     at.encoding = enc;
     at.page_table = st.page_table;
@@ -292,19 +322,32 @@ struct qllm_provider {
     at.max_splits = splits;
     at.bf16 = bf;
     at.workspace = attn_ws.p;
-    at.out = attn.p;
+    at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
     at.impl = (attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
                rows * (c.q_heads / c.kv_heads) <= 32U) ? 1 : 0;
+    at.error = kernel_error.p;
+    at.skip_combine = true;
     ok(launch_attention(at, stream));
-    project(b.o, attn.p, hidden.p, rows);
-    ok(launch_add(hidden.p, residual.p, static_cast<uint64_t>(rows) * c.hidden, bf, stream));
-    cu(cudaMemcpyAsync(residual.p, hidden.p, static_cast<size_t>(rows) * c.hidden * sizeof(float),
-                       cudaMemcpyDeviceToDevice, stream), "retain FFN residual");
-    ok(launch_rms_norm(hidden.p, b.post_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
-    project(b.gate_up, normalized.p, gate_up.p, rows);
-    ok(launch_silu_product(gate_up.p, inter.p, rows, c.ffn, bf, stream));
-    project(b.down, inter.p, hidden.p, rows);
-    ok(launch_add(hidden.p, residual.p, static_cast<uint64_t>(rows) * c.hidden, bf, stream));
+    CombineArgs cb{};
+    const size_t items = static_cast<size_t>(rows) * splits * c.q_heads;
+    cb.maxima = reinterpret_cast<const float*>(attn_ws.p);
+    cb.sums = cb.maxima + items;
+    cb.outputs = cb.maxima + 2U * items;
+    cb.first_position = first_position;
+    cb.position_offset = position_offset;
+    cb.q_heads = c.q_heads;
+    cb.head_dim = c.head_dim;
+    cb.split_tokens = c.split_tokens;
+    cb.max_splits = splits;
+    cb.bf16 = bf;
+    cb.out = nullptr;
+    cb.sink = sink_for(b.o, rows);
+    ok(launch_combine_quant(cb, rows, stream));
+    const GemvOut o_out = gemv(b.o, rows);
+    norm_quant(h, c.hidden, &o_out, h, b.post_norm, &b.gate_up, rows);
+    const GemvOut gu = gemv(b.gate_up, rows);
+    ok(launch_silu_quant(gu, c.ffn, bf, sink_for(b.down, rows), nullptr, stream));
+    *pending = gemv(b.down, rows);
   }
 
   uint32_t splits_for(uint32_t tokens) const {
@@ -316,12 +359,17 @@ struct qllm_provider {
                   const uint32_t* first_position, uint32_t splits, bool with_head) {
     const auto& c = cfg;
     ok(launch_embedding(embedding, tokens, hidden.p, rows, c.hidden, c.vocab, stream));
+    GemvOut pending{};
     for (uint32_t l = 0; l < c.layers; ++l)
-      block(layers[l], rows, c.kv_encoding, layer_off[l], st, first_position, 0U, 0U, splits);
+      block(layers[l], hidden.p, true, &pending, l > 0U, rows, c.kv_encoding, layer_off[l], st, first_position,
+            0U, 0U, splits);
     last_rows = rows;
+    // last residual add (+ final norm and the head's operand)
+    norm_quant(hidden.p, c.hidden, &pending, hidden.p, with_head ? final_norm : nullptr, with_head ? &head : nullptr,
+               rows);
     if (with_head) {
-      ok(launch_rms_norm(hidden.p, final_norm, normalized.p, rows, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
-      project(head, normalized.p, logits.p, rows);
+      const GemvOut lg = gemv(head, rows, 0U, logits.p);
+      ok(launch_gemv_finalize(lg, logits.p, stream));
     }
   }
 
@@ -343,16 +391,20 @@ struct qllm_provider {
                uint32_t top_k) {
     const auto& c = cfg;
     ok(launch_embedding(embedding, tokens, mtp_emb.p, rows, c.hidden, c.vocab, stream));
-    // [norm(embedding) | norm(previous hidden)] written straight into the fusion input
-    ok(launch_rms_norm(mtp_emb.p, mtp_embedding_norm, fused.p, rows, c.hidden, c.hidden, 2U * c.hidden, c.eps, nullptr, stream));
-    ok(launch_rms_norm(previous_hidden, mtp_hidden_norm, fused.p + c.hidden, rows, c.hidden, c.hidden, 2U * c.hidden, c.eps, nullptr, stream));
-    project(mtp_fusion, fused.p, hidden.p, rows);
-    block(mtp_block, rows, c.mtp_kv_encoding, layer_off[c.layers], st, first_position,
-          position_offset, 1U, splits);
+    // [norm(embedding) | norm(previous hidden)] quantised straight into the two halves of
+    // the fusion projection's operand
+    norm_quant(mtp_emb.p, c.hidden, nullptr, nullptr, mtp_embedding_norm, &mtp_fusion, rows, 0U);
+    norm_quant(previous_hidden, c.hidden, nullptr, nullptr, mtp_hidden_norm, &mtp_fusion, rows, c.hidden / 16U);
+    GemvOut pending = gemv(mtp_fusion, rows);
+    // the draft block runs in its own residual buffer, so the target's rows stay readable
+    block(mtp_block, mtp_hidden.p, false, &pending, true, rows, c.mtp_kv_encoding, layer_off[c.layers], st,
+          first_position, position_offset, 1U, splits);
     if (!produce) return;
-    ok(launch_copy_rows(st.mtp_last_hidden, c.hidden, hidden.p, c.hidden, 1, c.hidden, select_row, stream));
-    ok(launch_rms_norm(st.mtp_last_hidden, mtp_draft_norm, normalized.p, 1, c.hidden, c.hidden, c.hidden, c.eps, nullptr, stream));
-    project(head, normalized.p, draft_logits.p, 1, 0, c.draft_vocab);
+    // residual add of the selected row, kept as the chained passes' previous hidden, then the
+    // draft norm and the head over the draft vocabulary
+    norm_quant(mtp_hidden.p, c.hidden, &pending, st.mtp_last_hidden, mtp_draft_norm, &head, 1U, 0U, select_row);
+    const GemvOut lg = gemv(head, 1U, c.draft_vocab, draft_logits.p);
+    ok(launch_gemv_finalize(lg, draft_logits.p, stream));
     select_candidates(draft_logits.p, 1, c.draft_vocab, c.draft_vocab, sampled, top_k);
   }
 
@@ -365,7 +417,7 @@ struct qllm_provider {
               i - 1U, splits, true, nullptr, sampled, top_k);
       DraftSampleArgs ds{st.state, argmax_out.p, top_values.p, top_tokens.p,
                          i | (i + 1U == c.draft_depth ? 0x80000000U : 0U), from_sync ? 1U : 0U,
-                         st.results, kResultRing};
+                         st.results, kResultRing, kernel_error.p};
       ok(launch_draft_sample(ds, stream));
     }
   }
@@ -382,21 +434,13 @@ struct qllm_provider {
     ok(launch_accept(aa, stream));
     // first draft pass: accepted drafts + selected token against the target's hidden rows;
     // rows past accepted+1 are padding whose cache records are overwritten before any read
-    run_mtp(st, s->mtp_tokens, hidden_rows_for_mtp(), R, &s->position, 0U, mtp_splits, true,
+    run_mtp(st, s->mtp_tokens, hidden.p, R, &s->position, 0U, mtp_splits, true,
             &s->accepted, sampled, top_k);
     DraftSampleArgs ds{s, argmax_out.p, top_values.p, top_tokens.p,
-                       0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 0U, st.results, kResultRing};
+                       0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 0U, st.results, kResultRing,
+                       kernel_error.p};
     ok(launch_draft_sample(ds, stream));
     rollout(st, mtp_splits, sampled, top_k);
-  }
-
-  // run_mtp reuses `hidden` as its working buffer, so the verify rows are parked first.
-  DeviceBuffer<float> verify_hidden;
-  const float* hidden_rows_for_mtp() {
-    const auto& c = cfg;
-    cu(cudaMemcpyAsync(verify_hidden.p, hidden.p, static_cast<size_t>(last_rows) * c.hidden * sizeof(float),
-                       cudaMemcpyDeviceToDevice, stream), "park verify hidden rows");
-    return verify_hidden.p;
   }
 
   void bind_request(qllm_request_state& st, const qllm_request& rq) {
@@ -595,7 +639,7 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
     if (produce) {
       DraftSampleArgs ds{s, p->argmax_out.p, p->top_values.p, p->top_tokens.p,
                          0U | (c.draft_depth == 1U ? 0x80000000U : 0U), 1U, st->results,
-                         qllm_provider::kResultRing};
+                         qllm_provider::kResultRing, p->kernel_error.p};
       ok(launch_draft_sample(ds, p->stream));
       p->rollout(*st, splits, sampled, rq->sampling_top_k, true);
       uint32_t drafts = 0;
@@ -759,7 +803,7 @@ int qllm_provider_read_hidden(qllm_provider* p, qllm_request_state* st, int whic
   return guarded([&] {
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
-    const float* src = which ? p->verify_hidden.p : st->retained_hidden;
+    const float* src = which ? p->hidden.p : st->retained_hidden;
     cu(cudaMemcpy(out, src, static_cast<size_t>(rows) * p->cfg.hidden * sizeof(float), cudaMemcpyDeviceToHost), "read hidden");
   });
 }

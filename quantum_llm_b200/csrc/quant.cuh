@@ -1,0 +1,79 @@
+// Device-side NVFP4 activation quantisation shared by the fused producer kernels, and the
+// descriptor of a GEMV result that its consumers read (final values or split-K partials).
+#pragma once
+
+#include "common.cuh"
+
+namespace qllm {
+
+// Where quantised activations go: the operand format of the CUDA-core GEMV (INT8 values +
+// FP32 block scales) or of the tensor-core GEMV (packed E2M1 codes + E4M3 scale atoms).
+struct QuantSink {
+  int kind;          // 0 = CUDA-core operand, 1 = tensor-core operand
+  int8_t* xi8;       // [rows, cols]
+  float* xscale;     // [rows, cols/16]
+  uint8_t* codes;    // [rows_padded, cols/2]
+  uint8_t* atoms;    // [cols/64][512]: (row%32)*16 + (row/32)*4 + block%4
+  uint32_t cols;     // row length of the operand (K of the GEMV that consumes it)
+  float g;           // activation global scale of that GEMV
+};
+
+// Quantises 16 consecutive values (block `block` of row `row`) and stores them.
+__device__ __forceinline__ void quant_store_block16(const QuantSink& q, uint32_t row, uint32_t block,
+                                                    const float (&v)[16]) {
+  float amax = 0.0F;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const unsigned sc = e4m3_code(fminf(448.0F, q.g * amax / 6.0F));
+  const float local = e4m3_value(sc);
+  if (q.kind == 0) {
+    uint32_t packed[4] = {0U, 0U, 0U, 0U};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float scaled = local == 0.0F ? 0.0F : fminf(6.0F, fmaxf(-6.0F, v[i] * q.g / local));
+      const unsigned code = e2m1_code(scaled);
+      const unsigned m = code & 7U;
+      int twice = m < 5U ? static_cast<int>(m) : static_cast<int>(2U * m - 4U) + (m == 7U ? 2 : 0);
+      if (code & 8U) twice = -twice;
+      packed[i / 4] |= (static_cast<uint32_t>(twice) & 0xffU) << (8 * (i % 4));
+    }
+    const size_t blocks = q.cols / 16U;
+    reinterpret_cast<uint4*>(q.xi8 + static_cast<size_t>(row) * q.cols)[block] =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    q.xscale[static_cast<size_t>(row) * blocks + block] = local;
+  } else {
+    uint32_t packed[2] = {0U, 0U};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      unsigned code = 0U;
+      if (local != 0.0F) code = e2m1_code(fminf(6.0F, fmaxf(-6.0F, v[i] * q.g / local)));
+      packed[i / 8] |= code << (4 * (i % 8));
+    }
+    reinterpret_cast<uint2*>(q.codes + static_cast<size_t>(row) * (q.cols / 2U))[block] =
+        make_uint2(packed[0], packed[1]);
+    const uint32_t tile = row / 128U, r = row % 128U;
+    q.atoms[(static_cast<size_t>(tile) * (q.cols / 64U) + block / 4U) * 512U + (r % 32U) * 16U + (r / 32U) * 4U +
+            block % 4U] = static_cast<uint8_t>(sc);
+  }
+}
+
+// Result of a GEMV as its consumers see it: either final BF16-rounded values [batch, n], or
+// `split` raw FP32 partial sums [split][batch][n] that still need the output scale.
+struct GemvOut {
+  const float* data;
+  uint32_t split;   // 0: data holds final values
+  uint32_t n;       // outputs per activation row
+  uint32_t batch;
+  float weight_scale, input_scale;
+};
+
+__device__ __forceinline__ float gemv_value(const GemvOut& o, uint32_t row, uint32_t col) {
+  const size_t i = static_cast<size_t>(row) * o.n + col;
+  if (o.split == 0U) return o.data[i];
+  float sum = 0.0F;
+  const size_t stride = static_cast<size_t>(o.batch) * o.n;
+  for (uint32_t s = 0; s < o.split; ++s) sum += o.data[s * stride + i];
+  return bf16r(sum * o.weight_scale / o.input_scale);
+}
+
+}  // namespace qllm

@@ -99,6 +99,20 @@ def test_tiny_greedy_tokens_and_logits(graph):
     assert t["exact_calls"] == gpu["steps"] and t["kernel_launches"] > 0
 
 
+def test_tiny_greedy_with_tensor_core_gemv():
+    # tcgen05 accumulates in FP32 inside the tensor core: results may land one BF16 step
+    # away from the exactly-rounded oracle, and W4A4 re-quantisation can amplify that for a
+    # row; most rows stay within the stated tolerance and the stream follows the oracle until
+    # a tie or such an event
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prompt = synth.prompt(4096, 128, 0)
+    gpu = run_gpu(model, prompt, 0, 64, graph=True, gemv_impl=1)
+    cpu = run_cpu(model, prompt, 0, 64)
+    c = compare(gpu, cpu, len(prompt))
+    print("tensor-core greedy parity", c)
+    assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
+
+
 def test_greedy_stream_equals_plain_target_decoding_on_gpu():
     # property that needs no oracle: speculative greedy output does not depend on the drafts,
     # so a provider with a different draft block emits the same tokens
