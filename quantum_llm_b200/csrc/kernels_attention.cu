@@ -158,6 +158,59 @@ static Partials partials_of(const AttentionArgs& a) {
 // ------------------------------------------------- scalar attention (all encodings)
 // CTA = (kv head, split), 256 threads, 32-key tiles staged in shared memory.
 // Dynamic shared memory: q[MR][hd] | tile[32][hd+1] | S[MR][33] | P[MR][33] | stats.
+// Decodes the K (or V) records of up to 32 tokens into tile[j][d] (FP32, row stride hd+1).
+// 256 threads: thread = (token j, eighth of the head); every thread resolves its page and
+// record once and then issues independent vector loads.
+template <uint32_t ENC>
+__device__ __forceinline__ void load_kv_tile(const AttentionArgs& a, uint32_t kvh, uint32_t t0, uint32_t n,
+                                             bool is_value, float* tile) {
+  const uint32_t hd = a.head_dim, pt = a.page_tokens;
+  const uint32_t j = threadIdx.x >> 3U, part = threadIdx.x & 7U;
+  const uint32_t dpp = hd / 8U, d0 = part * dpp;  // dims per thread (multiple of 8)
+  float* out = tile + j * (hd + 1U) + d0;
+  if (j >= n) {
+    for (uint32_t e = 0; e < dpp; ++e) out[e] = 0.0F;
+    return;
+  }
+  const uint32_t tok = t0 + j;
+  const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
+  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
+  if (ENC == QLLM_KV_Q4H) {
+    const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
+    const uint8_t* codes = layer + (is_value ? records * (hd / 2U) + records * 2U : 0U) + rec * (hd / 2U) + d0 / 2U;
+    for (uint32_t w = 0; w < dpp / 8U; ++w) {
+      const uint32_t word = reinterpret_cast<const uint32_t*>(codes)[w];
+#pragma unroll
+      for (uint32_t i = 0; i < 8U; ++i) {
+        const int nib = static_cast<int>((word >> (4U * i)) & 15U);
+        out[8U * w + i] = static_cast<float>(nib >= 8 ? nib - 16 : nib);
+      }
+    }
+  } else if (ENC == QLLM_KV_Q8) {
+    const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+    const uint8_t* r8 = layer + (is_value ? records * (hd + 2U) : 0U) + rec * (hd + 2U);
+    const float sc = __half2float(*reinterpret_cast<const __half*>(r8 + hd));
+    const uint16_t* pairs = reinterpret_cast<const uint16_t*>(r8 + d0);  // records are 2-byte aligned
+    for (uint32_t e = 0; e < dpp / 2U; ++e) {
+      const uint16_t two = pairs[e];
+      out[2U * e] = bf16r(static_cast<float>(static_cast<int8_t>(two & 0xffU)) * sc);
+      out[2U * e + 1U] = bf16r(static_cast<float>(static_cast<int8_t>(two >> 8U)) * sc);
+    }
+  } else {
+    const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
+    const uint4* r16 = reinterpret_cast<const uint4*>(layer + (is_value ? records * hd * 2U : 0U) + (rec * hd + d0) * 2U);
+    for (uint32_t w = 0; w < dpp / 8U; ++w) {
+      const uint4 q = r16[w];
+      const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (uint32_t i = 0; i < 4U; ++i) {
+        out[8U * w + 2U * i] = __half2float(__ushort_as_half(static_cast<unsigned short>(words[i] & 0xffffU)));
+        out[8U * w + 2U * i + 1U] = __half2float(__ushort_as_half(static_cast<unsigned short>(words[i] >> 16U)));
+      }
+    }
+  }
+}
+
 template <uint32_t ENC>
 __global__ void __launch_bounds__(256)
 attention_scalar_kernel(AttentionArgs a, Partials part) {
@@ -216,29 +269,7 @@ attention_scalar_kernel(AttentionArgs a, Partials part) {
   for (uint32_t t0 = first; t0 < last; t0 += 32U) {
     const uint32_t n = min(32U, last - t0);
     // ---- K tile
-    for (uint32_t item = tid; item < 32U * hd; item += 256U) {
-      const uint32_t j = item / hd, d = item % hd;
-      float value = 0.0F;
-      if (j < n) {
-        const uint32_t tok = t0 + j;
-        const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
-        if (ENC == QLLM_KV_Q4H) {
-          const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
-          const uint8_t byte = layer[rec * (hd / 2U) + d / 2U];
-          const int nib = (d & 1U) ? (byte >> 4) : (byte & 15);
-          value = static_cast<float>(nib >= 8 ? nib - 16 : nib);
-        } else if (ENC == QLLM_KV_Q8) {
-          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
-          const uint8_t* kr = layer + rec * (hd + 2U);
-          const float sc = __half2float(*reinterpret_cast<const __half*>(kr + hd));
-          value = bf16r(static_cast<float>(static_cast<int8_t>(kr[d])) * sc);
-        } else {
-          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
-          value = __half2float(reinterpret_cast<const __half*>(layer)[rec * hd + d]);
-        }
-      }
-      tile[j * (hd + 1U) + d] = value;
-    }
+    load_kv_tile<ENC>(a, kvh, t0, n, false, tile);
     if (ENC == QLLM_KV_Q4H && tid < 64U) {
       const uint32_t j = tid & 31U;
       float sc = 0.0F;
@@ -302,29 +333,7 @@ attention_scalar_kernel(AttentionArgs a, Partials part) {
     }
     __syncthreads();
     // ---- V tile (reuses the K buffer)
-    for (uint32_t item = tid; item < 32U * hd; item += 256U) {
-      const uint32_t j = item / hd, d = item % hd;
-      float value = 0.0F;
-      if (j < n) {
-        const uint32_t tok = t0 + j;
-        const uint8_t* layer = a.page_table[tok / pt] + a.layer_offset;
-        if (ENC == QLLM_KV_Q4H) {
-          const size_t rec = static_cast<size_t>(kvh) * pt + tok % pt;
-          const uint8_t byte = layer[records * (hd / 2U) + records * 2U + rec * (hd / 2U) + d / 2U];
-          const int nib = (d & 1U) ? (byte >> 4) : (byte & 15);
-          value = static_cast<float>(nib >= 8 ? nib - 16 : nib);
-        } else if (ENC == QLLM_KV_Q8) {
-          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
-          const uint8_t* vr = layer + records * (hd + 2U) + rec * (hd + 2U);
-          const float sc = __half2float(*reinterpret_cast<const __half*>(vr + hd));
-          value = bf16r(static_cast<float>(static_cast<int8_t>(vr[d])) * sc);
-        } else {
-          const size_t rec = static_cast<size_t>(tok % pt) * a.kv_heads + kvh;
-          value = __half2float(reinterpret_cast<const __half*>(layer + records * hd * 2U)[rec * hd + d]);
-        }
-      }
-      tile[j * (hd + 1U) + d] = value;
-    }
+    load_kv_tile<ENC>(a, kvh, t0, n, true, tile);
     __syncthreads();
     // ---- P.V, each thread owns outputs tid, tid+256, ...
 #pragma unroll
@@ -395,7 +404,7 @@ __global__ void attention_combine_kernel(AttentionArgs a, Partials part) {
 int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   const uint32_t group = a.kv_heads ? a.q_heads / a.kv_heads : 0U;
   const uint32_t MR = a.rows * group;
-  if (!a.rows || !group || a.q_heads % a.kv_heads || a.head_dim % 32U || a.head_dim > 256U ||
+  if (!a.rows || !group || a.q_heads % a.kv_heads || a.head_dim % 64U || a.head_dim > 256U ||
       a.split_tokens % 32U || !a.split_tokens || a.page_tokens % 32U || !a.max_splits || MR > 64U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported attention geometry");
   const Partials part = partials_of(a);

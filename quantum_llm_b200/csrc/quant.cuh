@@ -57,6 +57,45 @@ __device__ __forceinline__ void quant_store_block16(const QuantSink& q, uint32_t
   }
 }
 
+// Warp-cooperative form: four consecutive lanes hold one 16-value block as a float4 each
+// (lane & 3 = position inside the block).  All 32 lanes must call it; lanes with
+// valid == false take part in the shuffles only.
+__device__ __forceinline__ void quant_store_quad(const QuantSink& q, uint32_t row, uint32_t block, float4 v,
+                                                 bool valid) {
+  const uint32_t quad_lane = threadIdx.x & 3U;
+  float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, 2));
+  if (!valid) return;
+  const unsigned sc = e4m3_code(fminf(448.0F, q.g * amax / 6.0F));
+  const float local = e4m3_value(sc);
+  const float in[4] = {v.x, v.y, v.z, v.w};
+  unsigned code[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    code[i] = local == 0.0F ? 0U : e2m1_code(fminf(6.0F, fmaxf(-6.0F, in[i] * q.g / local)));
+  if (q.kind == 0) {
+    uint32_t packed = 0U;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const unsigned m = code[i] & 7U;
+      int twice = m < 5U ? static_cast<int>(m) : static_cast<int>(2U * m - 4U) + (m == 7U ? 2 : 0);
+      if (code[i] & 8U) twice = -twice;
+      packed |= (static_cast<uint32_t>(twice) & 0xffU) << (8 * i);
+    }
+    reinterpret_cast<uint32_t*>(q.xi8 + static_cast<size_t>(row) * q.cols)[block * 4U + quad_lane] = packed;
+    if (quad_lane == 0U) q.xscale[static_cast<size_t>(row) * (q.cols / 16U) + block] = local;
+  } else {
+    const uint16_t packed = static_cast<uint16_t>(code[0] | (code[1] << 4U) | (code[2] << 8U) | (code[3] << 12U));
+    reinterpret_cast<uint16_t*>(q.codes + static_cast<size_t>(row) * (q.cols / 2U))[block * 4U + quad_lane] = packed;
+    if (quad_lane == 0U) {
+      const uint32_t tile = row / 128U, r = row % 128U;
+      q.atoms[(static_cast<size_t>(tile) * (q.cols / 64U) + block / 4U) * 512U + (r % 32U) * 16U + (r / 32U) * 4U +
+              block % 4U] = static_cast<uint8_t>(sc);
+    }
+  }
+}
+
 // Result of a GEMV as its consumers see it: either final BF16-rounded values [batch, n], or
 // `split` raw FP32 partial sums [split][batch][n] that still need the output scale.
 struct GemvOut {
@@ -74,6 +113,21 @@ __device__ __forceinline__ float gemv_value(const GemvOut& o, uint32_t row, uint
   const size_t stride = static_cast<size_t>(o.batch) * o.n;
   for (uint32_t s = 0; s < o.split; ++s) sum += o.data[s * stride + i];
   return bf16r(sum * o.weight_scale / o.input_scale);
+}
+
+// Four consecutive outputs (col % 4 == 0, n % 4 == 0): 16-byte loads of every split.
+__device__ __forceinline__ float4 gemv_value4(const GemvOut& o, uint32_t row, uint32_t col) {
+  const size_t i = (static_cast<size_t>(row) * o.n + col) / 4U;
+  const float4* data = reinterpret_cast<const float4*>(o.data);
+  if (o.split == 0U) return data[i];
+  const size_t stride = static_cast<size_t>(o.batch) * o.n / 4U;
+  float4 sum = data[i];
+  for (uint32_t s = 1; s < o.split; ++s) {
+    const float4 t = data[s * stride + i];
+    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+  }
+  return make_float4(bf16r(sum.x * o.weight_scale / o.input_scale), bf16r(sum.y * o.weight_scale / o.input_scale),
+                     bf16r(sum.z * o.weight_scale / o.input_scale), bf16r(sum.w * o.weight_scale / o.input_scale));
 }
 
 }  // namespace qllm
