@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "fused.h"
 #include "gemv_mma.h"
+#include "launch.cuh"
 
 namespace qllm {
 
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                       const __grid_constant__ CUtensorMap act_map, GemvMmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  pdl_trigger();  // the consumer kernel may be scheduled; it waits for this grid to finish
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
@@ -344,19 +346,33 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
 
   if (tid == 0U) {
     // ---- producer: TMA loads of weight codes, weight scales, activation codes, activation scales
-    for (uint32_t i = 0; i < kcn; ++i) {
-      const uint32_t s = i % p.stages, round = i / p.stages;
-      if (round > 0U && !mbar_wait(&empty_bar[s], (round - 1U) & 1U, abort_flag)) break;
+    auto load_weights = [&](uint32_t i) {
+      const uint32_t s = i % p.stages, kc = kc0 + i;
       uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
-      const uint32_t kc = kc0 + i;
       mbar_expect_tx(&full_bar[s], kABytes + 2U * kSfBytes + b_bytes);
       tma_load_2d(st, &weight_map, &full_bar[s], kc * 128U, tile * kTileRows);
       bulk_load(st + kABytes, p.tiled_scales + (static_cast<size_t>(tile) * p.k_atoms + kc * 4U) * kAtomBytes,
                 kSfBytes, &full_bar[s]);
+    };
+    auto load_activations = [&](uint32_t i) {
+      const uint32_t s = i % p.stages, kc = kc0 + i;
+      uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
       tma_load_2d(st + kABytes + kSfBytes, &act_map, &full_bar[s], kc * 128U, n_tile * 128U);
       bulk_load(st + stage_bytes - kSfBytes,
                 p.act_atoms + (static_cast<size_t>(n_tile) * p.k_atoms + kc * 4U) * kAtomBytes, kSfBytes,
                 &full_bar[s]);
+    };
+    // the weights do not depend on the kernel before this one: the first stages start
+    // streaming while that kernel is still producing the activations
+    const uint32_t ahead = min(kcn, p.stages);
+    for (uint32_t i = 0; i < ahead; ++i) load_weights(i);
+    pdl_wait();
+    for (uint32_t i = 0; i < ahead; ++i) load_activations(i);
+    for (uint32_t i = ahead; i < kcn; ++i) {
+      const uint32_t s = i % p.stages, round = i / p.stages;
+      if (!mbar_wait(&empty_bar[s], (round - 1U) & 1U, abort_flag)) break;
+      load_weights(i);
+      load_activations(i);
     }
   } else if (tid == 32U) {
     // ---- tensor-core driver
@@ -530,9 +546,9 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.raw = raw ? 1U : 0U;
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
-  nvfp4_gemv_mma_kernel<<<dim3(row_tiles, split, n_tiles), 128, smem, stream>>>(w.codes_map, act_map, p);
   count_launch();
-  return check_launch("nvfp4_gemv_mma");
+  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+                               w.codes_map, act_map, p), "nvfp4_gemv_mma");
 }
 
 // ---- operand buffers and the implementation-neutral GEMV core ---------------------------

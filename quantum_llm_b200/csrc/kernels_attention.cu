@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "fused.h"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace qllm {
 
@@ -38,6 +39,7 @@ __device__ __forceinline__ float block_max_small(float v, float* scratch) {
 // partials) and the rotated queries are written to q_out [rows, q_heads*head_dim].
 __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, bool fused) {
   __shared__ float src[256];
+  pdl_wait();  // no early trigger: the attention kernel after this one is launched the ordinary way
   __shared__ float scratch[8];
   const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
   const uint32_t hd = a.head_dim;
@@ -133,9 +135,9 @@ int launch_rope_kv_store_fused(const RopeStoreFusedArgs& f, cudaStream_t stream)
   const RopeStoreArgs& a = f.base;
   if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U || !f.q_out)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
-  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a, f.qkv, f.q_out, true);
   count_launch();
-  return check_launch("rope_kv_store");
+  return check_cuda(launch_pdl(rope_kv_store_kernel, dim3(a.q_heads + a.kv_heads, a.rows), dim3(a.head_dim), 0, stream,
+                               a, f.qkv, f.q_out, true), "rope_kv_store");
 }
 
 // ------------------------------------------------------------------ partials

@@ -10,6 +10,7 @@
 // quantisation block.
 #include "common.cuh"
 #include "fused.h"
+#include "launch.cuh"
 
 namespace qllm {
 
@@ -23,6 +24,8 @@ constexpr uint32_t kNormVecs = 6;  // up to 512*6*4 = 12288 columns
 __global__ void __launch_bounds__(kNormThreads)
 residual_norm_quant_kernel(NormQuantArgs a) {
   __shared__ double partial[16];
+  pdl_trigger();
+  pdl_wait();
   const uint32_t out_row = blockIdx.x;
   const uint32_t in_row = a.row_select ? *a.row_select : out_row;
   const uint32_t n4 = a.cols / 4U;
@@ -78,15 +81,17 @@ int launch_residual_norm_quant(const NormQuantArgs& a, uint32_t rows, cudaStream
   if (!rows || !a.cols || a.cols % 16U || a.cols > kNormThreads * kNormVecs * 4U || a.x_stride % 4U ||
       a.store_stride % 4U || a.normalized_stride % 4U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported row length for the fused norm");
-  residual_norm_quant_kernel<<<rows, kNormThreads, 0, stream>>>(a);
   count_launch();
-  return check_launch("residual_norm_quant");
+  return check_cuda(launch_pdl(residual_norm_quant_kernel, dim3(rows), dim3(kNormThreads), 0, stream, a),
+                    "residual_norm_quant");
 }
 
 // ------------------------------------------------------------ SiLU product + quantise
 // One thread per 4 outputs: inter = act(act(silu(g)) * u), quantised for the down GEMV.
 __global__ void __launch_bounds__(256)
 silu_quant_kernel(GemvOut gate_up, uint32_t ffn, bool bf16, QuantSink sink, float* inter) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t n4 = ffn / 4U;
   const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
   const bool valid = item < gate_up.batch * n4;
@@ -108,9 +113,9 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
                       cudaStream_t stream) {
   if (ffn % 16U) return fail(QLLM_INVALID_ARGUMENT, "FFN width must be a multiple of 16");
   const uint32_t items = gate_up.batch * (ffn / 4U);
-  silu_quant_kernel<<<(items + 255U) / 256U, 256, 0, stream>>>(gate_up, ffn, bf16, sink, inter);
   count_launch();
-  return check_launch("silu_quant");
+  return check_cuda(launch_pdl(silu_quant_kernel, dim3((items + 255U) / 256U), dim3(256), 0, stream, gate_up, ffn,
+                               bf16, sink, inter), "silu_quant");
 }
 
 // ------------------------------------------------------------- split combine + quantise
@@ -119,60 +124,80 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
 // independent of the visiting order) and writes the o-projection operand.
 constexpr uint32_t kCombineSplits = 512;
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 combine_quant_kernel(CombineArgs c) {
-  __shared__ float weights[4][kCombineSplits];
+  // CTA = (row, query head), 8 warps: warp w merges the splits s = w (mod 8); a lane owns
+  // 4 (head_dim 128) or 8 (head_dim 256) output dims.
+  __shared__ float weights[kCombineSplits];
+  __shared__ double partial[8][4][64];
+  __shared__ float stats[2];
+  pdl_trigger();
+  pdl_wait();
   const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
-  const uint32_t head = blockIdx.x * 4U + warp, row = blockIdx.y, hd = c.head_dim;
-  if (head >= c.q_heads) return;  // whole warp
+  const uint32_t head = blockIdx.x, row = blockIdx.y, hd = c.head_dim;
   const uint32_t ctx = *c.first_position + c.position_offset + 1U + row;
   const uint32_t active = (ctx + c.split_tokens - 1U) / c.split_tokens;
   const size_t base = static_cast<size_t>(row) * c.max_splits * c.q_heads + head;
-  float m = kNegInf;
-  for (uint32_t s = lane; s < active; s += 32U) m = fmaxf(m, c.maxima[base + static_cast<size_t>(s) * c.q_heads]);
-  m = warp_max(m);
-  double sum = 0.0;
-  for (uint32_t s = lane; s < active; s += 32U) {
-    const size_t p = base + static_cast<size_t>(s) * c.q_heads;
-    const float w = expf(c.maxima[p] - m);
-    weights[warp][s] = w;
-    sum += static_cast<double>(c.sums[p] * w);
-  }
-  const float gsum = static_cast<float>(warp_sum_f64(sum));
-  __syncwarp();
-  for (uint32_t f = lane; f < ((hd / 4U + 31U) & ~31U); f += 32U) {  // warp-uniform trip count
-    const bool valid = f < hd / 4U;
-    float4 out = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-    if (valid) {
-      double r0 = 0.0, r1 = 0.0, r2 = 0.0, r3 = 0.0;
-#pragma unroll 4
-      for (uint32_t s = 0; s < active; ++s) {
-        const size_t p = base + static_cast<size_t>(s) * c.q_heads;
-        const float4 o = reinterpret_cast<const float4*>(c.outputs + p * hd)[f];
-        const float w = weights[warp][s];
-        r0 += static_cast<double>(o.x * w);
-        r1 += static_cast<double>(o.y * w);
-        r2 += static_cast<double>(o.z * w);
-        r3 += static_cast<double>(o.w * w);
-      }
-      out = make_float4(actv(static_cast<float>(r0) / gsum, c.bf16), actv(static_cast<float>(r1) / gsum, c.bf16),
-                        actv(static_cast<float>(r2) / gsum, c.bf16), actv(static_cast<float>(r3) / gsum, c.bf16));
-      if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(row) * c.q_heads + head) * hd)[f] = out;
+  if (warp == 0U) {
+    float m = kNegInf;
+    for (uint32_t s = lane; s < active; s += 32U) m = fmaxf(m, c.maxima[base + static_cast<size_t>(s) * c.q_heads]);
+    m = warp_max(m);
+    double sum = 0.0;
+    for (uint32_t s = lane; s < active; s += 32U) {
+      const size_t p = base + static_cast<size_t>(s) * c.q_heads;
+      const float w = expf(c.maxima[p] - m);
+      weights[s] = w;
+      sum += static_cast<double>(c.sums[p] * w);
     }
-    if (c.sink.kind >= 0) quant_store_quad(c.sink, row, (head * hd + 4U * f) / 16U, out, valid);
+    sum = warp_sum_f64(sum);
+    if (lane == 0U) stats[0] = static_cast<float>(sum);
   }
+  __syncthreads();
+  const uint32_t vecs = hd / 4U;  // float4s per head: 16, 32 or 64
+  for (uint32_t f = lane; f < vecs; f += 32U) {
+    double r0 = 0.0, r1 = 0.0, r2 = 0.0, r3 = 0.0;
+#pragma unroll 4
+    for (uint32_t s = warp; s < active; s += 8U) {
+      const size_t p = base + static_cast<size_t>(s) * c.q_heads;
+      const float4 o = reinterpret_cast<const float4*>(c.outputs + p * hd)[f];
+      const float w = weights[s];
+      r0 += static_cast<double>(o.x * w);
+      r1 += static_cast<double>(o.y * w);
+      r2 += static_cast<double>(o.z * w);
+      r3 += static_cast<double>(o.w * w);
+    }
+    partial[warp][0][f] = r0; partial[warp][1][f] = r1; partial[warp][2][f] = r2; partial[warp][3][f] = r3;
+  }
+  __syncthreads();
+  if (warp >= (vecs + 31U) / 32U) return;  // warps 0 (and 1 for head_dim 256) finish
+  const uint32_t f = warp * 32U + lane;
+  const bool valid = f < vecs;
+  float4 out = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+  if (valid) {
+    double r[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+      for (int w = 0; w < 8; ++w) r[e] += partial[w][e][f];
+    const float gsum = stats[0];
+    out = make_float4(actv(static_cast<float>(r[0]) / gsum, c.bf16), actv(static_cast<float>(r[1]) / gsum, c.bf16),
+                      actv(static_cast<float>(r[2]) / gsum, c.bf16), actv(static_cast<float>(r[3]) / gsum, c.bf16));
+    if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(row) * c.q_heads + head) * hd)[f] = out;
+  }
+  if (c.sink.kind >= 0) quant_store_quad(c.sink, row, (head * hd + 4U * f) / 16U, out, valid);
 }
 
 int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t stream) {
   if (c.max_splits > kCombineSplits || c.head_dim > 256U || c.head_dim % 16U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported split count or head_dim for the combine");
-  combine_quant_kernel<<<dim3((c.q_heads + 3U) / 4U, rows), 128, 0, stream>>>(c);
   count_launch();
-  return check_launch("combine_quant");
+  return check_cuda(launch_pdl(combine_quant_kernel, dim3(c.q_heads, rows), dim3(256), 0, stream, c), "combine_quant");
 }
 
 // --------------------------------------------------------- materialise a GEMV result
 __global__ void gemv_finalize_kernel(GemvOut o, float* y) {
+  pdl_trigger();
+  pdl_wait();
   const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const uint64_t count = static_cast<uint64_t>(o.batch) * o.n / 4U;
   if (i >= count) return;
@@ -185,9 +210,9 @@ int launch_gemv_finalize(const GemvOut& o, float* y, cudaStream_t stream) {
   if (o.split == 0U && o.data == y) return 0;
   if (o.n % 4U) return fail(QLLM_INVALID_ARGUMENT, "GEMV output width must be a multiple of 4");
   const uint64_t count = static_cast<uint64_t>(o.batch) * o.n / 4U;
-  gemv_finalize_kernel<<<static_cast<unsigned>((count + 255U) / 256U), 256, 0, stream>>>(o, y);
   count_launch();
-  return check_launch("gemv_finalize");
+  return check_cuda(launch_pdl(gemv_finalize_kernel, dim3(static_cast<unsigned>((count + 255U) / 256U)), dim3(256), 0,
+                               stream, o, y), "gemv_finalize");
 }
 
 }  // namespace qllm

@@ -35,6 +35,17 @@ int check_cuda(cudaError_t error, const char* what) {
   return fail(QLLM_INTERNAL, std::string(what) + ": " + cudaGetErrorString(error));
 }
 int check_launch(const char* what) { return check_cuda(cudaPeekAtLastError(), what); }
+namespace {
+int g_pdl = -1;
+}
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* env = std::getenv("QLLM_PDL");  // QLLM_PDL=0: ordinary launches only
+    g_pdl = (env && env[0] == '0') ? 0 : 1;
+  }
+  return g_pdl == 1;
+}
+void set_pdl_enabled(bool enabled) { g_pdl = enabled ? 1 : 0; }
 void count_launch(unsigned launches) { g_launches += launches; }
 unsigned long long launches_counted() { return g_launches; }
 
