@@ -34,7 +34,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "0")))
+    ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "1")))
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -57,6 +57,10 @@ struct RopeStoreFusedArgs {
   GemvOut qkv;
   float* q_out;
   RopeStoreArgs base;        // qkv pointer unused
+  // optional: INT8 copy of the rotated queries for the Q4H attention (scale = max(absmax/127,
+  // 2^-24) per head, code = rn(q/scale)): [rows, q_heads, head_dim] and [rows, q_heads]
+  int8_t* q8_out;
+  float* q8_scale;
 };
 int launch_rope_kv_store_fused(const RopeStoreFusedArgs& a, cudaStream_t stream);
 

@@ -73,6 +73,10 @@ struct AttentionArgs {
   int impl;                   // 0 scalar, 1 tensor-core (Q4H)
   uint32_t* error;            // optional device status word (set when a pipeline wait runs out)
   bool skip_combine;          // leave the per-split partials in the workspace (merged by the caller)
+  // optional (tensor-core Q4H path): queries already quantised to INT8 by the RoPE kernel,
+  // [rows, q_heads, head_dim] codes and [rows, q_heads] scales; null = quantise from `query`
+  const int8_t* query_q8;
+  const float* query_q8_scale;
 };
 int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
                                    uint32_t* error, cudaStream_t stream);

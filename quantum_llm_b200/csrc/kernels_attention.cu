@@ -37,7 +37,8 @@ __device__ __forceinline__ float block_max_small(float v, float* scratch) {
 // grid (q_heads + kv_heads, rows), block head_dim threads.
 // With `fused` the projections are read from the GEMV result `src` (final values or split-K
 // partials) and the rotated queries are written to q_out [rows, q_heads*head_dim].
-__global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, bool fused) {
+__global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, bool fused,
+                                     int8_t* q8_out, float* q8_scale) {
   __shared__ float src[256];
   pdl_wait();  // no early trigger: the attention kernel after this one is launched the ordinary way
   __shared__ float scratch[8];
@@ -60,7 +61,16 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_
   }
   result = actv(result, a.bf16);
   if (v) v[d] = result;
-  if (head < a.q_heads) return;
+  if (head < a.q_heads) {
+    if (q8_out) {  // uniform per block
+      const float qmax = block_max_small(fabsf(result), scratch);
+      const float qsc = fmaxf(qmax / 127.0F, 0x1p-24F);
+      const size_t item = static_cast<size_t>(row) * a.q_heads + head;
+      q8_out[item * hd + d] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(result / qsc))));
+      if (d == 0U) q8_scale[item] = qsc;
+    }
+    return;
+  }
 
   // K head: quantise and store the K record and the V record of the same kv head
   const uint32_t kvh = head - a.q_heads;
@@ -126,7 +136,8 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_
 int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream) {
   if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
-  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a, GemvOut{}, nullptr, false);
+  rope_kv_store_kernel<<<dim3(a.q_heads + a.kv_heads, a.rows), a.head_dim, 0, stream>>>(a, GemvOut{}, nullptr, false,
+                                                                                             nullptr, nullptr);
   count_launch();
   return check_launch("rope_kv_store");
 }
@@ -137,7 +148,7 @@ int launch_rope_kv_store_fused(const RopeStoreFusedArgs& f, cudaStream_t stream)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
   count_launch();
   return check_cuda(launch_pdl(rope_kv_store_kernel, dim3(a.q_heads + a.kv_heads, a.rows), dim3(a.head_dim), 0, stream,
-                               a, f.qkv, f.q_out, true), "rope_kv_store");
+                               a, f.qkv, f.q_out, true, f.q8_out, f.q8_scale), "rope_kv_store");
 }
 
 // ------------------------------------------------------------------ partials
@@ -421,9 +432,20 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   } else {
     const size_t smem = (static_cast<size_t>(MR) * a.head_dim + 32U * (a.head_dim + 1U) +
                          2U * MR * 33U + 5U * MR + 64U) * sizeof(float);
+    // The opt-in limit is a property of the function, not of a launch: it is only ever
+    // raised (to the largest geometry the kernel accepts), because launches captured into a
+    // graph earlier keep their own, possibly larger, shared-memory size.
+    constexpr size_t kLargest = (64U * 256U + 32U * 257U + 2U * 64U * 33U + 5U * 64U + 64U) * sizeof(float);
+    static bool configured[64][3] = {};  // per device, per instantiation
+    int device = 0;
+    cudaGetDevice(&device);
     auto set = [&](auto kernel) {
-      return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(smem));
+      bool& done = configured[device & 63][a.encoding == QLLM_KV_Q4H ? 0 : a.encoding == QLLM_KV_Q8 ? 1 : 2];
+      if (done) return cudaSuccess;
+      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kLargest));
+      done = e == cudaSuccess;
+      return e;
     };
     cudaError_t e;
     switch (a.encoding) {

@@ -136,7 +136,8 @@ struct qllm_provider {
   std::vector<size_t> layer_off;
   size_t page_bytes = 0;
   // workspaces (rows <= kMaxRows)
-  DeviceBuffer<float> hidden, mtp_hidden, qkv, logits, mtp_emb, draft_logits;
+  DeviceBuffer<float> hidden, mtp_hidden, qkv, logits, mtp_emb, draft_logits, q8_scale;
+  DeviceBuffer<int8_t> q8;  // INT8 copy of the rotated queries for the Q4H attention
   DeviceBuffer<float> partial_buf, gemv_out;   // tensor-core split-K partials / CUDA-core results
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
@@ -227,6 +228,8 @@ struct qllm_provider {
     hidden.alloc(static_cast<size_t>(R) * c.hidden, "hidden");
     mtp_hidden.alloc(static_cast<size_t>(R) * c.hidden, "draft residual stream");
     qkv.alloc(static_cast<size_t>(R) * qkv_w, "rotated queries");
+    q8.alloc(static_cast<size_t>(R) * c.q_heads * c.head_dim, "INT8 queries");
+    q8_scale.alloc(static_cast<size_t>(R) * c.q_heads, "INT8 query scales");
     logits.alloc(static_cast<size_t>(R) * c.vocab, "logits");
     const uint32_t widest = std::max(std::max(2U * c.hidden, c.ffn), c.q_heads * c.head_dim);
     quant_buf.alloc(quant_buffer_bytes(R, widest), "quantised GEMV operand");
@@ -314,6 +317,10 @@ struct qllm_provider {
     rs.base = RopeStoreArgs{nullptr, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
                             first_position, position_offset, rotary_offset, st.page_table, layer_offset,
                             c.page_tokens, enc, bf};
+    const bool tensor_attention = attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
+                                  rows * (c.q_heads / c.kv_heads) <= 32U;
+    rs.q8_out = tensor_attention ? q8.p : nullptr;
+    rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
     ok(launch_rope_kv_store_fused(rs, stream));
     const uint32_t qkv_w = c.q_heads * c.head_dim;  // rotated queries only
     AttentionArgs at{};
@@ -334,8 +341,9 @@ struct qllm_provider {
     at.bf16 = bf;
     at.workspace = attn_ws.p;
     at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
-    at.impl = (attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
-               rows * (c.q_heads / c.kv_heads) <= 32U) ? 1 : 0;
+    at.impl = tensor_attention ? 1 : 0;
+    at.query_q8 = rs.q8_out;
+    at.query_q8_scale = rs.q8_scale;
     at.error = kernel_error.p;
     at.skip_combine = true;
     ok(launch_attention(at, stream));
