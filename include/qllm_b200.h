@@ -219,6 +219,14 @@ void qllm_k_matrix_release(qllm_prepared_matrix* prepared);
 int qllm_k_nvfp4_gemv_prepared(const qllm_prepared_matrix* prepared, const float* x, float* y,
                                uint32_t batch, void* workspace, size_t workspace_bytes, int impl,
                                void* stream);
+/* The tensor-core GEMV kernel alone (nvfp4_gemv_batch_reuse_kernel's role,
+ * transformer_kernels.cu:1970-2002, without the activation quantiser and the split-K
+ * finalisation): re-runs it over the quantised operand that a qllm_k_nvfp4_gemv_prepared
+ * call (impl 1) with the same handle, batch and workspace left behind, leaving split-K
+ * partial sums in the workspace.  This is how the provider chains it between fused
+ * producer/consumer kernels, and what the benchmark times as the dominant kernel. */
+int qllm_k_nvfp4_gemv_prepared_core(const qllm_prepared_matrix* prepared, uint32_t batch,
+                                    void* workspace, size_t workspace_bytes, void* stream);
 /* Harness-owned weight quantiser on the device (formula of transformer_kernels.cu:1960-1967
  * applied to weight rows); w is fp32 [rows, cols]. */
 int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols,

@@ -107,6 +107,13 @@ int qllm_k_nvfp4_gemv_prepared(const qllm_prepared_matrix* p, const float* x, fl
   return launch_gemv_mma(p->mma, p->m, 0U, p->m.rows, x, y, batch, workspace, workspace_bytes, s);
 }
 
+int qllm_k_nvfp4_gemv_prepared_core(const qllm_prepared_matrix* p, uint32_t batch, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  if (!p || !workspace || !batch) return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 GEMV");
+  if (!p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+  return launch_gemv_mma_core_only(p->mma, p->m, batch, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int qllm_k_nvfp4_quantize_weights(const float* w, uint32_t rows, uint32_t cols, float global_scale,
                                   uint8_t* codes, uint8_t* scales, void* stream) {
   if (!w || !codes || !scales || !rows || !cols || cols % 16U || !(global_scale > 0.0F))

@@ -153,9 +153,10 @@ struct MmaWorkspace {
 static size_t align_up(size_t v, size_t a) { return (v + a - 1U) / a * a; }
 
 static uint32_t pick_split(uint32_t row_tiles, uint32_t n_tiles, uint32_t k_chunks) {
-  // fill two CTAs per SM, but keep at least 4 stages of work per CTA
-  const uint32_t want = (2U * 148U + row_tiles * n_tiles - 1U) / (row_tiles * n_tiles);
-  const uint32_t cap = std::max(1U, k_chunks / 4U);
+  // one wave of at most two CTAs per SM (a second, partial wave costs a whole CTA's time),
+  // with at least 3 k-chunks of work per CTA
+  const uint32_t want = (2U * 148U) / (row_tiles * n_tiles);
+  const uint32_t cap = std::max(1U, k_chunks / 3U);
   return std::max(1U, std::min(want, cap));
 }
 
@@ -496,6 +497,20 @@ int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_ro
     rc = check_launch("gemv_mma_finalize");
   }
   return rc;
+}
+
+// The tensor-core kernel alone, over the quantised operand that a launch_gemv_mma() call with
+// the same workspace, matrix and batch left behind; leaves split-K partials in the workspace.
+int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_t batch, void* workspace,
+                              size_t workspace_bytes, cudaStream_t stream) {
+  if (!w.ready || m.cols % kTileK || !batch || batch > 128U)
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, rows <= 128)");
+  const uint32_t row_tiles = (m.rows + kTileRows - 1U) / kTileRows;
+  const uint32_t split = pick_split(row_tiles, 1U, m.cols / kTileK);
+  size_t need = 0;
+  const MmaWorkspace ws = carve(workspace, batch, m.rows, m.cols, split, &need);
+  if (need > workspace_bytes) return fail(QLLM_INVALID_ARGUMENT, "tensor-core GEMV workspace is too small");
+  return mma_core(w, m, 0U, m.rows, batch, ws.codes, ws.atoms, ws.partials, nullptr, ws.error, true, nullptr, stream);
 }
 
 // Tensor-core GEMV over an operand that is already quantised (codes + atoms).  With `raw`

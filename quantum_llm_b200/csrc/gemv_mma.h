@@ -34,5 +34,9 @@ size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                     uint32_t row_count, const float* x, float* y, uint32_t batch, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream);
+// The tensor-core kernel alone over the operand a launch_gemv_mma() call with the same
+// workspace, matrix and batch left behind (split-K partials stay in the workspace).
+int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_t batch, void* workspace,
+                              size_t workspace_bytes, cudaStream_t stream);
 
 }  // namespace qllm

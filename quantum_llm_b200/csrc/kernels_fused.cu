@@ -12,32 +12,50 @@
 #include "fused.h"
 #include "launch.cuh"
 
+#include <cooperative_groups.h>
+
 namespace qllm {
 
 // ---------------------------------------------------- residual + norm + quantise
-// One CTA (512 threads) per row, the row lives in registers as float4s.
+// A cluster of four CTAs per row (the kernel sits on the critical path between two GEMVs and
+// is bound by its own latency, so the row is spread over four SMs); each CTA keeps its quarter
+// of the row in registers as float4s and the sums of squares meet in distributed shared memory.
 // x' = act(x + delta) (delta optional), optionally stored back; then
 // n = x' * rsqrt(mean x'^2 + eps) * w, optionally stored; then the NVFP4 operand of n.
-constexpr uint32_t kNormThreads = 512;
-constexpr uint32_t kNormVecs = 6;  // up to 512*6*4 = 12288 columns
+constexpr uint32_t kNormThreads = 320;
+constexpr uint32_t kNormVecs = 3;     // up to 4 * 320 * 3 * 4 = 15360 columns
+constexpr uint32_t kNormCluster = 4;
 
 __global__ void __launch_bounds__(kNormThreads)
 residual_norm_quant_kernel(NormQuantArgs a) {
-  __shared__ double partial[16];
+  namespace cg = cooperative_groups;
+  __shared__ double partial[kNormThreads / 32U];
+  __shared__ double cta_sum;
   pdl_trigger();
-  pdl_wait();
-  const uint32_t out_row = blockIdx.x;
-  const uint32_t in_row = a.row_select ? *a.row_select : out_row;
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t rank = cluster.block_rank();
+  const uint32_t out_row = blockIdx.x / kNormCluster;
   const uint32_t n4 = a.cols / 4U;
+  const uint32_t chunk = ((n4 + kNormCluster - 1U) / kNormCluster + 3U) & ~3U;  // whole 16-value blocks
+  const uint32_t begin = rank * chunk, end = min(n4, begin + chunk);
+  // the norm weights do not depend on the kernel before this one
+  float4 w[kNormVecs];
+#pragma unroll
+  for (uint32_t k = 0; k < kNormVecs; ++k) {
+    const uint32_t f = begin + threadIdx.x + k * kNormThreads;
+    w[k] = (a.weight && f < end) ? reinterpret_cast<const float4*>(a.weight)[f] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+  }
+  pdl_wait();
+  const uint32_t in_row = a.row_select ? *a.row_select : out_row;
   // x == null: the row is the GEMV result alone (0 + delta is exact)
   const float4* x4 = a.x ? reinterpret_cast<const float4*>(a.x + static_cast<size_t>(in_row) * a.x_stride) : nullptr;
   float4 v[kNormVecs];
   double sq = 0.0;
 #pragma unroll
   for (uint32_t k = 0; k < kNormVecs; ++k) {
-    const uint32_t f = threadIdx.x + k * kNormThreads;
+    const uint32_t f = begin + threadIdx.x + k * kNormThreads;
     v[k] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-    if (f < n4) {
+    if (f < end) {
       if (x4) v[k] = x4[f];
       if (a.has_delta) {
         const float4 d = gemv_value4(a.delta, in_row, 4U * f);
@@ -49,40 +67,43 @@ residual_norm_quant_kernel(NormQuantArgs a) {
             static_cast<double>(v[k].z) * v[k].z + static_cast<double>(v[k].w) * v[k].w;
     }
   }
-  if (!a.weight) return;  // residual update only
+  if (!a.weight) return;  // residual update only (uniform over the grid)
   sq = warp_sum_f64(sq);
   if ((threadIdx.x & 31U) == 0U) partial[threadIdx.x >> 5U] = sq;
   __syncthreads();
-  if (threadIdx.x < 32U) {
-    double t = threadIdx.x < (kNormThreads >> 5U) ? partial[threadIdx.x] : 0.0;
-    t = warp_sum_f64(t);
-    if (threadIdx.x == 0U) partial[0] = t;
+  if (threadIdx.x == 0U) {
+    double t = 0.0;
+    for (uint32_t i = 0; i < kNormThreads / 32U; ++i) t += partial[i];
+    cta_sum = t;
   }
-  __syncthreads();
-  const float inverse = 1.0F / sqrtf(static_cast<float>(partial[0]) / static_cast<float>(a.cols) + a.eps);
-  const float4* w4 = reinterpret_cast<const float4*>(a.weight);
+  cluster.sync();
+  double total = 0.0;
+  for (uint32_t r = 0; r < kNormCluster; ++r) total += *cluster.map_shared_rank(&cta_sum, r);
+  const float inverse = 1.0F / sqrtf(static_cast<float>(total) / static_cast<float>(a.cols) + a.eps);
 #pragma unroll
   for (uint32_t k = 0; k < kNormVecs; ++k) {
-    const uint32_t f = threadIdx.x + k * kNormThreads;
-    if (k * kNormThreads >= n4) break;  // uniform: no lane of the CTA has work left
-    const bool valid = f < n4;
+    const uint32_t f = begin + threadIdx.x + k * kNormThreads;
+    if (begin + k * kNormThreads >= end) break;  // uniform: no lane of the CTA has work left
+    const bool valid = f < end;
     float4 n = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
     if (valid) {
-      const float4 w = w4[f];
-      n = make_float4(v[k].x * inverse * w.x, v[k].y * inverse * w.y, v[k].z * inverse * w.z, v[k].w * inverse * w.w);
+      n = make_float4(v[k].x * inverse * w[k].x, v[k].y * inverse * w[k].y, v[k].z * inverse * w[k].z,
+                      v[k].w * inverse * w[k].w);
       if (a.normalized)
         reinterpret_cast<float4*>(a.normalized + static_cast<size_t>(out_row) * a.normalized_stride)[f] = n;
     }
     if (a.sink.kind >= 0) quant_store_quad(a.sink, out_row, a.sink_block_offset + f / 4U, n, valid);
   }
+  cluster.sync();  // no CTA leaves while a neighbour may still read its sum
 }
 
 int launch_residual_norm_quant(const NormQuantArgs& a, uint32_t rows, cudaStream_t stream) {
-  if (!rows || !a.cols || a.cols % 16U || a.cols > kNormThreads * kNormVecs * 4U || a.x_stride % 4U ||
+  if (!rows || !a.cols || a.cols % 16U || a.cols > kNormCluster * kNormThreads * kNormVecs * 4U || a.x_stride % 4U ||
       a.store_stride % 4U || a.normalized_stride % 4U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported row length for the fused norm");
   count_launch();
-  return check_cuda(launch_pdl(residual_norm_quant_kernel, dim3(rows), dim3(kNormThreads), 0, stream, a),
+  return check_cuda(launch_pdl_cluster(residual_norm_quant_kernel, dim3(rows * kNormCluster), dim3(kNormThreads),
+                                       kNormCluster, 0, stream, a),
                     "residual_norm_quant");
 }
 

@@ -87,6 +87,7 @@ SIGNATURES = {
     "qllm_k_matrix_prepare": (ci, [P(Matrix), vp, P(vp)]),
     "qllm_k_matrix_release": (None, [vp]),
     "qllm_k_nvfp4_gemv_prepared": (ci, [vp, vp, vp, u32, vp, sz, ci, vp]),
+    "qllm_k_nvfp4_gemv_prepared_core": (ci, [vp, u32, vp, sz, vp]),
     "qllm_k_nvfp4_quantize_weights": (ci, [vp, u32, u32, f32, vp, vp, vp]),
     "qllm_k_add": (ci, [vp, vp, u64, ci, vp]),
     "qllm_k_silu_product": (ci, [vp, vp, u32, u32, ci, vp]),
