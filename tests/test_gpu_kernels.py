@@ -182,7 +182,8 @@ def _filled_cache(enc, hd, kv, pt, tokens, rng, layers=1):
 @pytest.mark.parametrize("enc,impl,qh,kv,hd", [
     (ob.KV_Q4H, 0, 10, 2, 128), (ob.KV_Q4H, 1, 10, 2, 128), (ob.KV_Q4H, 1, 8, 8, 128),
     (ob.KV_Q4H, 0, 12, 2, 256),  # the reference's own smoke geometry: head_dim 256, group 6
-    (ob.KV_Q8, 0, 10, 2, 128), (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128)])
+    (ob.KV_Q8, 0, 10, 2, 128), (ob.KV_Q8, 1, 10, 2, 128), (ob.KV_Q8, 1, 40, 8, 128),
+    (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128)])
 @pytest.mark.parametrize("ctx,rows", [(8, 5), (300, 5), (1500, 5), (1027, 1), (64, 4)])
 def test_attention_matches_oracle(L, enc, impl, qh, kv, hd, ctx, rows):
     import torch
@@ -207,7 +208,11 @@ def test_attention_matches_oracle(L, enc, impl, qh, kv, hd, ctx, rows):
     assert np.isfinite(got).all()
     # outputs are BF16-rounded: equal up to one BF16 step (exp() differs in the last place
     # between the device and the host library); in practice almost all are identical
-    close = (bf16_ulps(got, want) <= 1) | (np.abs(got - want) < 2e-4)
+    # The tensor-core kernels take exp() from ex2.approx: a probability that sits on a BF16 (Q8)
+    # or INT8 (Q4H) rounding boundary can land on the other side, which moves an output
+    # dominated by that key by up to 2^-8 of |v|.  Bound: 1e-3 absolute, half of what the
+    # reference allows its own tensor-core kernels against its host check (2e-3).
+    close = (bf16_ulps(got, want) <= 1) | (np.abs(got - want) < (1e-3 if impl == 1 else 2e-4))
     assert close.all(), np.abs(got - want).max()
     assert (got != want).mean() < 0.02
 
