@@ -26,6 +26,10 @@ if ROOT not in sys.path:
 CONTEXT = 32768          # cached tokens when the timed region starts
 REAL_PREFILL = 40        # last prompt tokens run through the real prefill path
 METRIC = "decode_tok_per_s_mtp4_q4h_32k"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up GEMV launch (tcgen05 kernel,
+# 34816x5120, 5 rows), from the ncu capture summarised in
+# profiles/nvfp4_gemv_and_attention_kernels_4layer_case.md (100.39 MB read + 3.62 MB written)
+GATE_UP_DRAM_BYTES_NCU = 104.0e6
 
 
 def parse():
@@ -90,84 +94,104 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_baseline_sample(threads=None):
-    """Times the CPU oracle (a port of the reference's arithmetic) on a bounded sample of the
-    workload: the four NVFP4 GEMVs of ONE 27B-geometry layer at 5 rows plus the Q4H attention
-    of one layer over 2048 cached tokens, then scales by algorithmic bytes to a full step."""
-    import numpy as np
-    from oracle import binding as ob
-    threads = threads or os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
-    O = ob.lib()
-    rng = np.random.default_rng(0)
-    H, F, QH, KV, HD = 5120, 17408, 40, 8, 128
-    shapes = [((QH + 2 * KV) * HD, H), (H, QH * HD), (2 * F, H), (H, F)]
-    mats, sample_bytes = [], 0
-    for rows, cols in shapes:
-        codes = rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8)
-        scales = rng.integers(0x20, 0x48, (rows, cols // 16), dtype=np.uint8)
-        mats.append((ob.matrix(codes, scales, 1e-3, 336.0), codes, scales, rng.normal(0, 1, (5, cols)).astype(np.float32)))
-        sample_bytes += codes.size + scales.size
-    ctx, pt = 2048, 256
-    layer_bytes = O.qo_kv_layer_bytes(ob.KV_Q4H, pt, KV, HD)
-    pages = [rng.integers(0, 256, layer_bytes, dtype=np.uint8) for _ in range((ctx + 4 + pt - 1) // pt)]
-    table = (C.c_void_p * len(pages))(*[p.ctypes.data for p in pages])
-    k = rng.normal(0, 1, (ctx + 4, KV * HD)).astype(np.float32)
-    O.qo_kv_store(ob.KV_Q4H, table, 0, pt, KV, HD, ob._ptr(k), ob._ptr(k), ctx + 4, KV * HD, 0)
-    q = rng.normal(0, 1, (5, QH * HD)).astype(np.float32)
-    out = np.empty_like(q)
-    sample_bytes += (ctx + 4) * KV * (HD // 2 + 2) * 2
-    t0 = time.perf_counter()
-    for m, _, _, x in mats:
-        ob.gemv(m, x)
-    O.qo_attention(ob.KV_Q4H, table, 0, pt, ob._ptr(q), QH * HD, 5, ctx, QH, KV, HD, 512, 1, ob._ptr(out))
-    dt = time.perf_counter() - t0
-    return dt, sample_bytes, threads
+class CpuSample:
+    """A bounded sample of the workload for the CPU oracle (a port of the reference's
+    arithmetic): the four NVFP4 GEMVs of ONE 27B-geometry layer at 5 rows plus the Q4H
+    attention of one layer over 2048 cached tokens (186 MB of weights, 2.2 MB of KV records).
+    Built once; `time(seconds)` repeats passes over it and returns the mean seconds per pass,
+    which the caller scales by algorithmic bytes to a full step."""
+
+    def __init__(self, threads=None):
+        import numpy as np
+        from oracle import binding as ob
+        self.threads = threads or os.cpu_count() or 1
+        os.environ.setdefault("OMP_NUM_THREADS", str(self.threads))
+        self.ob, self.O = ob, ob.lib()
+        rng = np.random.default_rng(0)
+        H, F, QH, KV, HD = 5120, 17408, 40, 8, 128
+        self.geometry = (QH, KV, HD)
+        shapes = [((QH + 2 * KV) * HD, H), (H, QH * HD), (2 * F, H), (H, F)]
+        self.mats, self.bytes = [], 0
+        for rows, cols in shapes:
+            codes = rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8)
+            scales = rng.integers(0x20, 0x48, (rows, cols // 16), dtype=np.uint8)
+            self.mats.append((ob.matrix(codes, scales, 1e-3, 336.0), codes, scales,
+                              rng.normal(0, 1, (5, cols)).astype(np.float32)))
+            self.bytes += codes.size + scales.size
+        self.ctx, self.pt = 2048, 256
+        layer_bytes = self.O.qo_kv_layer_bytes(ob.KV_Q4H, self.pt, KV, HD)
+        self.pages = [rng.integers(0, 256, layer_bytes, dtype=np.uint8)
+                      for _ in range((self.ctx + 4 + self.pt - 1) // self.pt)]
+        self.table = (C.c_void_p * len(self.pages))(*[p.ctypes.data for p in self.pages])
+        k = rng.normal(0, 1, (self.ctx + 4, KV * HD)).astype(np.float32)
+        self.O.qo_kv_store(ob.KV_Q4H, self.table, 0, self.pt, KV, HD, ob._ptr(k), ob._ptr(k), self.ctx + 4, KV * HD, 0)
+        self.q = rng.normal(0, 1, (5, QH * HD)).astype(np.float32)
+        self.out = np.empty_like(self.q)
+        self.bytes += (self.ctx + 4) * KV * (HD // 2 + 2) * 2
+        self.description = ("one 27B-geometry layer (4 NVFP4 GEMVs at 5 rows, 186 MB of weights) + Q4H attention "
+                            "over 2048 cached tokens, scaled by algorithmic bytes to a full step")
+
+    def one_pass(self):
+        QH, KV, HD = self.geometry
+        for m, _, _, x in self.mats:
+            self.ob.gemv(m, x)
+        self.O.qo_attention(self.ob.KV_Q4H, self.table, 0, self.pt, self.ob._ptr(self.q), QH * HD, 5, self.ctx,
+                            QH, KV, HD, 512, 1, self.ob._ptr(self.out))
+
+    def time(self, seconds):
+        passes, t0 = 0, time.perf_counter()
+        while True:
+            self.one_pass()
+            passes += 1
+            elapsed = time.perf_counter() - t0
+            if elapsed >= seconds:
+                return elapsed / passes, passes, elapsed
 
 
-def timed_cpu_baseline(min_seconds=12.0):
-    reps, total, info = 0, 0.0, None
-    while total < min_seconds and reps < 12:
-        dt, sample_bytes, threads = cpu_baseline_sample()
-        total += dt
-        reps += 1
-        info = (sample_bytes, threads)
-    return total / reps, info[0], info[1], reps
+def algorithmic_step_bytes(cfg, context):
+    """Bytes one MTP-4 step must read: verify weights + target KV + 4 draft passes."""
+    nv = lambda r, c: r * c * 9 // 16   # NVFP4: 4-bit codes + one E4M3 scale per 16
+    per_layer = (nv((cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"], cfg["hidden"]) +
+                 nv(cfg["hidden"], cfg["q_heads"] * cfg["head_dim"]) + nv(2 * cfg["ffn"], cfg["hidden"]) +
+                 nv(cfg["hidden"], cfg["ffn"]))
+    head = nv(cfg["vocab"], cfg["hidden"])
+    kv = 2 * (cfg["head_dim"] // 2 + 2) * cfg["kv_heads"] * cfg["layers"] * context
+    draft = per_layer + nv(cfg["hidden"], 2 * cfg["hidden"]) + nv(cfg["draft_vocab"], cfg["hidden"]) \
+        + 2 * (cfg["head_dim"] + 2) * cfg["kv_heads"] * context
+    return per_layer * cfg["layers"] + head + kv + 4 * draft
+
+
+def workload_name(context):
+    return ("27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936), 1 stream/GPU, "
+            f"{context} cached tokens, Q4H target KV + Q8 draft KV, MTP-4, greedy")
 
 
 def reference_arm(args):
-    """Reference arm: the reference's host-side arithmetic for this path, timed on the
-    host cores.  The reference's provider itself needs a CUDA device and a compiled model
-    artifact, so its CPU implementation of the path is the oracle port (kind "port")."""
+    """Reference arm: the reference's arithmetic for this path on the host cores.  The
+    reference's provider itself needs a CUDA device and a compiled model artifact, so its CPU
+    implementation of the path is the oracle port (kind "port").  One step = repeated passes
+    over the bounded sample for about 3 s, scaled by algorithmic bytes to a full step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from quantum_llm_b200.synthetic import DENSE_27B
-    cfg = DENSE_27B
-    # algorithmic bytes of a full step without touching a GPU
-    per_layer = sum(r * c * 9 // 16 for r, c in [((cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"], cfg["hidden"]),
-                                                  (cfg["hidden"], cfg["q_heads"] * cfg["head_dim"]),
-                                                  (2 * cfg["ffn"], cfg["hidden"]), (cfg["hidden"], cfg["ffn"])])
-    head = cfg["vocab"] * cfg["hidden"] * 9 // 16
-    kv = 2 * (cfg["head_dim"] // 2 + 2) * cfg["kv_heads"] * cfg["layers"] * args.context
-    draft = per_layer + 2 * cfg["hidden"] * cfg["hidden"] * 9 // 16 + cfg["draft_vocab"] * cfg["hidden"] * 9 // 16 \
-        + 2 * (cfg["head_dim"] + 2) * cfg["kv_heads"] * args.context
-    step_bytes = per_layer * cfg["layers"] + head + kv + 4 * draft
-    times = []
+    step_bytes = algorithmic_step_bytes(DENSE_27B, args.context)
+    sample = CpuSample()
+    per_pass, passes = [], 0
     for i in range(args.warmup + args.steps):
-        dt, sample_bytes, threads = cpu_baseline_sample()
+        seconds, n, _ = sample.time(3.0 if i >= args.warmup else 1.0)
         if i >= args.warmup:
-            times.append(dt)
-    dt = sum(times) / len(times)
-    step_s = dt * step_bytes / sample_bytes
+            per_pass.append(seconds)
+            passes += n
+    step_s = (sum(per_pass) / len(per_pass)) * step_bytes / sample.bytes
     value = 1.0 / step_s   # accepted length 1.0 on random-init weights: one token per step
-    sample = ("one 27B-geometry layer (4 NVFP4 GEMVs, 5 rows) + Q4H attention over 2048 tokens, "
-              "scaled by algorithmic bytes to a full step")
+    text = f"{sample.description}; {passes} timed passes on {sample.threads} threads"
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
-            "config": {"workload": "27B dense, 1 stream, 32768 ctx, Q4H KV, MTP-4 (CPU port of the reference arithmetic)"},
-            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "config": {"workload": workload_name(args.context), "layers": DENSE_27B["layers"],
+                       "parallelism": "host cores of rank 0", "implementation": "CPU port of the reference arithmetic"},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.threads, "kind": "port", "sample": text},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -341,8 +365,7 @@ def ours(args):
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
-        "config": {"workload": "27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936), 1 stream/GPU, "
-                               f"{context} cached tokens, Q4H target KV + Q8 draft KV, MTP-4, greedy",
+        "config": {"workload": workload_name(context),
                    "layers": cfg["layers"], "parallelism": f"dp{world} replicas",
                    "l2_policy": "inputs larger than L2 (16 GB streamed per step)",
                    "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",
@@ -353,18 +376,19 @@ def ours(args):
         "step_algorithmic_gb": step_bytes / 1e9, "step_gbs": step_gbs, "step_frac_of_hbm": step_gbs / hbm_peak,
         "roofline": {"bound": "hbm", "kernel": "nvfp4_gemv gate_up 34816x5120 M=5", "achieved": achieved,
                      "peak": hbm_peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "kernel_ms": kernel_ms},
+                     "traffic": GATE_UP_DRAM_BYTES_NCU if args.gemv_impl == 1 else None,
+                     "algorithmic_bytes": kernel_bytes, "kernel_ms": kernel_ms},
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 56,
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": clocks.summary(),
     }
-    if not args.no_cpu_baseline and world >= 1:
-        dt, sample_bytes, threads, reps = timed_cpu_baseline()
-        cpu_step = dt * step_bytes / sample_bytes
-        line["cpu_baseline"] = {"value": 1.0 / cpu_step, "unit": "tok/s", "cores": threads, "kind": "port",
-                                "sample": f"one layer's 4 NVFP4 GEMVs at 5 rows + Q4H attention over 2048 tokens "
-                                          f"({reps} repetitions, {dt:.2f} s each), scaled by algorithmic bytes to a step"}
+    if not args.no_cpu_baseline:
+        sample = CpuSample()
+        per_pass, passes, elapsed = sample.time(12.0)
+        cpu_step = per_pass * step_bytes / sample.bytes
+        line["cpu_baseline"] = {"value": 1.0 / cpu_step, "unit": "tok/s", "cores": sample.threads, "kind": "port",
+                                "sample": f"{sample.description}; {passes} passes in {elapsed:.1f} s"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
