@@ -208,6 +208,19 @@ size_t qllm_k_nvfp4_gemv_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t
 int qllm_k_nvfp4_gemv(const qllm_matrix* matrix, uint32_t first_row, uint32_t row_count,
                       const float* x, float* y, uint32_t batch, void* workspace,
                       size_t workspace_bytes, int impl, void* stream);
+/* No counterpart in the reference.  qllm_k_nvfp4_gemv (CUDA-core implementation, impl 0)
+ * for callers that cannot hand over a device workspace at call time and must not reach the
+ * CUDA allocator: a runtime that gave all device memory to its own pool at start-up, or a
+ * thread holding a lock under which cudaMalloc/cudaFree (which synchronise the device) would
+ * stall other streams.  The quantised activations live in a fixed array inside the library
+ * (qllm_k_nvfp4_gemv_static_scratch_bytes() bytes, 2 MiB: batch * cols * 1.25 must fit,
+ * otherwise QLLM_INVALID_ARGUMENT).  The array is shared by all calls on a device: calls on
+ * one stream are ordered, calls that overlap in time on different streams or threads race.
+ * Nothing in it needs to start at zero.  The first call on a device looks up the array's
+ * address; issue it once during start-up, before any stream capture on that device. */
+size_t qllm_k_nvfp4_gemv_static_scratch_bytes(void);
+int qllm_k_nvfp4_gemv_static(const qllm_matrix* matrix, uint32_t first_row, uint32_t row_count,
+                             const float* x, float* y, uint32_t batch, void* stream);
 /* Load-time preparation of one matrix (the provider does this once per tensor when it binds
  * the weights, cf. ensure_tensor, dense_fp4_provider.cpp:3486-3677): builds the TMA descriptor
  * and the re-tiled block scales the tensor-core GEMV reads.  The matrix memory must outlive

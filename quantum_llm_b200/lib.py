@@ -84,6 +84,8 @@ SIGNATURES = {
     "qllm_k_nvfp4_fake_quant": (ci, [vp, vp, u32, u32, f32, vp]),
     "qllm_k_nvfp4_gemv_workspace_bytes": (sz, [u32, u32, u32]),
     "qllm_k_nvfp4_gemv": (ci, [P(Matrix), u32, u32, vp, vp, u32, vp, sz, ci, vp]),
+    "qllm_k_nvfp4_gemv_static_scratch_bytes": (sz, []),
+    "qllm_k_nvfp4_gemv_static": (ci, [P(Matrix), u32, u32, vp, vp, u32, vp]),
     "qllm_k_matrix_prepare": (ci, [P(Matrix), vp, P(vp)]),
     "qllm_k_matrix_release": (None, [vp]),
     "qllm_k_nvfp4_gemv_prepared": (ci, [vp, vp, vp, u32, vp, sz, ci, vp]),
