@@ -196,6 +196,19 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def reduce_over_ranks(times_ms, counts, device):
+    """Whole-job figures of a replica run: the slowest rank's device times (MAX) and the
+    units all ranks processed (SUM).  A single process returns its own numbers."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(times_ms, dtype=torch.float64, device=device)
+    c = torch.tensor(counts, dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(c, op=dist.ReduceOp.SUM)
+    return [float(x) for x in t.cpu()], [float(x) for x in c.cpu()]
+
+
 def gemv_kernel_leg(model, provider, gemv_impl, rows=5, repeats=3):
     """Average duration of the dominant kernel (gate/up NVFP4 GEMV, 34816x5120, 5 rows) over
     all layers' weights back to back (6.4 GB, far beyond L2), timed with CUDA events on the
@@ -268,7 +281,7 @@ def ours(args):
         cfg["layers"] = 4
     context = args.context
     cfg["max_context"] = context + 1024
-    steps_total = args.warmup + 2 * args.steps + 8
+    steps_total = args.warmup + 2 * args.steps + 32
     assert context + 5 * steps_total + 16 < cfg["max_context"], "too many steps for the context reserve"
     model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
     provider = model.provider()
@@ -334,14 +347,27 @@ def ours(args):
     stop.synchronize()
     barrier()
     ms_e2e = start.elapsed_time(stop)
+    # ---- the same step with temperature rejection sampling (T 0.7, top-p 0.95, top-k 20):
+    # exact top-k of the 5 logits rows, device-side acceptance/residual sampling
+    sampled = RequestParameters(sampling_seed=1 + rank, sampling_temperature_ppm=700000, sampling_top_p_ppm=950000,
+                                sampling_top_k=20, sampling_min_p_ppm=0, reserved_context_tokens=cfg["max_context"])
+    sampled_steps = min(16, args.steps)
+    tokens_c = 0
+    for timed in (False, True):   # the first round captures the sampled step's graph
+        barrier()
+        start.record(stream)
+        for _ in range(sampled_steps if timed else 3):
+            r = provider.execute_exact_decode(state, sampled, token, position, cfg["max_context"])
+            tokens_c += r.positions_advanced if timed else 0
+            position += r.positions_advanced
+            token = r.next_token
+        stop.record(stream)
+        stop.synchronize()
+    barrier()
+    ms_sampled = start.elapsed_time(stop)
 
-    stats = torch.tensor([ms_value, ms_e2e], dtype=torch.float64, device=f"cuda:{local}")
-    totals = torch.tensor([tokens_a, tokens_b, accepted_a], dtype=torch.float64, device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
-    ms_value, ms_e2e = (float(x) for x in stats.cpu())
-    tokens_a, tokens_b, accepted_a = (float(x) for x in totals.cpu())
+    (ms_value, ms_e2e, ms_sampled), (tokens_a, tokens_b, accepted_a, tokens_c) = reduce_over_ranks(
+        [ms_value, ms_e2e, ms_sampled], [tokens_a, tokens_b, accepted_a, tokens_c], f"cuda:{local}")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -380,6 +406,8 @@ def ours(args):
                      "algorithmic_bytes": kernel_bytes, "kernel_ms": kernel_ms},
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 56,
                 "ms_per_step": ms_e2e / args.steps},
+        "sampled_t0.7_top_p0.95_top_k20": {"value": tokens_c / (ms_sampled * 1e-3), "unit": "tok/s",
+                                           "ms_per_step": ms_sampled / sampled_steps, "steps": sampled_steps},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": clocks.summary(),
     }
