@@ -104,9 +104,10 @@ class CpuSample:
     def __init__(self, threads=None):
         import numpy as np
         from oracle import binding as ob
-        self.threads = threads or os.cpu_count() or 1
-        os.environ.setdefault("OMP_NUM_THREADS", str(self.threads))
         self.ob, self.O = ob, ob.lib()
+        # explicit: launchers such as torchrun export OMP_NUM_THREADS=1
+        self.O.qo_set_threads(threads or len(os.sched_getaffinity(0)) or 1)
+        self.threads = int(self.O.qo_max_threads())
         rng = np.random.default_rng(0)
         H, F, QH, KV, HD = 5120, 17408, 40, 8, 128
         self.geometry = (QH, KV, HD)

@@ -96,7 +96,7 @@ def lib():
             "qo_kv_layer_bytes": (sz, [u32, u32, u32, u32]),
             "qo_kv_store": (None, [u32, vp, sz, u32, u32, u32, vp, vp, u32, u32, u32]),
             "qo_attention": (None, [u32, vp, sz, u32, vp, u32, u32, u32, u32, u32, u32, u32, C.c_int, vp]),
-            "qo_argmax": (u32, [vp, u32]), "qo_topk": (None, [vp, u32, u32, vp, vp]),
+            "qo_argmax": (u32, [vp, u32]), "qo_set_threads": (None, [u32]), "qo_max_threads": (u32, []), "qo_topk": (None, [vp, u32, u32, vp, vp]),
             "qo_counter_uniform": (f64, [u64, u32, u32, u32]),
             "qo_make_distribution": (C.c_int, [vp, vp, u32, u32, u32, u32, vp, vp]),
             "qo_sample_distribution": (u32, [vp, vp, u32, f64]),

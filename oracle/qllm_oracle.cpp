@@ -11,6 +11,8 @@
 #include <string>
 #include <vector>
 
+#include <omp.h>
+
 namespace {
 
 thread_local std::string g_error;
@@ -873,6 +875,9 @@ void qo_attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset
             split_tokens, bf16 != 0, out);
 }
 uint32_t qo_argmax(const float* v, uint32_t count) { return argmax(v, count); }
+// Host threads the parallel loops (GEMV rows, attention heads) use; for the timed baseline.
+void qo_set_threads(uint32_t threads) { omp_set_num_threads(threads ? static_cast<int>(threads) : 1); }
+uint32_t qo_max_threads(void) { return static_cast<uint32_t>(omp_get_max_threads()); }
 void qo_topk(const float* v, uint32_t count, uint32_t k, float* ov, uint32_t* ot) {
   topk(v, count, k, ov, ot);
 }

@@ -141,6 +141,9 @@ void qo_attention(uint32_t encoding, const uint8_t* const* pages,
                   uint32_t kv_heads, uint32_t head_dim, uint32_t split_tokens,
                   int act_bf16, float* out);
 uint32_t qo_argmax(const float* values, uint32_t count);
+/* thread count of the OpenMP loops (timed CPU baseline) */
+void qo_set_threads(uint32_t threads);
+uint32_t qo_max_threads(void);
 void qo_topk(const float* values, uint32_t count, uint32_t k, float* out_values,
              uint32_t* out_tokens);
 
