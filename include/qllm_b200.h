@@ -170,6 +170,9 @@ void* qllm_provider_stream(qllm_provider* provider);
 int qllm_provider_set_graph_mode(qllm_provider* provider, int enabled);
 /* GEMV implementation: 0 = CUDA-core kernel, 1 = tcgen05 block-scaled MMA kernel. */
 int qllm_provider_set_gemv_impl(qllm_provider* provider, int impl);
+/* Attention implementation: 1 (default) = tensor-core kernels where the geometry allows
+ * (Q4H and Q8 caches, head_dim 128), 0 = the order-independent scalar kernel everywhere. */
+int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
 
 /* inspection for parity tests (device -> host copies) */
 int qllm_provider_read_logits(qllm_provider* provider, float* out, uint32_t rows);

@@ -40,7 +40,8 @@ __device__ __forceinline__ float block_max_small(float v, float* scratch) {
 __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, bool fused,
                                      int8_t* q8_out, float* q8_scale) {
   __shared__ float src[256];
-  pdl_wait();  // no early trigger: the attention kernel after this one is launched the ordinary way
+  pdl_trigger();  // the attention kernel may be scheduled; it waits for this grid before reading
+  pdl_wait();
   __shared__ float scratch[8];
   const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
   const uint32_t hd = a.head_dim;
@@ -133,6 +134,122 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_
   }
 }
 
+// head_dim 128, fused form: one warp per (head, row), a lane owns 4 consecutive dims, every
+// reduction is a warp shuffle (no shared memory, no block barrier) and the rotation partner
+// d +- rotary_dim/2 lives in another lane at the same element index.  Same arithmetic as
+// rope_kv_store_kernel.  grid = ceil(heads*rows / 4), block = 128 (4 warps).
+__global__ void __launch_bounds__(128)
+rope_kv_store_warp128_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, int8_t* q8_out, float* q8_scale) {
+  pdl_trigger();  // the attention kernel may be scheduled; it waits for this grid before reading
+  pdl_wait();
+  constexpr uint32_t hd = 128;
+  const uint32_t lane = threadIdx.x & 31U;
+  const uint32_t item = blockIdx.x * 4U + (threadIdx.x >> 5U);
+  const uint32_t heads = a.q_heads + a.kv_heads;
+  if (item >= heads * a.rows) return;
+  const uint32_t head = item % heads, row = item / heads;
+  const uint32_t cache_position = *a.first_position + a.position_offset + row;
+  const uint32_t rotary_position = cache_position + a.rotary_offset;
+  const uint32_t d0 = 4U * lane, half = a.rotary_dim / 2U;
+  const float4 s4 = gemv_value4(src_out, row, head * hd + d0);
+  const float src[4] = {actv(s4.x, a.bf16), actv(s4.y, a.bf16), actv(s4.z, a.bf16), actv(s4.w, a.bf16)};
+  const bool rotated = d0 < a.rotary_dim;      // rotary_dim % 8 == 0: a lane is inside or outside
+  const bool low = d0 < half;
+  const uint32_t partner = rotated ? (low ? lane + half / 4U : lane - half / 4U) : lane;
+  float result[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float other_raw = __shfl_sync(0xffffffffU, src[i], partner);
+    result[i] = src[i];
+    if (rotated) {
+      const uint32_t pair = (d0 + i) % half;
+      const float angle = static_cast<float>(rotary_position) * a.inv_freq[pair];
+      const float other = low ? -other_raw : other_raw;
+      result[i] = src[i] * actv(cosf(angle), a.bf16) + other * actv(sinf(angle), a.bf16);
+    }
+    result[i] = actv(result[i], a.bf16);
+  }
+  if (head < a.q_heads) {
+    const size_t item_q = static_cast<size_t>(row) * a.q_heads + head;
+    *reinterpret_cast<float4*>(q_out + item_q * hd + d0) = make_float4(result[0], result[1], result[2], result[3]);
+    if (q8_out) {
+      const float qmax = warp_max(fmaxf(fmaxf(fabsf(result[0]), fabsf(result[1])), fmaxf(fabsf(result[2]), fabsf(result[3]))));
+      const float qsc = fmaxf(qmax / 127.0F, 0x1p-24F);
+      uint32_t packed = 0U;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        packed |= (static_cast<uint32_t>(max(-127, min(127, __float2int_rn(result[i] / qsc)))) & 0xffU) << (8 * i);
+      *reinterpret_cast<uint32_t*>(q8_out + item_q * hd + d0) = packed;
+      if (lane == 0U) q8_scale[item_q] = qsc;
+    }
+    return;
+  }
+  // K head: quantise and store the K record and the V record of the same kv head
+  const uint32_t kvh = head - a.q_heads;
+  const float4 v4 = gemv_value4(src_out, row, (a.q_heads + a.kv_heads + kvh) * hd + d0);
+  const float value[4] = {v4.x, v4.y, v4.z, v4.w};
+  const uint32_t pt = a.page_tokens;
+  uint8_t* layer = a.page_table[cache_position / pt] + a.layer_offset;
+  const size_t records = static_cast<size_t>(pt) * a.kv_heads;
+  const uint32_t slot = cache_position % pt;
+  if (a.encoding == QLLM_KV_F16) {
+    const size_t rec = static_cast<size_t>(slot) * a.kv_heads + kvh;
+    __half* kdst = reinterpret_cast<__half*>(layer) + rec * hd + d0;
+    __half* vdst = reinterpret_cast<__half*>(layer + records * hd * 2U) + rec * hd + d0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { kdst[i] = __float2half_rn(result[i]); vdst[i] = __float2half_rn(value[i]); }
+    return;
+  }
+  const float kmax = warp_max(fmaxf(fmaxf(fabsf(result[0]), fabsf(result[1])), fmaxf(fabsf(result[2]), fabsf(result[3]))));
+  const float vmax = warp_max(fmaxf(fmaxf(fabsf(value[0]), fabsf(value[1])), fmaxf(fabsf(value[2]), fabsf(value[3]))));
+  if (a.encoding == QLLM_KV_Q4H) {
+    const __half ksh = __float2half_rn(fmaxf(kmax / 7.0F, 0x1p-24F));
+    const __half vsh = __float2half_rn(fmaxf(vmax / 7.0F, 0x1p-24F));
+    const float ks = __half2float(ksh), vs = __half2float(vsh);
+    uint8_t* kc = layer;
+    uint8_t* ksc = kc + records * (hd / 2U);
+    uint8_t* vc = ksc + records * 2U;
+    uint8_t* vsc = vc + records * (hd / 2U);
+    const size_t rec = static_cast<size_t>(kvh) * pt + slot;
+    if (lane == 0U) {
+      reinterpret_cast<__half*>(ksc)[rec] = ksh;
+      reinterpret_cast<__half*>(vsc)[rec] = vsh;
+    }
+    uint32_t kb = 0U, vb = 0U;  // two bytes each: dims (d0, d0+1) and (d0+2, d0+3)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int kq = max(-7, min(7, __float2int_rn(result[i] / ks)));
+      const int vq = max(-7, min(7, __float2int_rn(value[i] / vs)));
+      kb |= (static_cast<uint32_t>(kq) & 15U) << (4 * i);
+      vb |= (static_cast<uint32_t>(vq) & 15U) << (4 * i);
+    }
+    reinterpret_cast<uint16_t*>(kc + rec * (hd / 2U))[lane] = static_cast<uint16_t>(kb);
+    reinterpret_cast<uint16_t*>(vc + rec * (hd / 2U))[lane] = static_cast<uint16_t>(vb);
+  } else {  // Q8: records are 2-byte aligned
+    const __half ksh = __float2half_rn(fmaxf(kmax / 127.0F, 0x1p-24F));
+    const __half vsh = __float2half_rn(fmaxf(vmax / 127.0F, 0x1p-24F));
+    const float ks = __half2float(ksh), vs = __half2float(vsh);
+    const size_t rb = hd + 2U;
+    const size_t rec = static_cast<size_t>(slot) * a.kv_heads + kvh;
+    uint8_t* kr = layer + rec * rb;
+    uint8_t* vr = layer + records * rb + rec * rb;
+    if (lane == 0U) {
+      *reinterpret_cast<__half*>(kr + hd) = ksh;
+      *reinterpret_cast<__half*>(vr + hd) = vsh;
+    }
+    uint32_t kb = 0U, vb = 0U;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      kb |= (static_cast<uint32_t>(max(-127, min(127, __float2int_rn(result[i] / ks)))) & 0xffU) << (8 * i);
+      vb |= (static_cast<uint32_t>(max(-127, min(127, __float2int_rn(value[i] / vs)))) & 0xffU) << (8 * i);
+    }
+    reinterpret_cast<uint16_t*>(kr)[2U * lane] = static_cast<uint16_t>(kb & 0xffffU);
+    reinterpret_cast<uint16_t*>(kr)[2U * lane + 1U] = static_cast<uint16_t>(kb >> 16U);
+    reinterpret_cast<uint16_t*>(vr)[2U * lane] = static_cast<uint16_t>(vb & 0xffffU);
+    reinterpret_cast<uint16_t*>(vr)[2U * lane + 1U] = static_cast<uint16_t>(vb >> 16U);
+  }
+}
+
 int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream) {
   if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
@@ -147,6 +264,11 @@ int launch_rope_kv_store_fused(const RopeStoreFusedArgs& f, cudaStream_t stream)
   if (a.head_dim > 256U || a.head_dim % 32U || a.rotary_dim > a.head_dim || a.rotary_dim % 2U || !f.q_out)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported head geometry for RoPE/KV store");
   count_launch();
+  if (a.head_dim == 128U && a.rotary_dim % 8U == 0U && f.qkv.n % 4U == 0U) {
+    const uint32_t items = (a.q_heads + a.kv_heads) * a.rows;
+    return check_cuda(launch_pdl(rope_kv_store_warp128_kernel, dim3((items + 3U) / 4U), dim3(128), 0, stream, a, f.qkv,
+                                 f.q_out, f.q8_out, f.q8_scale), "rope_kv_store");
+  }
   return check_cuda(launch_pdl(rope_kv_store_kernel, dim3(a.q_heads + a.kv_heads, a.rows), dim3(a.head_dim), 0, stream,
                                a, f.qkv, f.q_out, true, f.q8_out, f.q8_scale), "rope_kv_store");
 }
@@ -228,6 +350,8 @@ template <uint32_t ENC>
 __global__ void __launch_bounds__(256)
 attention_scalar_kernel(AttentionArgs a, Partials part) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const uint32_t hd = a.head_dim, group = a.q_heads / a.kv_heads;
   const uint32_t MR = a.rows * group;
   float* qs = smem;
@@ -458,15 +582,15 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
     switch (a.encoding) {
       case QLLM_KV_Q4H:
         e = set(attention_scalar_kernel<QLLM_KV_Q4H>);
-        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_Q4H><<<grid, 256, smem, stream>>>(a, part);
+        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_Q4H>, grid, dim3(256), smem, stream, a, part);
         break;
       case QLLM_KV_Q8:
         e = set(attention_scalar_kernel<QLLM_KV_Q8>);
-        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_Q8><<<grid, 256, smem, stream>>>(a, part);
+        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_Q8>, grid, dim3(256), smem, stream, a, part);
         break;
       case QLLM_KV_F16:
         e = set(attention_scalar_kernel<QLLM_KV_F16>);
-        if (e == cudaSuccess) attention_scalar_kernel<QLLM_KV_F16><<<grid, 256, smem, stream>>>(a, part);
+        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_F16>, grid, dim3(256), smem, stream, a, part);
         break;
       default:
         return fail(QLLM_INVALID_ARGUMENT, "unknown KV encoding");

@@ -20,6 +20,7 @@
 // queries taken ready-made from the RoPE kernel when the caller provides them.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace qllm {
 
@@ -229,6 +230,8 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
   __shared__ float qscale_s[32];
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
   __shared__ uint32_t abort_word;
+  pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
+  pdl_wait();     // queries and the newest records come from the RoPE kernel before this one
   const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
   const uint32_t g = lane >> 2U, t = lane & 3U;
   const uint32_t kvh = blockIdx.x, split = blockIdx.y;
@@ -421,8 +424,10 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
 int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
                                    uint32_t* error, cudaStream_t stream) {
   Q4hPartials part{maxima, sums, outputs};
-  attention_q4h_pipelined_kernel<<<dim3(a.kv_heads, a.max_splits), 64, 0, stream>>>(a, part, error);
-  return check_launch("attention_q4h");
+  // Ordinary stream order on purpose: started early, the thousand CTAs of this grid (and, behind
+  // them, those of the next GEMVs) sit on the SMs waiting; measured 0.5 ms per step slower.
+  return check_cuda(launch_ordered(attention_q4h_pipelined_kernel, dim3(a.kv_heads, a.max_splits), dim3(64), 0, stream,
+                                   a, part, error), "attention_q4h");
 }
 
 }  // namespace qllm

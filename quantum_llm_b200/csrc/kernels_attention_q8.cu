@@ -15,6 +15,7 @@
 // conflicts because consecutive tokens are 260 words apart).
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 #include <cuda_bf16.h>
 
@@ -86,6 +87,8 @@ attention_q8_mma_kernel(AttentionArgs a, Q8Partials part, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
   __shared__ uint32_t abort_word;
+  pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
+  pdl_wait();     // queries and the newest records come from the RoPE kernel before this one
   const uint32_t tid = threadIdx.x, kvh = tid >> 5U, lane = tid & 31U;
   const uint32_t g = lane >> 2U, t = lane & 3U;
   const uint32_t split = blockIdx.x, mtile = blockIdx.y;
@@ -319,8 +322,8 @@ int launch_attention_q8_mma(const AttentionArgs& a, float* maxima, float* sums, 
     if (e != cudaSuccess) return check_cuda(e, "Q8 attention shared memory opt-in");
     configured[device & 63] = true;
   }
-  attention_q8_mma_kernel<<<dim3(a.max_splits, mtiles), 32U * a.kv_heads, smem, stream>>>(a, part, error);
-  return check_launch("attention_q8_mma");
+  return check_cuda(launch_ordered(attention_q8_mma_kernel, dim3(a.max_splits, mtiles), dim3(32U * a.kv_heads), smem,
+                                   stream, a, part, error), "attention_q8_mma");
 }
 
 }  // namespace qllm

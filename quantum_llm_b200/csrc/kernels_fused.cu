@@ -149,9 +149,11 @@ __global__ void __launch_bounds__(256)
 combine_quant_kernel(CombineArgs c) {
   // CTA = (row, query head), 8 warps: warp w merges the splits s = w (mod 8); a lane owns
   // 4 (head_dim 128) or 8 (head_dim 256) output dims.
-  __shared__ float weights[kCombineSplits];
+  // Every load is issued before anything is reduced, so the kernel costs one memory round
+  // trip and one barrier: each warp finds the global maximum itself (the maxima of all
+  // splits are a few hundred floats) while the partial outputs of its own splits are in flight.
   __shared__ double partial[8][4][64];
-  __shared__ float stats[2];
+  __shared__ double sums[8];
   pdl_trigger();
   pdl_wait();
   const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
@@ -159,36 +161,60 @@ combine_quant_kernel(CombineArgs c) {
   const uint32_t ctx = *c.first_position + c.position_offset + 1U + row;
   const uint32_t active = (ctx + c.split_tokens - 1U) / c.split_tokens;
   const size_t base = static_cast<size_t>(row) * c.max_splits * c.q_heads + head;
-  if (warp == 0U) {
-    float m = kNegInf;
-    for (uint32_t s = lane; s < active; s += 32U) m = fmaxf(m, c.maxima[base + static_cast<size_t>(s) * c.q_heads]);
-    m = warp_max(m);
-    double sum = 0.0;
-    for (uint32_t s = lane; s < active; s += 32U) {
-      const size_t p = base + static_cast<size_t>(s) * c.q_heads;
-      const float w = expf(c.maxima[p] - m);
-      weights[s] = w;
-      sum += static_cast<double>(c.sums[p] * w);
-    }
-    sum = warp_sum_f64(sum);
-    if (lane == 0U) stats[0] = static_cast<float>(sum);
-  }
-  __syncthreads();
   const uint32_t vecs = hd / 4U;  // float4s per head: 16, 32 or 64
-  for (uint32_t f = lane; f < vecs; f += 32U) {
-    double r0 = 0.0, r1 = 0.0, r2 = 0.0, r3 = 0.0;
-#pragma unroll 4
-    for (uint32_t s = warp; s < active; s += 8U) {
-      const size_t p = base + static_cast<size_t>(s) * c.q_heads;
-      const float4 o = reinterpret_cast<const float4*>(c.outputs + p * hd)[f];
-      const float w = weights[s];
-      r0 += static_cast<double>(o.x * w);
-      r1 += static_cast<double>(o.y * w);
-      r2 += static_cast<double>(o.z * w);
-      r3 += static_cast<double>(o.w * w);
-    }
-    partial[warp][0][f] = r0; partial[warp][1][f] = r1; partial[warp][2][f] = r2; partial[warp][3][f] = r3;
+  constexpr uint32_t kBatch = 8;  // splits of this warp held in registers at a time
+  float mine[kCombineSplits / 32U];  // maxima of the splits lane, lane+32, ...
+  float m = kNegInf;
+#pragma unroll
+  for (uint32_t i = 0; i < kCombineSplits / 32U; ++i) {
+    const uint32_t s = lane + 32U * i;
+    mine[i] = s < active ? c.maxima[base + static_cast<size_t>(s) * c.q_heads] : kNegInf;
   }
+  double r[2][4] = {{0.0, 0.0, 0.0, 0.0}, {0.0, 0.0, 0.0, 0.0}};
+  double sum = 0.0;
+  bool have_max = false;
+  for (uint32_t s0 = warp; s0 < active; s0 += 8U * kBatch) {
+    float4 o[kBatch][2];
+    float ssum[kBatch], smax[kBatch];
+#pragma unroll
+    for (uint32_t b = 0; b < kBatch; ++b) {
+      const uint32_t s = s0 + 8U * b;
+      const size_t p = base + static_cast<size_t>(min(s, active - 1U)) * c.q_heads;
+      const float4* src = reinterpret_cast<const float4*>(c.outputs + p * hd);
+      o[b][0] = lane < vecs ? src[lane] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+      o[b][1] = lane + 32U < vecs ? src[lane + 32U] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+      ssum[b] = c.sums[p];
+      smax[b] = c.maxima[p];
+    }
+    if (!have_max) {
+#pragma unroll
+      for (uint32_t i = 0; i < kCombineSplits / 32U; ++i) m = fmaxf(m, mine[i]);
+      m = warp_max(m);
+      have_max = true;
+    }
+#pragma unroll
+    for (uint32_t b = 0; b < kBatch; ++b) {
+      if (s0 + 8U * b >= active) break;
+      const float w = expf(smax[b] - m);
+      sum += static_cast<double>(ssum[b] * w);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        r[h][0] += static_cast<double>(o[b][h].x * w);
+        r[h][1] += static_cast<double>(o[b][h].y * w);
+        r[h][2] += static_cast<double>(o[b][h].z * w);
+        r[h][3] += static_cast<double>(o[b][h].w * w);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t f = lane + 32U * h;
+    if (f < vecs) {
+      partial[warp][0][f] = r[h][0]; partial[warp][1][f] = r[h][1];
+      partial[warp][2][f] = r[h][2]; partial[warp][3][f] = r[h][3];
+    }
+  }
+  if (lane == 0U) sums[warp] = sum;
   __syncthreads();
   if (warp >= (vecs + 31U) / 32U) return;  // warps 0 (and 1 for head_dim 256) finish
   const uint32_t f = warp * 32U + lane;
@@ -200,7 +226,10 @@ combine_quant_kernel(CombineArgs c) {
     for (int e = 0; e < 4; ++e)
 #pragma unroll
       for (int w = 0; w < 8; ++w) r[e] += partial[w][e][f];
-    const float gsum = stats[0];
+    double total = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += sums[w];
+    const float gsum = static_cast<float>(total);
     out = make_float4(actv(static_cast<float>(r[0]) / gsum, c.bf16), actv(static_cast<float>(r[1]) / gsum, c.bf16),
                       actv(static_cast<float>(r[2]) / gsum, c.bf16), actv(static_cast<float>(r[3]) / gsum, c.bf16));
     if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(row) * c.q_heads + head) * hd)[f] = out;

@@ -43,6 +43,19 @@ cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
   return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
+// Ordinary stream order (the kernel starts after everything before it has finished) for a
+// kernel that contains the dependency instructions.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ordered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                        Args&&... args) {

@@ -696,7 +696,7 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
   const uint32_t ring_start = st->ring_cursor;
   if (p->graph_mode) {
     if (!st->step_graph || st->graph_splits != splits || st->graph_sampled != static_cast<int>(sampled) ||
-        st->graph_gemv != p->gemv_impl) {
+        st->graph_gemv != p->gemv_impl + 2 * p->attention_impl) {
       if (st->step_graph) { cudaGraphExecDestroy(st->step_graph); st->step_graph = nullptr; }
       cudaGraph_t graph = nullptr;
       cu(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeThreadLocal), "begin step capture");
@@ -713,7 +713,7 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
       cu(e, "instantiate step graph");
       st->graph_splits = splits;
       st->graph_sampled = sampled;
-      st->graph_gemv = p->gemv_impl;
+      st->graph_gemv = p->gemv_impl + 2 * p->attention_impl;  // kernel selection baked into the graph
     }
     for (uint32_t i = 0; i < steps; ++i) cu(cudaGraphLaunch(st->step_graph, p->stream), "launch step graph");
   } else {
@@ -807,6 +807,12 @@ int qllm_provider_set_graph_mode(qllm_provider* p, int enabled) {
 int qllm_provider_set_gemv_impl(qllm_provider* p, int impl) {
   if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
   p->gemv_impl = impl;
+  return QLLM_OK;
+}
+
+int qllm_provider_set_attention_impl(qllm_provider* p, int impl) {
+  if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown attention implementation");
+  p->attention_impl = impl;
   return QLLM_OK;
 }
 

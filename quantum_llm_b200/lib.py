@@ -72,6 +72,7 @@ SIGNATURES = {
     "qllm_provider_stream": (vp, [vp]),
     "qllm_provider_set_graph_mode": (ci, [vp, ci]),
     "qllm_provider_set_gemv_impl": (ci, [vp, ci]),
+    "qllm_provider_set_attention_impl": (ci, [vp, ci]),
     "qllm_provider_read_logits": (ci, [vp, vp, u32]),
     "qllm_provider_read_hidden": (ci, [vp, vp, ci, vp, u32]),
     "qllm_provider_read_drafts": (ci, [vp, vp, vp, P(u32)]),

@@ -158,6 +158,9 @@ class Nvfp4MtpProvider:
     def set_graph_mode(self, enabled):
         _l.check(self.L.qllm_provider_set_graph_mode(self.h, int(enabled)))
 
+    def set_attention_impl(self, impl):
+        _l.check(self.L.qllm_provider_set_attention_impl(self.h, int(impl)))
+
     def set_gemv_impl(self, impl):
         _l.check(self.L.qllm_provider_set_gemv_impl(self.h, int(impl)))
 

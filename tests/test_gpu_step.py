@@ -14,13 +14,14 @@ pytestmark = pytest.mark.gpu
 LOGIT_MAX_ABS, LOGIT_REL_RMS = 2e-2, 1e-3   # the stated F16-KV parity tolerance
 
 
-def run_gpu(model, prompt, temperature, generate, graph=False, gemv_impl=0, seed=1234):
+def run_gpu(model, prompt, temperature, generate, graph=False, gemv_impl=0, seed=1234, attention_impl=1):
     """Decode `generate` tokens on the CUDA provider.  Returns the token stream (first token
     onwards), {position: logits row whose inputs are emitted tokens}, and the provider."""
     prq, _ = request_pair(seed=seed, temperature_ppm=temperature, context_limit=model.cfg["max_context"])
     p = provider_from_synth(model)
     p.set_graph_mode(graph)
     p.set_gemv_impl(gemv_impl)
+    p.set_attention_impl(attention_impl)
     st = p.create_request_state()
     first = p.prefill(st, prq, prompt, chunk_rows=5)
     drafts = [int(t) for t in p.read_drafts(st)]
@@ -111,6 +112,38 @@ def test_tiny_greedy_with_tensor_core_gemv():
     c = compare(gpu, cpu, len(prompt))
     print("tensor-core greedy parity", c)
     assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
+
+
+# The tiny geometry with head_dim 128 and a Q4H target cache: the shapes the warp-per-head
+# RoPE/KV-store kernel and the tensor-core attention kernels (INT8 MMA over Q4H for the target
+# layers, BF16 MMA over Q8 for the draft layer) are written for.
+WIDE = dict(synth.TINY, head_dim=128, rotary_dim=128, kv_encoding=ob.KV_Q4H)
+
+
+@pytest.mark.parametrize("attention_impl", [0, 1])
+def test_head_dim_128_q4h_cache(attention_impl):
+    model = synth.SynthModel(WIDE, seed=2)
+    prompt = synth.prompt(4096, 128, 2)
+    gpu = run_gpu(model, prompt, 0, 32, graph=True, attention_impl=attention_impl)
+    cpu = run_cpu(model, prompt, 0, 32)
+    c = compare(gpu, cpu, len(prompt))
+    print("head_dim 128 parity, attention_impl", attention_impl, c)
+    p, st, o = gpu["provider"], gpu["state"], cpu["oracle"]
+    # layer 0 of the prompt pages: RoPE + Q4H store see identical inputs -> identical bytes
+    for page in range(2):
+        g, want = p.read_page(st, page), o.page(page)
+        lo, hi = o.layer_offset(0), o.layer_offset(1)
+        assert np.array_equal(g[lo:hi], want[lo:hi])
+    assert gpu["stream"][0] == cpu["stream"][0]
+    if attention_impl == 0:
+        # scalar attention: order-independent arithmetic end to end -> the same bits
+        assert c["prefix"] == 33 and c["exact"] == c["shared"] and gpu["drafts"] == cpu["drafts"]
+        for page in range(2):   # every layer, including the Q8 records of the draft layer
+            want = o.page(page)
+            assert np.array_equal(p.read_page(st, page)[:want.size], want)
+    else:
+        # tensor-core attention: exp() from ex2.approx, FP32 accumulation -> stated tolerance
+        assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
 
 
 def test_greedy_stream_equals_plain_target_decoding_on_gpu():
