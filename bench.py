@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "1")))
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
     ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--split-tokens", type=int, default=0,
+                    help="cached tokens per attention CTA (multiple of 64; 0 = the model configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
@@ -282,6 +284,8 @@ def ours(args):
         cfg["layers"] = 4
     context = args.context
     cfg["max_context"] = context + 1024
+    if args.split_tokens:
+        cfg["split_tokens"] = args.split_tokens
     steps_total = args.warmup + 2 * args.steps + 32
     assert context + 5 * steps_total + 16 < cfg["max_context"], "too many steps for the context reserve"
     model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")

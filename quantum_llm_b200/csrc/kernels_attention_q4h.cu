@@ -226,8 +226,11 @@ struct Q4hPartials {
 __global__ void __launch_bounds__(64)
 attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* error) {
   __shared__ __align__(128) uint8_t ring[kStages][kStageBytes];
-  __shared__ __align__(16) int8_t qs[32][HD + 16];
-  __shared__ float qscale_s[32];
+  // staging of in-kernel quantised queries (callers without ready-made INT8 queries): lives in
+  // the last pipeline stage, which is not filled before the queries are in registers
+  int8_t (*qs)[HD + 16] = reinterpret_cast<int8_t (*)[HD + 16]>(&ring[kStages - 1U][0]);
+  float* qscale_s = reinterpret_cast<float*>(&ring[kStages - 1U][32U * (HD + 16U)]);
+  static_assert(32U * (HD + 16U) + 32U * sizeof(float) <= kStageBytes, "query staging must fit one stage");
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
   __shared__ uint32_t abort_word;
   pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
@@ -321,6 +324,8 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
     }
     qscale_lo = qscale_s[row_lo];
     qscale_hi = qscale_s[row_hi];
+    __syncthreads();  // the staging area is about to be reused as a pipeline stage ...
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // ... written by bulk copies
   }
 
   // producer state (thread 0) -------------------------------------------------------------
