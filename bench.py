@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "1")))
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
     ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--kv-encoding", default="q4h", choices=["q4h", "f16"],
+                    help="target KV cache: Q4H (the headline metric) or exact F16 (metric ..._f16kv_32k)")
     ap.add_argument("--split-tokens", type=int, default=0,
                     help="cached tokens per attention CTA (multiple of 64; 0 = the model configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -164,9 +166,9 @@ def algorithmic_step_bytes(cfg, context):
     return per_layer * cfg["layers"] + head + kv + 4 * draft
 
 
-def workload_name(context):
+def workload_name(context, kv="q4h"):
     return ("27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936), 1 stream/GPU, "
-            f"{context} cached tokens, Q4H target KV + Q8 draft KV, MTP-4, greedy")
+            f"{context} cached tokens, {'exact F16' if kv == 'f16' else 'Q4H'} target KV + Q8 draft KV, MTP-4, greedy")
 
 
 def reference_arm(args):
@@ -286,6 +288,9 @@ def ours(args):
     cfg["max_context"] = context + 1024
     if args.split_tokens:
         cfg["split_tokens"] = args.split_tokens
+    if args.kv_encoding == "f16":   # exact-F16 target cache (262144 B/token instead of 67584)
+        from quantum_llm_b200 import lib as _ql
+        cfg["kv_encoding"] = _ql.KV_F16
     steps_total = args.warmup + 2 * args.steps + 32
     assert context + 5 * steps_total + 16 < cfg["max_context"], "too many steps for the context reserve"
     model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
@@ -393,10 +398,11 @@ def ours(args):
     value = tokens_a / (ms_value * 1e-3)
     e2e = tokens_b / (ms_e2e * 1e-3)
     line = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if args.kv_encoding == "q4h" else METRIC.replace("q4h", "f16kv"), "value": value,
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
-        "config": {"workload": workload_name(context),
+        "config": {"workload": workload_name(context, args.kv_encoding),
                    "layers": cfg["layers"], "parallelism": f"dp{world} replicas",
                    "l2_policy": "inputs larger than L2 (16 GB streamed per step)",
                    "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",

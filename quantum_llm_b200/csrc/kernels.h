@@ -84,6 +84,10 @@ int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float*
 bool attention_q8_mma_supported(const AttentionArgs& a);
 int launch_attention_q8_mma(const AttentionArgs& a, float* maxima, float* sums, float* outputs, uint32_t* error,
                             cudaStream_t stream);
+// F16 tensor-core kernel over the exact-F16 cache (head_dim 128).
+bool attention_f16_mma_supported(const AttentionArgs& a);
+int launch_attention_f16_mma(const AttentionArgs& a, float* maxima, float* sums, float* outputs, uint32_t* error,
+                             cudaStream_t stream);
 size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                                  uint32_t max_splits);
 int launch_attention(const AttentionArgs& a, cudaStream_t stream);

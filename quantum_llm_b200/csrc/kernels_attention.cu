@@ -546,7 +546,13 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
     return fail(QLLM_INVALID_ARGUMENT, "unsupported attention geometry");
   const Partials part = partials_of(a);
   const dim3 grid(a.kv_heads, a.max_splits);
-  if (a.impl == 1 && a.encoding == QLLM_KV_Q8) {
+  if (a.impl == 1 && a.encoding == QLLM_KV_F16) {
+    if (!attention_f16_mma_supported(a))
+      return fail(QLLM_INVALID_ARGUMENT,
+                  "tensor-core F16 attention needs head_dim 128, rows*group <= 32, 32-token aligned pages and splits");
+    const int rc = launch_attention_f16_mma(a, part.maxima, part.sums, part.outputs, a.error, stream);
+    if (rc) return rc;
+  } else if (a.impl == 1 && a.encoding == QLLM_KV_Q8) {
     if (!attention_q8_mma_supported(a))
       return fail(QLLM_INVALID_ARGUMENT,
                   "tensor-core Q8 attention needs head_dim 128, at most 8 kv heads, rows*group <= 32, "

@@ -343,6 +343,7 @@ struct qllm_provider {
     at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
     at.impl = tensor_attention ? 1 : 0;
     if (attention_impl == 1 && enc == QLLM_KV_Q8 && attention_q8_mma_supported(at)) at.impl = 1;
+    if (attention_impl == 1 && enc == QLLM_KV_F16 && attention_f16_mma_supported(at)) at.impl = 1;
     at.query_q8 = rs.q8_out;
     at.query_q8_scale = rs.q8_scale;
     at.error = kernel_error.p;

@@ -183,7 +183,7 @@ def _filled_cache(enc, hd, kv, pt, tokens, rng, layers=1):
     (ob.KV_Q4H, 0, 10, 2, 128), (ob.KV_Q4H, 1, 10, 2, 128), (ob.KV_Q4H, 1, 8, 8, 128),
     (ob.KV_Q4H, 0, 12, 2, 256),  # the reference's own smoke geometry: head_dim 256, group 6
     (ob.KV_Q8, 0, 10, 2, 128), (ob.KV_Q8, 1, 10, 2, 128), (ob.KV_Q8, 1, 40, 8, 128),
-    (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128)])
+    (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128), (ob.KV_F16, 1, 10, 2, 128), (ob.KV_F16, 1, 40, 8, 128)])
 @pytest.mark.parametrize("ctx,rows", [(8, 5), (300, 5), (1500, 5), (1027, 1), (64, 4)])
 def test_attention_matches_oracle(L, enc, impl, qh, kv, hd, ctx, rows):
     import torch

@@ -121,15 +121,16 @@ WIDE = dict(synth.TINY, head_dim=128, rotary_dim=128, kv_encoding=ob.KV_Q4H)
 
 
 @pytest.mark.parametrize("attention_impl", [0, 1])
-def test_head_dim_128_q4h_cache(attention_impl):
-    model = synth.SynthModel(WIDE, seed=2)
+@pytest.mark.parametrize("kv_encoding", [ob.KV_Q4H, ob.KV_F16])
+def test_head_dim_128_caches(kv_encoding, attention_impl):
+    model = synth.SynthModel(dict(WIDE, kv_encoding=kv_encoding), seed=2)
     prompt = synth.prompt(4096, 128, 2)
     gpu = run_gpu(model, prompt, 0, 32, graph=True, attention_impl=attention_impl)
     cpu = run_cpu(model, prompt, 0, 32)
     c = compare(gpu, cpu, len(prompt))
     print("head_dim 128 parity, attention_impl", attention_impl, c)
     p, st, o = gpu["provider"], gpu["state"], cpu["oracle"]
-    # layer 0 of the prompt pages: RoPE + Q4H store see identical inputs -> identical bytes
+    # layer 0 of the prompt pages: RoPE + KV store see identical inputs -> identical bytes
     for page in range(2):
         g, want = p.read_page(st, page), o.page(page)
         lo, hi = o.layer_offset(0), o.layer_offset(1)
