@@ -58,6 +58,14 @@ typedef struct qllm_block {
   const float* post_norm;
   qllm_matrix gate_up; /* [2*ffn, hidden] gate rows then up rows */
   qllm_matrix down;    /* [hidden, ffn] */
+  /* Routed mixture of experts in place of the dense FFN when config.experts != 0
+   * (NVFP4 branch of run_router / run_routed_moe, dense_fp4_provider.cpp:8128-8166, 8207-8248;
+   * expert arithmetic runtime/src/cuda/moe_kernels.cu:171-264, 430-510, 633-690, 759-790).
+   * The arrays are host arrays of `experts` descriptors. */
+  qllm_matrix router;              /* [experts, hidden] */
+  const qllm_matrix* expert_gate;  /* each [expert_ffn, hidden] */
+  const qllm_matrix* expert_up;    /* each [expert_ffn, hidden] */
+  const qllm_matrix* expert_down;  /* each [hidden, expert_ffn] */
 } qllm_block;
 
 /* Geometry the artifact declares (runtime/tools/dense_fp4_provider.cpp:804-960). */
@@ -73,6 +81,10 @@ typedef struct qllm_config {
   uint32_t draft_depth;
   uint32_t max_context;
   uint32_t split_tokens;
+  uint32_t experts;     /* 0 = dense FFN */
+  uint32_t route_width; /* experts selected per token (<= 8) */
+  uint32_t expert_ffn;  /* intermediate width of one expert */
+  float route_scale;    /* routed scaling factor (route_scale_f32_bits) */
 } qllm_config;
 
 /* Tensor roles of the exact-decode program (dense_fp4_provider.cpp:4733-4786). */
@@ -278,6 +290,11 @@ int qllm_k_attention(uint32_t encoding, const uint8_t* const* page_table, size_t
 /* argmax_batch / topk_logits (transformer_kernels.cu:7059-7178) */
 int qllm_k_argmax(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
                   uint32_t* out, void* stream);
+/* router_topk_normalized_logits_batch (transformer_kernels.cu:8652-8672, select kernel 2947-3006)
+ * with the BF16 rounding of logits and scores of run_router (dense_fp4_provider.cpp:8153-8164):
+ * logits [rows, experts] -> indices / scores [rows, top_k], top_k <= 8, experts <= 256. */
+int qllm_k_moe_route(const float* logits, uint32_t rows, uint32_t experts, uint32_t top_k,
+                     float route_scale, uint32_t* indices, float* scores, void* stream);
 size_t qllm_k_topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k);
 int qllm_k_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
                 uint32_t k, float* out_values, uint32_t* out_tokens, void* workspace,

@@ -21,7 +21,9 @@ class Matrix(C.Structure):
 
 class Block(C.Structure):
     _fields_ = [("input_norm", C.c_void_p), ("qkv", Matrix), ("o", Matrix),
-                ("post_norm", C.c_void_p), ("gate_up", Matrix), ("down", Matrix)]
+                ("post_norm", C.c_void_p), ("gate_up", Matrix), ("down", Matrix),
+                ("router", Matrix), ("expert_gate", C.POINTER(Matrix)), ("expert_up", C.POINTER(Matrix)),
+                ("expert_down", C.POINTER(Matrix))]
 
 
 class Config(C.Structure):
@@ -31,7 +33,8 @@ class Config(C.Structure):
                [("rope_theta", C.c_float), ("eps", C.c_float)] + \
                [(n, C.c_uint32) for n in
                 ("page_tokens", "kv_encoding", "mtp_kv_encoding",
-                 "activation_bf16", "draft_depth", "max_context", "split_tokens")]
+                 "activation_bf16", "draft_depth", "max_context", "split_tokens",
+                 "experts", "route_width", "expert_ffn")] + [("route_scale", C.c_float)]
 
 
 class Weights(C.Structure):
@@ -96,7 +99,7 @@ def lib():
             "qo_kv_layer_bytes": (sz, [u32, u32, u32, u32]),
             "qo_kv_store": (None, [u32, vp, sz, u32, u32, u32, vp, vp, u32, u32, u32]),
             "qo_attention": (None, [u32, vp, sz, u32, vp, u32, u32, u32, u32, u32, u32, u32, C.c_int, vp]),
-            "qo_argmax": (u32, [vp, u32]), "qo_set_threads": (None, [u32]), "qo_max_threads": (u32, []), "qo_topk": (None, [vp, u32, u32, vp, vp]),
+            "qo_argmax": (u32, [vp, u32]), "qo_set_threads": (None, [u32]), "qo_moe_route": (None, [vp, u32, u32, C.c_float, vp, vp]), "qo_max_threads": (u32, []), "qo_topk": (None, [vp, u32, u32, vp, vp]),
             "qo_counter_uniform": (f64, [u64, u32, u32, u32]),
             "qo_make_distribution": (C.c_int, [vp, vp, u32, u32, u32, u32, vp, vp]),
             "qo_sample_distribution": (u32, [vp, vp, u32, f64]),

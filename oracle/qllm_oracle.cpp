@@ -637,6 +637,40 @@ bool rejection_sample(uint32_t proposal, const Dist& target, const Dist& draft, 
   return false;
 }
 
+// Router selection of the NVFP4 routed-expert branch (router_select_batch_kernel +
+// scale_router_scores_kernel, runtime/src/cuda/transformer_kernels.cu:2947-3016, and the BF16
+// rounding of logits and scores in run_router, dense_fp4_provider.cpp:8153-8164): top-K by
+// repeated arg-max over the BF16-rounded logits (ties to the lower expert id), softmax over
+// the selected values, times the routed scaling factor, rounded to BF16.
+void moe_route(const float* logits, uint32_t experts, uint32_t top_k, float route_scale, uint32_t* chosen,
+               float* score) {
+  float value[8];
+  for (uint32_t slot = 0; slot < top_k; ++slot) {
+    float best = -INFINITY;
+    uint32_t best_index = 0xffffffffU;
+    for (uint32_t i = 0; i < experts; ++i) {
+      bool used = false;
+      for (uint32_t p = 0; p < slot; ++p) used |= chosen[p] == i;
+      const float v = bf16_round(logits[i]);
+      if (!used && (v > best || (v == best && i < best_index))) { best = v; best_index = i; }
+    }
+    chosen[slot] = best_index;
+    value[slot] = best;
+  }
+  // exp evaluated in double and rounded once, so that a device and a host evaluation agree
+  float top = -INFINITY, sum = 0.0F;
+  for (uint32_t slot = 0; slot < top_k; ++slot) top = std::max(top, value[slot]);
+  for (uint32_t slot = 0; slot < top_k; ++slot) {
+    score[slot] = static_cast<float>(std::exp(static_cast<double>(value[slot] - top)));
+    sum += score[slot];
+  }
+  for (uint32_t slot = 0; slot < top_k; ++slot) {
+    score[slot] /= sum;
+    if (route_scale != 1.0F) score[slot] *= route_scale;
+    score[slot] = bf16_round(score[slot]);
+  }
+}
+
 }  // namespace
 
 // --------------------------------------------------------------- whole step
@@ -677,6 +711,44 @@ struct qo_session {
       }
   }
 
+  // Routed mixture of experts in place of the dense FFN, NVFP4 branch of run_router +
+  // run_routed_moe (dense_fp4_provider.cpp:8128-8166, 8207-8248) with the routed-expert
+  // arithmetic of moe_kernels.cu:171-264, 430-510, 633-690, 759-790 and the router selection of
+  // transformer_kernels.cu:2947-3006; no shared expert.  `normalized` holds the post-attention
+  // RMSNorm rows, `residual` the residual stream; the result replaces `hidden`.
+  void moe_ffn(const qo_block& b, uint32_t rows) {
+    const auto& c = cfg;
+    const uint32_t H = c.hidden, E = c.experts, K = c.route_width, W = c.expert_ffn;
+    for (size_t i = 0; i < static_cast<size_t>(rows) * H; ++i) normalized[i] = bf16_round(normalized[i]);
+    std::vector<float> logits_r(static_cast<size_t>(rows) * E);
+    nvfp4_gemv(b.router, 0, E, normalized.data(), rows, logits_r.data());
+    std::vector<float> gate(W), up(W), mid(W), out(H), total(H);
+    for (uint32_t r = 0; r < rows; ++r) {
+      const float* lg = logits_r.data() + static_cast<size_t>(r) * E;
+      uint32_t chosen[8];
+      float score[8];
+      moe_route(lg, E, K, c.route_scale, chosen, score);
+      std::fill(total.begin(), total.end(), 0.0F);
+      const float* x = normalized.data() + static_cast<size_t>(r) * H;
+      for (uint32_t slot = 0; slot < K; ++slot) {
+        const uint32_t e = chosen[slot];
+        if (e >= E) throw std::runtime_error("router selected no expert");
+        // each projection fake-quantises its input with its own activation scale and rounds
+        // its dot products to BF16 (nvfp4_dot + bf16 in gate_up_silu_selection_batch)
+        nvfp4_gemv(b.expert_gate[e], 0, W, x, 1, gate.data());
+        nvfp4_gemv(b.expert_up[e], 0, W, x, 1, up.data());
+        for (uint32_t i = 0; i < W; ++i)
+          mid[i] = bf16_round((gate[i] / (1.0F + std::exp(-gate[i]))) * up[i]);
+        nvfp4_gemv(b.expert_down[e], 0, H, mid.data(), 1, out.data());
+        for (uint32_t i = 0; i < H; ++i) total[i] += score[slot] * out[i];  // ordered over the slots
+      }
+      for (uint32_t i = 0; i < H; ++i) {
+        const float moe = bf16_round(total[i]);
+        hidden[static_cast<size_t>(r) * H + i] = bf16_round(residual[static_cast<size_t>(r) * H + i] + moe);
+      }
+    }
+  }
+
   // attention sub-block (run_full_attention + residual add) then FFN (run_ffn)
   void block(const qo_block& b, uint32_t rows, uint32_t enc, size_t layer_offset,
              uint32_t first_cache_position, const uint32_t* rotary_positions) {
@@ -708,6 +780,10 @@ struct qo_session {
     // FFN
     residual = hidden;
     rmsnorm(hidden.data(), b.post_norm, normalized.data(), rows, c.hidden, c.eps);
+    if (c.experts) {
+      moe_ffn(b, rows);
+      return;
+    }
     nvfp4_gemv(b.gate_up, 0, b.gate_up.rows, normalized.data(), rows, gate_up.data());
     for (uint32_t r = 0; r < rows; ++r)
       for (uint32_t i = 0; i < c.ffn; ++i) {
@@ -875,6 +951,10 @@ void qo_attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset
             split_tokens, bf16 != 0, out);
 }
 uint32_t qo_argmax(const float* v, uint32_t count) { return argmax(v, count); }
+void qo_moe_route(const float* logits, uint32_t experts, uint32_t top_k, float route_scale, uint32_t* indices,
+                  float* scores) {
+  if (top_k <= 8U && top_k <= experts) moe_route(logits, experts, top_k, route_scale, indices, scores);
+}
 // Host threads the parallel loops (GEMV rows, attention heads) use; for the timed baseline.
 void qo_set_threads(uint32_t threads) { omp_set_num_threads(threads ? static_cast<int>(threads) : 1); }
 uint32_t qo_max_threads(void) { return static_cast<uint32_t>(omp_get_max_threads()); }
@@ -924,6 +1004,9 @@ qo_session* qo_session_create(const qo_config* config, const qo_weights* weights
         c.hidden % 16U || c.ffn % 16U || !c.page_tokens || c.page_tokens % 32U ||
         c.draft_depth > 4U || !c.split_tokens || c.split_tokens % 32U || c.draft_vocab > c.vocab)
       throw std::runtime_error("invalid oracle configuration");
+    if (c.experts && (!c.route_width || c.route_width > 8U || c.route_width > c.experts || !c.expert_ffn ||
+                      c.expert_ffn % 16U || !(c.route_scale > 0.0F)))
+      throw std::runtime_error("invalid routed-expert configuration");
     auto* s = new qo_session;
     s->cfg = c;
     s->w = *weights;

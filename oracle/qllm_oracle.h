@@ -53,6 +53,12 @@ typedef struct qo_block {
   const float* post_norm;   /* [hidden] */
   qo_matrix gate_up;        /* [2*ffn, hidden]: gate rows then up rows */
   qo_matrix down;           /* [hidden, ffn] */
+  /* routed mixture of experts instead of the dense FFN when cfg.experts != 0
+   * (runtime/tools/dense_fp4_provider.cpp:8128-8248, runtime/src/cuda/moe_kernels.cu:121-264) */
+  qo_matrix router;               /* [experts, hidden] */
+  const qo_matrix* expert_gate;   /* [experts], each [expert_ffn, hidden] */
+  const qo_matrix* expert_up;     /* [experts], each [expert_ffn, hidden] */
+  const qo_matrix* expert_down;   /* [experts], each [hidden, expert_ffn] */
 } qo_block;
 
 typedef struct qo_config {
@@ -67,6 +73,10 @@ typedef struct qo_config {
   uint32_t draft_depth;      /* D (<= 4) */
   uint32_t max_context;
   uint32_t split_tokens;     /* attention split length (multiple of 32) */
+  uint32_t experts;          /* 0 = dense FFN */
+  uint32_t route_width;      /* experts selected per token (<= 8) */
+  uint32_t expert_ffn;       /* intermediate width of one expert */
+  float route_scale;         /* routed scaling factor applied to the normalised scores */
 } qo_config;
 
 typedef struct qo_weights {
@@ -141,6 +151,9 @@ void qo_attention(uint32_t encoding, const uint8_t* const* pages,
                   uint32_t kv_heads, uint32_t head_dim, uint32_t split_tokens,
                   int act_bf16, float* out);
 uint32_t qo_argmax(const float* values, uint32_t count);
+/* router of the routed-expert FFN: top_k (<= 8) experts and their BF16-rounded weights */
+void qo_moe_route(const float* logits, uint32_t experts, uint32_t top_k, float route_scale,
+                  uint32_t* indices, float* scores);
 /* thread count of the OpenMP loops (timed CPU baseline) */
 void qo_set_threads(uint32_t threads);
 uint32_t qo_max_threads(void);

@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "gemv_mma.h"
 #include "kernels.h"
+#include "moe.h"
 
 using namespace qllm;
 
@@ -190,6 +191,26 @@ int qllm_k_argmax(const float* values, uint32_t rows, uint32_t count, uint32_t r
                   uint32_t* out, void* stream) {
   if (!values || !rows || !count || !out) return fail(QLLM_INVALID_ARGUMENT, "invalid argmax");
   return launch_argmax(values, rows, count, row_stride, out, static_cast<cudaStream_t>(stream));
+}
+
+int qllm_k_moe_route(const float* logits, uint32_t rows, uint32_t experts, uint32_t top_k, float route_scale,
+                     uint32_t* indices, float* scores, void* stream) {
+  if (!logits || !indices || !scores || !rows || !(route_scale > 0.0F))
+    return fail(QLLM_INVALID_ARGUMENT, "invalid router selection");
+  GemvOut values{};
+  values.data = logits;  // final values, row-major [rows, experts]
+  values.split = 0U;
+  values.n = experts;
+  values.batch = rows;
+  values.weight_scale = values.input_scale = 1.0F;
+  MoeArgs a{};
+  a.rows = rows;
+  a.experts = experts;
+  a.route_width = top_k;
+  a.route_scale = route_scale;
+  a.indices = indices;
+  a.scores = scores;
+  return launch_moe_router_select(values, a, static_cast<cudaStream_t>(stream));
 }
 
 size_t qllm_k_topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k) {

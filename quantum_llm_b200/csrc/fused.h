@@ -27,6 +27,7 @@ struct NormQuantArgs {
   float eps;
   float* normalized;         // optional FP32 copy of the normalised rows
   uint32_t normalized_stride;
+  bool round_normalized;     // round the normalised rows to BF16 before they are stored and quantised
   QuantSink sink;            // kind < 0: no quantised output
   uint32_t sink_block_offset;  // first 16-value block inside the operand row (concatenated inputs)
   const uint32_t* row_select;  // optional device index of the single input row

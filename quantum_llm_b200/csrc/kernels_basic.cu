@@ -3,6 +3,7 @@
 // product, argmax and exact top-k.  Arithmetic follows the reference launchers
 // named in include/qllm_b200.h; layouts and launch shapes are this library's own.
 #include "common.cuh"
+#include "fp4_dot.cuh"
 #include "kernels.h"
 
 namespace qllm {
@@ -165,28 +166,7 @@ int launch_act_quant_i8(const float* x, void* qact, uint32_t rows, uint32_t cols
 // A warp owns two weight rows and walks the row in 16-value blocks, one block per
 // lane per step: 8 code bytes + 1 scale byte per row, the activations of the block
 // (16 INT8 + 1 FP32 per batch row) are loaded once for both weight rows.
-// prmt.b32 in its default mode: selector nibble bits 2:0 pick a byte of {a, b}; bit 3
-// replaces the byte by eight copies of its sign bit.
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
-  return d;
-}
-
-__device__ __forceinline__ void expand_fp4x8(uint32_t w, uint32_t& lo4, uint32_t& hi4) {
-  // bytes of twice the E2M1 value of nibbles 0..3 (lo4) and 4..7 (hi4), element order kept
-  constexpr uint32_t kPos0 = 0x03020100U, kPos1 = 0x0c080604U;  // 0 1 2 3 | 4 6 8 12
-  constexpr uint32_t kNeg0 = 0xfdfeff00U, kNeg1 = 0xf4f8fafcU;  // 0 -1 -2 -3 | -4 -6 -8 -12
-  const uint32_t wl = w << 4U;
-  const uint32_t s_lo = w & 0x7777U, s_hi = (w >> 16U) & 0x7777U;
-  const uint32_t pos_lo = prmt(kPos0, kPos1, s_lo), neg_lo = prmt(kNeg0, kNeg1, s_lo);
-  const uint32_t pos_hi = prmt(kPos0, kPos1, s_hi), neg_hi = prmt(kNeg0, kNeg1, s_hi);
-  // byte masks from the sign bit of each nibble (sign-replicating permute)
-  const uint32_t m_lo = prmt(wl, w, 0xd9c8U), m_hi = prmt(wl, w, 0xfbeaU);
-  lo4 = (pos_lo & ~m_lo) | (neg_lo & m_lo);
-  hi4 = (pos_hi & ~m_hi) | (neg_hi & m_hi);
-}
-
+// (prmt / expand_fp4x8: fp4_dot.cuh)
 template <int B>
 __global__ void __launch_bounds__(256)
 nvfp4_gemv_dp4a_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,

@@ -89,6 +89,7 @@ residual_norm_quant_kernel(NormQuantArgs a) {
     if (valid) {
       n = make_float4(v[k].x * inverse * w[k].x, v[k].y * inverse * w[k].y, v[k].z * inverse * w[k].z,
                       v[k].w * inverse * w[k].w);
+      if (a.round_normalized) n = make_float4(bf16r(n.x), bf16r(n.y), bf16r(n.z), bf16r(n.w));
       if (a.normalized)
         reinterpret_cast<float4*>(a.normalized + static_cast<size_t>(out_row) * a.normalized_stride)[f] = n;
     }

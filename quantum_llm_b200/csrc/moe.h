@@ -1,0 +1,43 @@
+// Routed-expert FFN of the decode step: device descriptors and launchers (kernels_moe.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "quant.cuh"
+
+namespace qllm {
+
+// One expert projection on the device (NVFP4: codes [rows, cols/2], E4M3 scales [rows, cols/16]).
+struct ExpertMatrix {
+  const uint8_t* codes;
+  const uint8_t* scales;
+  float weight_scale;
+  float input_scale;
+};
+
+struct MoeArgs {
+  const float* x;          // [rows, x_stride] post-attention RMSNorm rows (rounded to BF16 on use)
+  uint32_t x_stride;
+  uint32_t rows, hidden, experts, route_width, expert_ffn;
+  float route_scale;
+  uint32_t* indices;       // [rows * route_width] selected expert per slot
+  float* scores;           // [rows * route_width] BF16-rounded routing weights
+  const ExpertMatrix* gate;  // [experts], each [expert_ffn, hidden]
+  const ExpertMatrix* up;    // [experts], each [expert_ffn, hidden]
+  const ExpertMatrix* down;  // [experts], each [hidden, expert_ffn]
+  float* mid;              // [rows * route_width, expert_ffn]
+  float* out;              // [rows * route_width, hidden]
+  float* moe;              // [rows, hidden] BF16-rounded weighted sum (added to the residual by the next norm)
+};
+
+// floats of workspace for indices, scores, mid, out and moe together
+size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn);
+// top-K selection + normalised scores from the router GEMV result
+int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream_t stream);
+// gate/up/SiLU, down and the ordered weighted sum (three launches)
+int launch_moe_experts(const MoeArgs& a, cudaStream_t stream);
+
+}  // namespace qllm

@@ -17,6 +17,7 @@
 #include "gemv_mma.h"
 #include "fused.h"
 #include "kernels.h"
+#include "moe.h"
 
 namespace qllm {
 
@@ -84,6 +85,11 @@ struct Block {
   const float* input_norm = nullptr;
   const float* post_norm = nullptr;
   Matrix qkv, o, gate_up, down;
+  // routed experts (cfg.experts != 0) replace gate_up/down: router + device arrays of descriptors
+  Matrix router;
+  const ExpertMatrix* expert_gate = nullptr;
+  const ExpertMatrix* expert_up = nullptr;
+  const ExpertMatrix* expert_down = nullptr;
 };
 
 }  // namespace qllm
@@ -139,6 +145,7 @@ struct qllm_provider {
   DeviceBuffer<float> hidden, mtp_hidden, qkv, logits, mtp_emb, draft_logits, q8_scale;
   DeviceBuffer<int8_t> q8;  // INT8 copy of the rotated queries for the Q4H attention
   DeviceBuffer<float> partial_buf, gemv_out;   // tensor-core split-K partials / CUDA-core results
+  DeviceBuffer<float> moe_x, moe_ws;           // routed experts: normalised input rows, selection workspace
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
@@ -178,9 +185,32 @@ struct qllm_provider {
     out.post_norm = bring(b.post_norm, c.hidden, on_device);
     out.qkv = bring(b.qkv, on_device, (c.q_heads + 2U * c.kv_heads) * c.head_dim, c.hidden, "qkv");
     out.o = bring(b.o, on_device, c.hidden, c.q_heads * c.head_dim, "o");
-    out.gate_up = bring(b.gate_up, on_device, 2U * c.ffn, c.hidden, "gate_up");
-    out.down = bring(b.down, on_device, c.hidden, c.ffn, "down");
+    if (!c.experts) {
+      out.gate_up = bring(b.gate_up, on_device, 2U * c.ffn, c.hidden, "gate_up");
+      out.down = bring(b.down, on_device, c.hidden, c.ffn, "down");
+      return out;
+    }
+    if (!b.expert_gate || !b.expert_up || !b.expert_down) throw Error(QLLM_INVALID_ARGUMENT, "missing expert tensors");
+    out.router = bring(b.router, on_device, c.experts, c.hidden, "router");
+    out.expert_gate = bring_experts(b.expert_gate, on_device, c.expert_ffn, c.hidden, "expert gate");
+    out.expert_up = bring_experts(b.expert_up, on_device, c.expert_ffn, c.hidden, "expert up");
+    out.expert_down = bring_experts(b.expert_down, on_device, c.hidden, c.expert_ffn, "expert down");
     return out;
+  }
+  // Host array of `experts` descriptors -> device array of (device) descriptors.
+  const ExpertMatrix* bring_experts(const qllm_matrix* src, bool on_device, uint32_t rows, uint32_t cols,
+                                    const char* name) {
+    std::vector<ExpertMatrix> host(cfg.experts);
+    for (uint32_t e = 0; e < cfg.experts; ++e) {
+      const qllm_matrix& m = src[e];
+      if (m.rows != rows || m.cols != cols || cols % 16U || !(m.weight_scale > 0.0F) || !(m.input_scale > 0.0F))
+        throw Error(QLLM_INVALID_ARGUMENT, std::string("native NVFP4 matrix geometry is invalid: ") + name);
+      host[e].codes = bring(m.codes, static_cast<size_t>(rows) * cols / 2U, on_device);
+      host[e].scales = bring(m.scales, static_cast<size_t>(rows) * cols / 16U, on_device);
+      host[e].weight_scale = m.weight_scale;
+      host[e].input_scale = m.input_scale;
+    }
+    return bring(host.data(), host.size(), false);
   }
 
   void create(const qllm_config& config, const qllm_weights& w, bool on_device, int dev) {
@@ -193,6 +223,9 @@ struct qllm_provider {
         c.kv_encoding > 2U || c.mtp_kv_encoding > 2U || c.rotary_dim > c.head_dim || c.rotary_dim % 2U ||
         kMaxRows * (c.q_heads / c.kv_heads) > 64U)
       throw Error(QLLM_INVALID_ARGUMENT, "provider does not support this model geometry");
+    if (c.experts && (!c.route_width || c.route_width > 8U || c.route_width > c.experts || c.experts > 256U ||
+                      !c.expert_ffn || c.expert_ffn % 16U || !(c.route_scale > 0.0F)))
+      throw Error(QLLM_INVALID_ARGUMENT, "provider does not support this routed-expert geometry");
     device = dev;
     borrowed = on_device;
     cu(cudaSetDevice(device), "select device");
@@ -234,8 +267,9 @@ struct qllm_provider {
     const uint32_t widest = std::max(std::max(2U * c.hidden, c.ffn), c.q_heads * c.head_dim);
     quant_buf.alloc(quant_buffer_bytes(R, widest), "quantised GEMV operand");
     size_t partial_floats = 0;
-    const uint32_t shapes[6][2] = {{qkv_w, c.hidden}, {c.hidden, c.q_heads * c.head_dim}, {2U * c.ffn, c.hidden},
-                                   {c.hidden, c.ffn}, {c.vocab, c.hidden}, {c.hidden, 2U * c.hidden}};
+    const uint32_t shapes[7][2] = {{qkv_w, c.hidden}, {c.hidden, c.q_heads * c.head_dim}, {2U * c.ffn, c.hidden},
+                                   {c.hidden, c.ffn}, {c.vocab, c.hidden}, {c.hidden, 2U * c.hidden},
+                                   {c.experts ? c.experts : 16U, c.hidden}};
     uint32_t most_outputs = 0;
     for (const auto& s : shapes) {
       partial_floats = std::max(partial_floats, gemv_partial_floats(R, s[0], s[1]));
@@ -245,6 +279,10 @@ struct qllm_provider {
     gemv_out.alloc(static_cast<size_t>(R) * most_outputs, "GEMV results");
     kernel_error.alloc(1, "kernel status word");
     cu(cudaMemsetAsync(kernel_error.p, 0, sizeof(uint32_t), stream), "kernel status word");
+    if (c.experts) {
+      moe_x.alloc(static_cast<size_t>(R) * c.hidden, "routed-expert input rows");
+      moe_ws.alloc(moe_workspace_floats(R, c.route_width, c.hidden, c.expert_ffn), "routed-expert workspace");
+    }
     mtp_emb.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding");
     draft_logits.alloc(c.draft_vocab, "draft logits");
     // the page pool keeps a few slots of slack past max_context for speculative rows
@@ -282,7 +320,7 @@ struct qllm_provider {
   // x' = act(x + delta) stored to `store`; operand of `next` = quantised rmsnorm(x') * weight
   void norm_quant(const float* x, uint32_t x_stride, const GemvOut* delta, float* store, const float* weight,
                   const Matrix* next, uint32_t rows, uint32_t sink_block_offset = 0,
-                  const uint32_t* row_select = nullptr) {
+                  const uint32_t* row_select = nullptr, float* normalized = nullptr, bool round_normalized = false) {
     const auto& c = cfg;
     NormQuantArgs a{};
     a.x = x;
@@ -298,7 +336,47 @@ struct qllm_provider {
     a.sink = next ? sink_for(*next, rows) : no_sink();
     a.sink_block_offset = sink_block_offset;
     a.row_select = row_select;
+    a.normalized = normalized;
+    a.normalized_stride = c.hidden;
+    a.round_normalized = round_normalized;
     ok(launch_residual_norm_quant(a, rows, stream));
+  }
+
+  // Routed experts in place of the dense FFN (run_router + run_routed_moe, NVFP4 branch,
+  // dense_fp4_provider.cpp:8128-8166, 8207-8248).  `attention_out` is the o-projection result still
+  // to be added to the residual stream `h`; the weighted expert sum becomes the new `pending`.
+  void routed_experts(const Block& b, float* h, const GemvOut& attention_out, uint32_t rows, GemvOut* pending) {
+    const auto& c = cfg;
+    norm_quant(h, c.hidden, &attention_out, h, b.post_norm, &b.router, rows, 0U, nullptr, moe_x.p, true);
+    const GemvOut logits = gemv(b.router, rows);
+    const size_t selections = static_cast<size_t>(rows) * c.route_width;
+    MoeArgs a{};
+    a.x = moe_x.p;
+    a.x_stride = c.hidden;
+    a.rows = rows;
+    a.hidden = c.hidden;
+    a.experts = c.experts;
+    a.route_width = c.route_width;
+    a.expert_ffn = c.expert_ffn;
+    a.route_scale = c.route_scale;
+    a.indices = reinterpret_cast<uint32_t*>(moe_ws.p);
+    a.scores = moe_ws.p + selections;
+    a.mid = a.scores + selections;
+    a.out = a.mid + selections * c.expert_ffn;
+    a.moe = a.out + selections * c.hidden;
+    a.gate = b.expert_gate;
+    a.up = b.expert_up;
+    a.down = b.expert_down;
+    ok(launch_moe_router_select(logits, a, stream));
+    ok(launch_moe_experts(a, stream));
+    GemvOut result{};
+    result.data = a.moe;  // final values: the next norm kernel adds them to the residual stream
+    result.split = 0U;
+    result.n = c.hidden;
+    result.batch = rows;
+    result.weight_scale = 1.0F;
+    result.input_scale = 1.0F;
+    *pending = result;
   }
 
   // One transformer block over `rows` rows held in hidden: attention sub-block
@@ -365,6 +443,10 @@ struct qllm_provider {
     cb.sink = sink_for(b.o, rows);
     ok(launch_combine_quant(cb, rows, stream));
     const GemvOut o_out = gemv(b.o, rows);
+    if (c.experts) {
+      routed_experts(b, h, o_out, rows, pending);
+      return;
+    }
     norm_quant(h, c.hidden, &o_out, h, b.post_norm, &b.gate_up, rows);
     const GemvOut gu = gemv(b.gate_up, rows);
     ok(launch_silu_quant(gu, c.ffn, bf, sink_for(b.down, rows), nullptr, stream));

@@ -21,7 +21,10 @@ class Matrix(C.Structure):
 
 class Block(C.Structure):
     _fields_ = [("input_norm", C.c_void_p), ("qkv", Matrix), ("o", Matrix), ("post_norm", C.c_void_p),
-                ("gate_up", Matrix), ("down", Matrix)]
+                ("gate_up", Matrix), ("down", Matrix),
+                # routed experts (config.experts != 0): router + host arrays of `experts` matrices
+                ("router", Matrix), ("expert_gate", C.POINTER(Matrix)), ("expert_up", C.POINTER(Matrix)),
+                ("expert_down", C.POINTER(Matrix))]
 
 
 class Config(C.Structure):
@@ -29,7 +32,8 @@ class Config(C.Structure):
                                           "vocab", "draft_vocab", "rotary_dim")] + \
                [("rope_theta", C.c_float), ("eps", C.c_float)] + \
                [(n, C.c_uint32) for n in ("page_tokens", "kv_encoding", "mtp_kv_encoding", "activation_bf16",
-                                          "draft_depth", "max_context", "split_tokens")]
+                                          "draft_depth", "max_context", "split_tokens",
+                                          "experts", "route_width", "expert_ffn")] + [("route_scale", C.c_float)]
 
 
 class Weights(C.Structure):
@@ -92,6 +96,7 @@ SIGNATURES = {
     "qllm_k_nvfp4_gemv_prepared": (ci, [vp, vp, vp, u32, vp, sz, ci, vp]),
     "qllm_k_nvfp4_gemv_prepared_core": (ci, [vp, u32, vp, sz, vp]),
     "qllm_k_nvfp4_quantize_weights": (ci, [vp, u32, u32, f32, vp, vp, vp]),
+    "qllm_k_moe_route": (ci, [vp, u32, u32, u32, f32, vp, vp, vp]),
     "qllm_k_add": (ci, [vp, vp, u64, ci, vp]),
     "qllm_k_silu_product": (ci, [vp, vp, u32, u32, ci, vp]),
     "qllm_k_rope_kv_store": (ci, [vp, u32, u32, u32, u32, u32, vp, vp, u32, u32, vp, sz, u32, u32, ci, vp]),

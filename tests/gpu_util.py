@@ -14,8 +14,14 @@ def c_matrix(m):
 
 
 def c_block(b):
+    if not getattr(b, "experts", 0):
+        return ql.Block(b.input_norm.ctypes.data, c_matrix(b.qkv), c_matrix(b.o), b.post_norm.ctypes.data,
+                        c_matrix(b.gate_up), c_matrix(b.down))
+    arrays = [(ql.Matrix * b.experts)(*[c_matrix(m) for m in group])
+              for group in (b.expert_gate, b.expert_up, b.expert_down)]
+    b._c_arrays = arrays   # host arrays of expert descriptors: alive until the provider has copied them
     return ql.Block(b.input_norm.ctypes.data, c_matrix(b.qkv), c_matrix(b.o), b.post_norm.ctypes.data,
-                    c_matrix(b.gate_up), c_matrix(b.down))
+                    c_matrix(b.gate_up), c_matrix(b.down), c_matrix(b.router), arrays[0], arrays[1], arrays[2])
 
 
 def c_config(cfg):

@@ -52,10 +52,17 @@ class SynthBlock:
         qkv_rows = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"]
         shapes = dict(qkv=(qkv_rows, H), o=(H, cfg["q_heads"] * cfg["head_dim"]),
                       gate_up=(2 * F, H), down=(H, F))
+        self.experts = int(cfg.get("experts", 0))
+        if self.experts:   # routed experts: separate gate / up / down matrices per expert
+            W = cfg["expert_ffn"]
+            shapes["router"] = (self.experts, H)
+            for e in range(self.experts):
+                shapes[f"gate{e}"], shapes[f"up{e}"], shapes[f"down{e}"] = (W, H), (W, H), (H, W)
         self.master = {}
         for name, shape in shapes.items():
             if base is None:
-                w = rng.normal(0.0, 0.02, shape).astype(np.float32)
+                std = 0.2 if name == "router" else 0.02   # router logits spread over a few units
+                w = rng.normal(0.0, std, shape).astype(np.float32)
             else:
                 w = base.master[name] + rng.normal(0.0, noise, shape).astype(np.float32)
             self.master[name] = w
@@ -63,10 +70,24 @@ class SynthBlock:
                                                      ("qkv", "o", "gate_up", "down"))
         self.input_norm = np.ones(H, np.float32)
         self.post_norm = np.ones(H, np.float32)
+        self.router = None
+        if self.experts:
+            # every projection has its own activation scale, as in the checkpoint format
+            self.router = SynthMatrix(self.master["router"])
+            self.expert_gate = [SynthMatrix(self.master[f"gate{e}"], INPUT_SCALE) for e in range(self.experts)]
+            self.expert_up = [SynthMatrix(self.master[f"up{e}"], 300.0 + 4.0 * e) for e in range(self.experts)]
+            self.expert_down = [SynthMatrix(self.master[f"down{e}"], 2000.0 + 16.0 * e) for e in range(self.experts)]
 
     def oracle(self):
+        if not self.experts:
+            return ob.Block(ob._ptr(self.input_norm), self.qkv.oracle(), self.o.oracle(),
+                            ob._ptr(self.post_norm), self.gate_up.oracle(), self.down.oracle())
+        arrays = [(ob.Matrix * self.experts)(*[m.oracle() for m in group])
+                  for group in (self.expert_gate, self.expert_up, self.expert_down)]
+        self._oracle_arrays = arrays   # keep the ctypes arrays alive
         return ob.Block(ob._ptr(self.input_norm), self.qkv.oracle(), self.o.oracle(),
-                        ob._ptr(self.post_norm), self.gate_up.oracle(), self.down.oracle())
+                        ob._ptr(self.post_norm), self.gate_up.oracle(), self.down.oracle(),
+                        self.router.oracle(), arrays[0], arrays[1], arrays[2])
 
 
 class SynthModel:
