@@ -7,6 +7,9 @@ execute_exact_decode: verify 5 rows, accept/rollback on the device, 4 draft pass
 one read at the end); `e2e` is the same through the provider's per-step call with the
 invocation cursor uploaded and the result record read back every step.
 N>1 runs N independent replicas (one stream per GPU, data parallel, no collective).
+`--model moe35b` runs the same step on the 35B-A3B-class routed model (48 layers, 128 experts,
+8 per token) at 8192 cached tokens; `--streams S` steps S independent requests in turn on each
+GPU (their rows are not batched into one pass).
 
   python bench.py --gpus N --steps K --warmup W [--impl reference]
 """
@@ -24,6 +27,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 CONTEXT = 32768          # cached tokens when the timed region starts
+MOE_CONTEXT = 8192       # the routed model's configuration
 REAL_PREFILL = 40        # last prompt tokens run through the real prefill path
 METRIC = "decode_tok_per_s_mtp4_q4h_32k"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up GEMV launch (tcgen05 kernel,
@@ -40,7 +44,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "1")))
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
-    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--model", default="dense27b", choices=["dense27b", "moe35b"],
+                    help="dense27b: the headline workload; moe35b: the routed 35B-A3B-class target")
+    ap.add_argument("--streams", type=int, default=1, help="independent requests per GPU, stepped in turn")
+    ap.add_argument("--context", type=int, default=0, help="cached tokens (0: 32768 dense, 8192 routed)")
     ap.add_argument("--kv-encoding", default="q4h", choices=["q4h", "f16"],
                     help="target KV cache: Q4H (the headline metric) or exact F16 (metric ..._f16kv_32k)")
     ap.add_argument("--split-tokens", type=int, default=0,
@@ -48,7 +55,10 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if not args.context:
+        args.context = CONTEXT if args.model == "dense27b" else MOE_CONTEXT
+    return args
 
 
 class ClockSampler:
@@ -166,8 +176,11 @@ def algorithmic_step_bytes(cfg, context):
     return per_layer * cfg["layers"] + head + kv + 4 * draft
 
 
-def workload_name(context, kv="q4h"):
-    return ("27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936), 1 stream/GPU, "
+def workload_name(context, kv="q4h", model="dense27b", streams=1):
+    arch = ("27B dense (64L, h5120, 40q/8kv, hd128, ffn17408, vocab151936)" if model == "dense27b" else
+            "35B-A3B routed (48L, h2048, 32q/4kv, hd128, 128 experts x ffn768, 8 per token, vocab151936)")
+    per_gpu = "1 stream/GPU" if streams == 1 else f"{streams} streams/GPU stepped in turn (rows not batched)"
+    return (f"{arch}, {per_gpu}, "
             f"{context} cached tokens, {'exact F16' if kv == 'f16' else 'Q4H'} target KV + Q8 draft KV, MTP-4, greedy")
 
 
@@ -179,6 +192,7 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    assert args.model == "dense27b" and args.streams == 1, "the reference arm times the headline workload only"
     from quantum_llm_b200.synthetic import DENSE_27B
     step_bytes = algorithmic_step_bytes(DENSE_27B, args.context)
     sample = CpuSample()
@@ -214,15 +228,15 @@ def reduce_over_ranks(times_ms, counts, device):
     return [float(x) for x in t.cpu()], [float(x) for x in c.cpu()]
 
 
-def gemv_kernel_leg(model, provider, gemv_impl, rows=5, repeats=3):
+def gemv_kernel_leg(model, provider, gemv_impl, rows=5, repeats=3, name="gate_up"):
     """Average duration of the dominant kernel (gate/up NVFP4 GEMV, 34816x5120, 5 rows) over
     all layers' weights back to back (6.4 GB, far beyond L2), timed with CUDA events on the
-    launching stream."""
+    launching stream.  (`name` picks another of the layers' matrices.)"""
     import torch
     from quantum_llm_b200 import lib as ql
     L = ql.load()
     dev = model.device
-    mats = [b.m["gate_up"] for b in model.layers]
+    mats = [b.m[name] for b in model.layers]
     rows_w, cols = mats[0].rows, mats[0].cols
     x = torch.randn((rows, cols), device=dev, dtype=torch.float32)
     y = torch.empty((rows, rows_w), device=dev, dtype=torch.float32)
@@ -279,9 +293,10 @@ def ours(args):
     if world > 1:
         dist.barrier()
     from quantum_llm_b200.provider import RequestParameters
-    from quantum_llm_b200.synthetic import DENSE_27B, DeviceModel
+    from quantum_llm_b200.synthetic import DENSE_27B, MOE_35B, DeviceModel
 
-    cfg = dict(DENSE_27B)
+    routed = args.model == "moe35b"
+    cfg = dict(MOE_35B if routed else DENSE_27B)
     if args.small:
         cfg["layers"] = 4
     context = args.context
@@ -296,29 +311,47 @@ def ours(args):
     model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
     provider = model.provider()
     provider.set_gemv_impl(args.gemv_impl)
-    state = provider.create_request_state()
     request = RequestParameters(sampling_seed=1 + rank, sampling_temperature_ppm=0,
                                 reserved_context_tokens=cfg["max_context"])
-    # prompt: seeded uniform ids; the first context-REAL_PREFILL positions are represented by
-    # seeded synthetic cache records, the tail goes through the real prefill + draft priming
-    prompt = np.random.default_rng(1 + rank).integers(0, cfg["vocab"], context, dtype=np.uint32)
     synthetic = context - REAL_PREFILL
-    provider.fill_synthetic_kv(state, 0, synthetic, seed=1234 + rank)
-    first = provider.prefill(state, request, prompt[synthetic:], first_position=synthetic, chunk_rows=5)
 
+    class Stream:
+        """One independent request: its own caches, cursor and (per-state) step graph."""
+        def __init__(self, index):
+            # prompt: seeded uniform ids; the first context-REAL_PREFILL positions are represented by
+            # seeded synthetic cache records, the tail goes through the real prefill + draft priming
+            seed = 1 + rank * args.streams + index
+            prompt = np.random.default_rng(seed).integers(0, cfg["vocab"], context, dtype=np.uint32)
+            self.state = provider.create_request_state()
+            provider.fill_synthetic_kv(self.state, 0, synthetic, seed=1233 + seed)
+            self.token = provider.prefill(self.state, request, prompt[synthetic:], first_position=synthetic,
+                                          chunk_rows=5)
+            self.position = context
+
+        def step(self, parameters=request):
+            r = provider.execute_exact_decode(self.state, parameters, self.token, self.position, cfg["max_context"])
+            self.position += r.positions_advanced
+            self.token = r.next_token
+            return r.positions_advanced
+
+        def steps(self, n):
+            advanced = 0
+            for r in provider.execute_exact_decode_steps(self.state, request, cfg["max_context"], n):
+                advanced += r.positions_advanced
+                self.position += r.positions_advanced
+                self.token = r.next_token
+            return advanced
+
+    streams = [Stream(i) for i in range(args.streams)]
     stream = torch.cuda.ExternalStream(provider.stream(), device=f"cuda:{local}")
-    position, token = context, first
-    launches0 = provider.telemetry(state)["kernel_launches"]
+    launches0 = provider.telemetry(streams[0].state)["kernel_launches"]
     provider.set_graph_mode(False)
-    r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
-    launches_per_step = provider.telemetry(state)["kernel_launches"] - launches0
-    position += r.positions_advanced
-    token = r.next_token
+    streams[0].step()
+    launches_per_step = provider.telemetry(streams[0].state)["kernel_launches"] - launches0
     provider.set_graph_mode(not args.no_graph)
     for _ in range(max(args.warmup, 3)):
-        r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
-        position += r.positions_advanced
-        token = r.next_token
+        for s in streams:
+            s.step()
 
     def barrier():
         if world > 1:
@@ -333,12 +366,11 @@ def ours(args):
         start.record(stream)
         done = 0
         while done < args.steps:
-            n = min(32, args.steps - done)
-            for r in provider.execute_exact_decode_steps(state, request, cfg["max_context"], n):
-                tokens_a += r.positions_advanced
-                accepted_a += r.positions_advanced - 1
-                position += r.positions_advanced
-                token = r.next_token
+            n = min(32 if args.streams == 1 else 4, args.steps - done)
+            for s in streams:
+                advanced = s.steps(n)
+                tokens_a += advanced
+                accepted_a += advanced - n
             done += n
         stop.record(stream)
         stop.synchronize()
@@ -349,10 +381,8 @@ def ours(args):
     tokens_b = 0
     start.record(stream)
     for _ in range(args.steps):
-        r = provider.execute_exact_decode(state, request, token, position, cfg["max_context"])
-        tokens_b += r.positions_advanced
-        position += r.positions_advanced
-        token = r.next_token
+        for s in streams:
+            tokens_b += s.step()
     stop.record(stream)
     stop.synchronize()
     barrier()
@@ -367,10 +397,9 @@ def ours(args):
         barrier()
         start.record(stream)
         for _ in range(sampled_steps if timed else 3):
-            r = provider.execute_exact_decode(state, sampled, token, position, cfg["max_context"])
-            tokens_c += r.positions_advanced if timed else 0
-            position += r.positions_advanced
-            token = r.next_token
+            for s in streams:
+                advanced = s.step(sampled)
+                tokens_c += advanced if timed else 0
         stop.record(stream)
         stop.synchronize()
     barrier()
@@ -390,36 +419,44 @@ def ours(args):
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if peaks else "fallback"
-    kernel_ms, kernel_bytes = gemv_kernel_leg(model, provider, args.gemv_impl)
+    # the dominant kernel: the dense model's gate/up GEMV; for the routed model the largest
+    # tensor-core GEMV of a layer (fused q/k/v projection) stands in, the expert kernels being
+    # selected per token
+    kernel_name = "qkv" if routed else "gate_up"
+    kernel_ms, kernel_bytes = gemv_kernel_leg(model, provider, args.gemv_impl, name=kernel_name)
     achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
     step_bytes, verify_bytes = model.step_bytes(context)
-    ms_per_step = ms_value / args.steps
+    ms_per_step = ms_value / (args.steps * args.streams)   # per step of one stream
+    kernel_shape = model.layers[0].m[kernel_name]
+    metric = METRIC if not routed else "decode_tok_per_s_mtp4_q4h_8k_moe35b"
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
     value = tokens_a / (ms_value * 1e-3)
     e2e = tokens_b / (ms_e2e * 1e-3)
     line = {
-        "metric": METRIC if args.kv_encoding == "q4h" else METRIC.replace("q4h", "f16kv"), "value": value,
+        "metric": metric if args.kv_encoding == "q4h" else metric.replace("q4h", "f16kv"), "value": value,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
-        "config": {"workload": workload_name(context, args.kv_encoding),
-                   "layers": cfg["layers"], "parallelism": f"dp{world} replicas",
-                   "l2_policy": "inputs larger than L2 (16 GB streamed per step)",
+        "config": {"workload": workload_name(context, args.kv_encoding, args.model, args.streams),
+                   "layers": cfg["layers"], "parallelism": f"dp{world} replicas", "streams_per_gpu": args.streams,
+                   "l2_policy": f"inputs larger than L2 ({step_bytes / 1e9:.1f} GB streamed per step)",
                    "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",
                    "gemv_impl": "tcgen05" if args.gemv_impl == 1 else "dp4a",
                    "launch": "per kernel" if args.no_graph else "CUDA graph per step"},
-        "accepted_len_per_step": tokens_a / (args.steps * world),
-        "tok_s_if_all_drafts_accepted": 5.0 * args.steps * world / (ms_value * 1e-3),
+        "accepted_len_per_step": tokens_a / (args.steps * args.streams * world),
+        "tok_s_if_all_drafts_accepted": 5.0 * args.steps * args.streams * world / (ms_value * 1e-3),
         "step_algorithmic_gb": step_bytes / 1e9, "step_gbs": step_gbs, "step_frac_of_hbm": step_gbs / hbm_peak,
-        "roofline": {"bound": "hbm", "kernel": "nvfp4_gemv gate_up 34816x5120 M=5", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": f"nvfp4_gemv {kernel_name} {kernel_shape.rows}x{kernel_shape.cols} M=5",
+                     "achieved": achieved,
                      "peak": hbm_peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": GATE_UP_DRAM_BYTES_NCU if args.gemv_impl == 1 else None,
+                     "traffic": GATE_UP_DRAM_BYTES_NCU if args.gemv_impl == 1 and not routed else None,
                      "algorithmic_bytes": kernel_bytes, "kernel_ms": kernel_ms},
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 56,
-                "ms_per_step": ms_e2e / args.steps},
+                "ms_per_step": ms_e2e / (args.steps * args.streams)},
         "sampled_t0.7_top_p0.95_top_k20": {"value": tokens_c / (ms_sampled * 1e-3), "unit": "tok/s",
-                                           "ms_per_step": ms_sampled / sampled_steps, "steps": sampled_steps},
-        "gpu_launches": int(launches_per_step * args.steps),
+                                           "ms_per_step": ms_sampled / (sampled_steps * args.streams),
+                                           "steps": sampled_steps},
+        "gpu_launches": int(launches_per_step * args.steps * args.streams),
         "clocks": clocks.summary(),
     }
     if not args.no_cpu_baseline:

@@ -560,10 +560,10 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
     const int rc = launch_attention_q8_mma(a, part.maxima, part.sums, part.outputs, a.error, stream);
     if (rc) return rc;
   } else if (a.impl == 1) {
-    if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 32U || a.query_row_stride % 4U ||
+    if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 64U || a.query_row_stride % 4U ||
         a.page_tokens % 64U || a.split_tokens % 64U)
       return fail(QLLM_INVALID_ARGUMENT,
-                  "tensor-core attention needs Q4H, head_dim 128, rows*group <= 32, 64-token aligned pages and splits");
+                  "tensor-core attention needs Q4H, head_dim 128, rows*group <= 64, 64-token aligned pages and splits");
     const int rc = launch_attention_q4h_pipelined(a, part.maxima, part.sums, part.outputs, a.error, stream);
     if (rc) return rc;
   } else {

@@ -5,8 +5,8 @@
 // FP32 accumulation, online softmax over tiles of 32 keys.
 //
 // Cache layout: [K: page_tokens * kv_heads * head_dim f16][V: ...], token-major, so the record
-// of one (token, kv head) is 256 contiguous bytes.  CTA = (kv head, context split), two warps =
-// the two 16-row matrix tiles of a kv head (matrix row = verify row * group + grouped head).
+// of one (token, kv head) is 256 contiguous bytes.  CTA = (kv head, context split), one warp per
+// 16-row matrix tile of a kv head (matrix row = verify row * group + grouped head, up to 64).
 // A tile of 32 keys is 64 bulk asynchronous copies of 256 bytes (one per record, issued by the
 // 32 lanes of warp 0) into rows padded to 272 bytes, which makes every ldmatrix of the tile free
 // of bank conflicts; three stages on an mbarrier ring.  No value passes through a conversion:
@@ -91,7 +91,7 @@ struct F16Partials {
 };
 
 // grid (kv heads, context splits), block 64; dynamic shared memory kStages * kStageBytes.
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(128)
 attention_f16_mma_kernel(AttentionArgs a, F16Partials part, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
@@ -118,7 +118,7 @@ attention_f16_mma_kernel(AttentionArgs a, F16Partials part, uint32_t* error) {
   if (tid == 0U) {
     for (uint32_t s = 0; s < kStages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&full_bar[s])), "r"(1U));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&empty_bar[s])), "r"(2U));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&empty_bar[s])), "r"(blockDim.x >> 5U));
     }
     abort_word = 0U;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -305,7 +305,7 @@ attention_f16_mma_kernel(AttentionArgs a, F16Partials part, uint32_t* error) {
 
 bool attention_f16_mma_supported(const AttentionArgs& a) {
   const uint32_t group = a.kv_heads ? a.q_heads / a.kv_heads : 0U;
-  return a.encoding == QLLM_KV_F16 && a.head_dim == HD && a.kv_heads && group && a.rows * group <= 32U &&
+  return a.encoding == QLLM_KV_F16 && a.head_dim == HD && a.kv_heads && group && a.rows * group <= 64U &&
          a.page_tokens % kTile == 0U && a.split_tokens % kTile == 0U && a.query_row_stride % 2U == 0U;
 }
 
@@ -322,7 +322,8 @@ int launch_attention_f16_mma(const AttentionArgs& a, float* maxima, float* sums,
     if (e != cudaSuccess) return check_cuda(e, "F16 attention shared memory opt-in");
     configured[device & 63] = true;
   }
-  return check_cuda(launch_ordered(attention_f16_mma_kernel, dim3(a.kv_heads, a.max_splits), dim3(64), smem, stream, a,
+  const uint32_t mtiles = (a.rows * (a.q_heads / a.kv_heads) + 15U) / 16U;  // one warp per 16 matrix rows
+  return check_cuda(launch_ordered(attention_f16_mma_kernel, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), smem, stream, a,
                                    part, error), "attention_f16_mma");
 }
 

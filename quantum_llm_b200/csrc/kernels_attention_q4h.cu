@@ -1,8 +1,8 @@
 // Flash-decode attention over the Q4H (int4 codes + f16 scale per head) paged cache with the
 // dequantisation fused into the kernel, head_dim 128.
 //
-// CTA = (kv head, context split), two warps: warp w owns matrix rows 16w..16w+15
-// (matrix row = verify row * group + grouped head, up to 32).  K/V codes and scales of 64 keys
+// CTA = (kv head, context split), one warp per 16 matrix rows: warp w owns rows 16w..16w+15
+// (matrix row = verify row * group + grouped head, up to 64 = four warps).  K/V codes and scales of 64 keys
 // at a time are staged into shared memory by bulk asynchronous copies (the records of one kv
 // head are contiguous inside a page) through a 4-stage mbarrier ring, so HBM latency is hidden
 // behind the tensor-core work.  Per 32 keys, as in the reference
@@ -223,14 +223,14 @@ struct Q4hPartials {
   float* outputs;
 };
 
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(128)
 attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* error) {
   __shared__ __align__(128) uint8_t ring[kStages][kStageBytes];
   // staging of in-kernel quantised queries (callers without ready-made INT8 queries): lives in
   // the last pipeline stage, which is not filled before the queries are in registers
-  int8_t (*qs)[HD + 16] = reinterpret_cast<int8_t (*)[HD + 16]>(&ring[kStages - 1U][0]);
-  float* qscale_s = reinterpret_cast<float*>(&ring[kStages - 1U][32U * (HD + 16U)]);
-  static_assert(32U * (HD + 16U) + 32U * sizeof(float) <= kStageBytes, "query staging must fit one stage");
+  int8_t (*qs)[HD + 16] = reinterpret_cast<int8_t (*)[HD + 16]>(&ring[kStages - 2U][0]);
+  float* qscale_s = reinterpret_cast<float*>(&ring[kStages - 2U][64U * (HD + 16U)]);
+  static_assert(64U * (HD + 16U) + 64U * sizeof(float) <= 2U * kStageBytes, "query staging must fit two stages");
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
   __shared__ uint32_t abort_word;
   pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
@@ -254,7 +254,7 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
   if (tid == 0U) {
     for (uint32_t s = 0; s < kStages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&full_bar[s])), "r"(1U));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&empty_bar[s])), "r"(2U));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&empty_bar[s])), "r"(blockDim.x >> 5U));
     }
     abort_word = 0U;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -431,7 +431,8 @@ int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float*
   Q4hPartials part{maxima, sums, outputs};
   // Ordinary stream order on purpose: started early, the thousand CTAs of this grid (and, behind
   // them, those of the next GEMVs) sit on the SMs waiting; measured 0.5 ms per step slower.
-  return check_cuda(launch_ordered(attention_q4h_pipelined_kernel, dim3(a.kv_heads, a.max_splits), dim3(64), 0, stream,
+  const uint32_t mtiles = (a.rows * (a.q_heads / a.kv_heads) + 15U) / 16U;  // one warp per 16 matrix rows
+  return check_cuda(launch_ordered(attention_q4h_pipelined_kernel, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), 0, stream,
                                    a, part, error), "attention_q4h");
 }
 

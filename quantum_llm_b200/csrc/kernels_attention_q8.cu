@@ -302,7 +302,7 @@ attention_q8_mma_kernel(AttentionArgs a, Q8Partials part, uint32_t* error) {
 bool attention_q8_mma_supported(const AttentionArgs& a) {
   const uint32_t group = a.kv_heads ? a.q_heads / a.kv_heads : 0U;
   return a.encoding == QLLM_KV_Q8 && a.head_dim == HD && a.kv_heads && a.kv_heads <= 8U && group &&
-         a.rows * group <= 32U && a.page_tokens % kTile == 0U && a.split_tokens % kTile == 0U &&
+         a.rows * group <= 64U && a.page_tokens % kTile == 0U && a.split_tokens % kTile == 0U &&
          a.query_row_stride % 4U == 0U;
 }
 

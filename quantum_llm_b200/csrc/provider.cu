@@ -396,7 +396,7 @@ struct qllm_provider {
                             first_position, position_offset, rotary_offset, st.page_table, layer_offset,
                             c.page_tokens, enc, bf};
     const bool tensor_attention = attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
-                                  rows * (c.q_heads / c.kv_heads) <= 32U;
+                                  rows * (c.q_heads / c.kv_heads) <= 64U;
     rs.q8_out = tensor_attention ? q8.p : nullptr;
     rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
     ok(launch_rope_kv_store_fused(rs, stream));

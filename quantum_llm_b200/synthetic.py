@@ -21,6 +21,15 @@ DENSE_27B = dict(layers=64, hidden=5120, q_heads=40, kv_heads=8, head_dim=128, f
                  max_context=33792, split_tokens=512)
 
 
+# 35B-A3B-class sparse target (48 layers, hidden 2048, 32q/4kv, head_dim 128, 128 routed experts of
+# width 768, 8 selected per token, no shared expert), Q4H target cache, Q8 draft cache.  `ffn` is
+# unused by a routed model (kept non-zero for buffer sizing).
+MOE_35B = dict(layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, ffn=768, vocab=151936,
+               draft_vocab=65536, rotary_dim=128, rope_theta=1e6, eps=1e-6, page_tokens=256,
+               kv_encoding=_l.KV_Q4H, mtp_kv_encoding=_l.KV_Q8, activation_bf16=1, draft_depth=4,
+               max_context=9216, split_tokens=256, experts=128, route_width=8, expert_ffn=768, route_scale=1.0)
+
+
 class DeviceMatrix:
     def __init__(self, codes, scales, weight_scale, rows, cols):
         self.codes, self.scales, self.weight_scale, self.rows, self.cols = codes, scales, weight_scale, rows, cols
@@ -65,8 +74,10 @@ class DeviceBlock:
         H, F = cfg["hidden"], cfg["ffn"]
         qkv_rows = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"]
         shapes = dict(qkv=(qkv_rows, H), o=(H, cfg["q_heads"] * cfg["head_dim"]), gate_up=(2 * F, H), down=(H, F))
+        self.experts = int(cfg.get("experts", 0))
+        names = self.SHAPES if not self.experts else ("qkv", "o")
         self.m = {}
-        for i, name in enumerate(self.SHAPES):
+        for i, name in enumerate(names):
             rows, cols = shapes[name]
             w = _random_rows(rows, cols, seed * 16 + i, device,
                              base_seed=None if base_seed is None else base_seed * 16 + i, noise=0.004)
@@ -74,13 +85,34 @@ class DeviceBlock:
             del w
         self.input_norm = torch.ones(H, dtype=torch.float32, device=device)
         self.post_norm = torch.ones(H, dtype=torch.float32, device=device)
+        if self.experts:
+            W = cfg["expert_ffn"]
+            base = None if base_seed is None else base_seed * 16
+            self.router = quantize(_random_rows(self.experts, H, seed * 16 + 4, device, std=0.2,
+                                                base_seed=None if base is None else base + 4, noise=0.004))
+            self.expert = {}
+            for j, (name, rows, cols) in enumerate((("gate", W, H), ("up", W, H), ("down", H, W))):
+                # one draw for all experts of a role, then one quantisation (own scale) per expert
+                w = _random_rows(self.experts * rows, cols, seed * 16 + 5 + j, device,
+                                 base_seed=None if base is None else base + 5 + j, noise=0.004)
+                self.expert[name] = [quantize(w[e * rows:(e + 1) * rows]) for e in range(self.experts)]
+                del w
 
     def c(self):
+        if not self.experts:
+            return _l.Block(self.input_norm.data_ptr(), self.m["qkv"].c(), self.m["o"].c(), self.post_norm.data_ptr(),
+                            self.m["gate_up"].c(), self.m["down"].c())
+        self._arrays = [(_l.Matrix * self.experts)(*[m.c() for m in self.expert[name]])
+                        for name in ("gate", "up", "down")]   # host descriptor arrays, kept alive here
         return _l.Block(self.input_norm.data_ptr(), self.m["qkv"].c(), self.m["o"].c(), self.post_norm.data_ptr(),
-                        self.m["gate_up"].c(), self.m["down"].c())
+                        _l.Matrix(), _l.Matrix(), self.router.c(), self._arrays[0], self._arrays[1], self._arrays[2])
 
     def nbytes(self):
-        return sum(x.nbytes() for x in self.m.values())
+        """Bytes one pass streams from this block (dense), or its attention + router part (routed)."""
+        return sum(x.nbytes() for x in self.m.values()) + (self.router.nbytes() if self.experts else 0)
+
+    def expert_nbytes(self):
+        return sum(self.expert[name][0].nbytes() for name in ("gate", "up", "down")) if self.experts else 0
 
 
 class DeviceModel:
@@ -131,10 +163,21 @@ class DeviceModel:
         draft = L.qllm_k_kv_layer_bytes(c["mtp_kv_encoding"], c["page_tokens"], c["kv_heads"], c["head_dim"])
         return target * c["layers"] // c["page_tokens"], draft // c["page_tokens"]
 
+    def expected_distinct_experts(self, rows):
+        """Expected number of distinct experts `rows` tokens touch under uniform routing."""
+        e, k = self.cfg.get("experts", 0), self.cfg.get("route_width", 0)
+        return e * (1.0 - (1.0 - k / e) ** rows) if e else 0.0
+
     def step_bytes(self, context):
         """Algorithmic bytes of one MTP-4 step at `context` cached tokens: one verify pass
-        (all layer weights + head + target cache) and draft_depth draft passes."""
+        (all layer weights + head + target cache) and draft_depth draft passes.  For a routed
+        model the expert bytes of a pass are those of the distinct experts its rows touch
+        (expectation under uniform routing: 5 rows in the verify pass, 1 in a draft pass)."""
         target_kv, draft_kv = self.kv_bytes_per_token()
         verify = self.verify_weight_bytes() + target_kv * context
         draft = self.draft_pass_weight_bytes() + draft_kv * context
+        if self.cfg.get("experts", 0):
+            per_expert = self.layers[0].expert_nbytes()
+            verify += int(self.cfg["layers"] * per_expert * self.expected_distinct_experts(5))
+            draft += int(per_expert * self.expected_distinct_experts(1))
         return verify + self.cfg["draft_depth"] * draft, verify

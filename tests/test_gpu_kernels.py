@@ -181,6 +181,7 @@ def _filled_cache(enc, hd, kv, pt, tokens, rng, layers=1):
 
 @pytest.mark.parametrize("enc,impl,qh,kv,hd", [
     (ob.KV_Q4H, 0, 10, 2, 128), (ob.KV_Q4H, 1, 10, 2, 128), (ob.KV_Q4H, 1, 8, 8, 128),
+    (ob.KV_Q4H, 1, 16, 2, 128), (ob.KV_Q8, 1, 16, 2, 128), (ob.KV_F16, 1, 16, 2, 128),  # group 8: 40 matrix rows
     (ob.KV_Q4H, 0, 12, 2, 256),  # the reference's own smoke geometry: head_dim 256, group 6
     (ob.KV_Q8, 0, 10, 2, 128), (ob.KV_Q8, 1, 10, 2, 128), (ob.KV_Q8, 1, 40, 8, 128),
     (ob.KV_F16, 0, 4, 2, 64), (ob.KV_F16, 0, 10, 2, 128), (ob.KV_F16, 1, 10, 2, 128), (ob.KV_F16, 1, 40, 8, 128)])
