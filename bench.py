@@ -9,7 +9,9 @@ invocation cursor uploaded and the result record read back every step.
 N>1 runs N independent replicas (one stream per GPU, data parallel, no collective).
 `--model moe35b` runs the same step on the 35B-A3B-class routed model (48 layers, 128 experts,
 8 per token) at 8192 cached tokens; `--streams S` steps S independent requests in turn on each
-GPU (their rows are not batched into one pass).
+GPU (their rows are not batched into one pass).  `--parallelism tp` shards ONE stream's model
+over the N GPUs instead (q/k/v heads and FFN columns per rank, partial sums of the o and down
+projections exchanged through peer memory inside the GEMV kernel).
 
   python bench.py --gpus N --steps K --warmup W [--impl reference]
 """
@@ -46,6 +48,9 @@ def parse():
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
     ap.add_argument("--model", default="dense27b", choices=["dense27b", "moe35b"],
                     help="dense27b: the headline workload; moe35b: the routed 35B-A3B-class target")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N > 1: dp = N independent replicas (weak scaling, the default); tp = ONE stream whose "
+                         "model is sharded over the N GPUs (tensor parallel, strong scaling; dense27b, N = 2 or 4)")
     ap.add_argument("--streams", type=int, default=1, help="independent requests per GPU, stepped in turn")
     ap.add_argument("--context", type=int, default=0, help="cached tokens (0: 32768 dense, 8192 routed)")
     ap.add_argument("--kv-encoding", default="q4h", choices=["q4h", "f16"],
@@ -297,6 +302,10 @@ def ours(args):
 
     routed = args.model == "moe35b"
     cfg = dict(MOE_35B if routed else DENSE_27B)
+    tensor_parallel = args.parallelism == "tp" and world > 1
+    assert not (tensor_parallel and (routed or args.gemv_impl != 1)), "tensor parallelism: dense27b, tcgen05 GEMV"
+    # tensor parallel: every rank works on the same request (same seeds); replicas: one per rank
+    replica = 0 if tensor_parallel else rank
     if args.small:
         cfg["layers"] = 4
     context = args.context
@@ -308,10 +317,15 @@ def ours(args):
         cfg["kv_encoding"] = _ql.KV_F16
     steps_total = args.warmup + 2 * args.steps + 32
     assert context + 5 * steps_total + 16 < cfg["max_context"], "too many steps for the context reserve"
-    model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
-    provider = model.provider()
+    if tensor_parallel:
+        model = DeviceModel(cfg, seed=0, device=f"cuda:{local}", tp=(rank, world))
+        provider = model.tensor_parallel_provider()
+        dist.barrier()   # every rank has mapped its peers' exchange areas
+    else:
+        model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
+        provider = model.provider()
     provider.set_gemv_impl(args.gemv_impl)
-    request = RequestParameters(sampling_seed=1 + rank, sampling_temperature_ppm=0,
+    request = RequestParameters(sampling_seed=1 + replica, sampling_temperature_ppm=0,
                                 reserved_context_tokens=cfg["max_context"])
     synthetic = context - REAL_PREFILL
 
@@ -320,7 +334,7 @@ def ours(args):
         def __init__(self, index):
             # prompt: seeded uniform ids; the first context-REAL_PREFILL positions are represented by
             # seeded synthetic cache records, the tail goes through the real prefill + draft priming
-            seed = 1 + rank * args.streams + index
+            seed = 1 + replica * args.streams + index
             prompt = np.random.default_rng(seed).integers(0, cfg["vocab"], context, dtype=np.uint32)
             self.state = provider.create_request_state()
             provider.fill_synthetic_kv(self.state, 0, synthetic, seed=1233 + seed)
@@ -389,7 +403,7 @@ def ours(args):
     ms_e2e = start.elapsed_time(stop)
     # ---- the same step with temperature rejection sampling (T 0.7, top-p 0.95, top-k 20):
     # exact top-k of the 5 logits rows, device-side acceptance/residual sampling
-    sampled = RequestParameters(sampling_seed=1 + rank, sampling_temperature_ppm=700000, sampling_top_p_ppm=950000,
+    sampled = RequestParameters(sampling_seed=1 + replica, sampling_temperature_ppm=700000, sampling_top_p_ppm=950000,
                                 sampling_top_k=20, sampling_min_p_ppm=0, reserved_context_tokens=cfg["max_context"])
     sampled_steps = min(16, args.steps)
     tokens_c = 0
@@ -407,8 +421,12 @@ def ours(args):
 
     (ms_value, ms_e2e, ms_sampled), (tokens_a, tokens_b, accepted_a, tokens_c) = reduce_over_ranks(
         [ms_value, ms_e2e, ms_sampled], [tokens_a, tokens_b, accepted_a, tokens_c], f"cuda:{local}")
+    if tensor_parallel:   # every rank emitted the same tokens: count them once
+        tokens_a, tokens_b, accepted_a, tokens_c = (x / world for x in (tokens_a, tokens_b, accepted_a, tokens_c))
+    jobs = 1 if tensor_parallel else world
     if rank != 0:
         if world > 1:
+            dist.barrier()   # tensor parallel: no rank unmaps its exchange area while a peer may still run
             dist.destroy_process_group()
         return
 
@@ -435,16 +453,19 @@ def ours(args):
     line = {
         "metric": metric if args.kv_encoding == "q4h" else metric.replace("q4h", "f16kv"), "value": value,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if tensor_parallel else "weak",
         "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32", "data": "synthetic",
         "config": {"workload": workload_name(context, args.kv_encoding, args.model, args.streams),
-                   "layers": cfg["layers"], "parallelism": f"dp{world} replicas", "streams_per_gpu": args.streams,
+                   "layers": cfg["layers"],
+                   "parallelism": f"tp{world}: one stream, model sharded over {world} GPUs" if tensor_parallel
+                   else f"dp{world} replicas", "streams_per_gpu": args.streams,
                    "l2_policy": f"inputs larger than L2 ({step_bytes / 1e9:.1f} GB streamed per step)",
                    "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",
                    "gemv_impl": "tcgen05" if args.gemv_impl == 1 else "dp4a",
                    "launch": "per kernel" if args.no_graph else "CUDA graph per step"},
-        "accepted_len_per_step": tokens_a / (args.steps * args.streams * world),
-        "tok_s_if_all_drafts_accepted": 5.0 * args.steps * args.streams * world / (ms_value * 1e-3),
+        "accepted_len_per_step": tokens_a / (args.steps * args.streams * jobs),
+        "tok_s_if_all_drafts_accepted": 5.0 * args.steps * args.streams * jobs / (ms_value * 1e-3),
         "step_algorithmic_gb": step_bytes / 1e9, "step_gbs": step_gbs, "step_frac_of_hbm": step_gbs / hbm_peak,
         "roofline": {"bound": "hbm", "kernel": f"nvfp4_gemv {kernel_name} {kernel_shape.rows}x{kernel_shape.cols} M=5",
                      "achieved": achieved,
@@ -459,6 +480,8 @@ def ours(args):
         "gpu_launches": int(launches_per_step * args.steps * args.streams),
         "clocks": clocks.summary(),
     }
+    if tensor_parallel:
+        line["step_bytes_scope"] = "per GPU: this rank's shard of the blocks and of the KV, plus the replicated heads"
     if not args.no_cpu_baseline:
         sample = CpuSample()
         per_pass, passes, elapsed = sample.time(12.0)
@@ -467,6 +490,7 @@ def ours(args):
                                 "sample": f"{sample.description}; {passes} passes in {elapsed:.1f} s"}
     print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

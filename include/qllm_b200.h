@@ -186,6 +186,26 @@ int qllm_provider_set_gemv_impl(qllm_provider* provider, int impl);
  * (Q4H and Q8 caches, head_dim 128), 0 = the order-independent scalar kernel everywhere. */
 int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
 
+/* Tensor-parallel verify (no reference counterpart: the reference runs one GPU per model; the
+ * sharding follows its projection layout, runtime/tools/dense_fp4_provider.cpp:6189-6278).
+ * One process per GPU, each with a provider over ITS shard: config.q_heads / kv_heads / ffn are
+ * the local counts (global / ranks), qkv holds the rank's q, k and v head rows, gate_up its gate
+ * and up rows, o and down its K columns (a slice of the same quantised tensor: one weight_scale
+ * for all ranks); embedding, norms, heads and the fusion projection are replicated.  The o and
+ * down projections then exchange FP32 partial sums through peer memory inside the GEMV kernel,
+ * and every rank computes identical rows, tokens and acceptance decisions.
+ *   1. every rank: qllm_provider_tp_export(provider, rank, ranks, handle)  -- allocates the
+ *      rank's exchange area and returns its inter-process handle (QLLM_TP_HANDLE_BYTES bytes);
+ *   2. the host exchanges the handles (all-gather in rank order);
+ *   3. every rank: qllm_provider_tp_attach(provider, all_handles)  -- maps the peers' areas.
+ * Needs the tensor-core GEMV (qllm_provider_set_gemv_impl(1)), K of the local o and down
+ * projections a multiple of 256, and peer access between the GPUs.  ranks == 1 runs the same
+ * code path without peers.  A peer that does not deliver within 2 s sets the provider's kernel
+ * error word (the step fails with QLLM_INTERNAL); nothing waits without a limit. */
+#define QLLM_TP_HANDLE_BYTES 64
+int qllm_provider_tp_export(qllm_provider* provider, uint32_t rank, uint32_t ranks, void* handle);
+int qllm_provider_tp_attach(qllm_provider* provider, const void* handles);
+
 /* inspection for parity tests (device -> host copies) */
 int qllm_provider_read_logits(qllm_provider* provider, float* out, uint32_t rows);
 /* which = 0: rows retained by the last prefill chunk; 1: target rows of the last exact step. */

@@ -29,6 +29,21 @@ struct MmaWeights {
   ~MmaWeights() { release(); }
 };
 
+// Tensor-parallel exchange of a K-split projection: every CTA of the GEMV stores its partial
+// sums into the same inbox slot of every rank (its own through the local pointer, the peers'
+// through their mapped memory), and the last CTA of the launch raises this rank's sequence
+// number in every peer's flag array.  The consumer sums all ranks' partials in rank order
+// (exchange_wait, quant.cuh), so every rank computes the same values.
+struct GemvExchange {
+  uint32_t ranks = 0, rank = 0;
+  float* inbox[8] = {};      // the slot of this exchange in every rank's inbox
+  uint32_t* flags[8] = {};   // every rank's flag array [ranks]
+  uint32_t* sequence = nullptr;  // local: exchanges produced so far
+  uint32_t* tickets = nullptr;   // local: CTAs of the running launch that have stored their part
+  uint32_t* error = nullptr;     // local error word of the consumers
+  size_t capacity_floats = 0;    // floats one slot holds
+};
+
 size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);
 // y[batch, row_count] = bf16(fakequant(x) . W[first_row .. first_row+row_count)^T)
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,

@@ -46,6 +46,7 @@ residual_norm_quant_kernel(NormQuantArgs a) {
     w[k] = (a.weight && f < end) ? reinterpret_cast<const float4*>(a.weight)[f] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
   }
   pdl_wait();
+  if (a.has_delta) exchange_wait(a.delta);  // tensor parallel: the peers' partial sums are part of delta
   const uint32_t in_row = a.row_select ? *a.row_select : out_row;
   // x == null: the row is the GEMV result alone (0 + delta is exact)
   const float4* x4 = a.x ? reinterpret_cast<const float4*>(a.x + static_cast<size_t>(in_row) * a.x_stride) : nullptr;

@@ -8,6 +8,8 @@
 //   per selection: gate = bf16(W1 . fq1(x)), up = bf16(W3 . fq3(x)) (each projection quantises
 //   its input with its own activation scale), mid = bf16(silu(gate) * up),
 //   out = bf16(W2 . fq2(mid)); moe = bf16(sum over the slots, in slot order, of score * out).
+// Three launches per layer: selection, gate/up (which also quantises mid for the down
+// projection), down fused with the weighted sum.
 // Dot products use the exact block arithmetic of the CUDA-core GEMV (integer block sums, block
 // terms summed in double), so the results do not depend on the launch shape.
 // Every selected expert's weights are streamed once per selection: the step is bound by
@@ -40,7 +42,11 @@ moe_router_select_kernel(GemvOut logits, uint32_t experts, uint32_t top_k, float
   uint32_t taken = 0U;  // bit i: this lane's i-th expert is already selected
   float chosen_value[8];
   uint32_t chosen_index[8];
-  for (uint32_t slot = 0; slot < top_k; ++slot) {
+#pragma unroll
+  for (uint32_t slot = 0; slot < 8U; ++slot) {
+    chosen_value[slot] = -INFINITY;
+    chosen_index[slot] = 0xffffffffU;
+    if (slot >= top_k) continue;
     float best = -INFINITY;
     uint32_t best_index = 0xffffffffU;
 #pragma unroll
@@ -61,143 +67,223 @@ moe_router_select_kernel(GemvOut logits, uint32_t experts, uint32_t top_k, float
     chosen_index[slot] = best_index;
     if (best_index != 0xffffffffU && (best_index & 31U) == lane) taken |= 1U << (best_index >> 5U);
   }
-  if (lane == 0U) {
-    float top = -INFINITY, sum = 0.0F, s[8];
-    for (uint32_t slot = 0; slot < top_k; ++slot) top = fmaxf(top, chosen_value[slot]);
-    for (uint32_t slot = 0; slot < top_k; ++slot) {
-      // exp in double, rounded once: the same FP32 value on the device and in a host check
-      s[slot] = static_cast<float>(exp(static_cast<double>(chosen_value[slot] - top)));
-      sum += s[slot];
-    }
-    for (uint32_t slot = 0; slot < top_k; ++slot) {
-      float v = s[slot] / sum;
-      if (route_scale != 1.0F) v *= route_scale;
-      scores[row * top_k + slot] = bf16r(v);
-      indices[row * top_k + slot] = chosen_index[slot];
-    }
+  // lane `slot` takes that slot's exponential (in double, rounded once: the same FP32 value on
+  // the device and in a host check); the sum runs in slot order on every lane
+  float top = -INFINITY, my_value = 0.0F;
+  uint32_t my_index = 0xffffffffU;
+#pragma unroll
+  for (uint32_t slot = 0; slot < 8U; ++slot) {
+    if (slot < top_k) top = fmaxf(top, chosen_value[slot]);
+    if (slot == lane) { my_value = chosen_value[slot]; my_index = chosen_index[slot]; }
+  }
+  const float mine = lane < top_k ? static_cast<float>(exp(static_cast<double>(my_value - top))) : 0.0F;
+  float sum = 0.0F;
+#pragma unroll
+  for (uint32_t slot = 0; slot < 8U; ++slot) {
+    const float term = __shfl_sync(0xffffffffU, mine, slot);
+    if (slot < top_k) sum += term;
+  }
+  if (lane < top_k) {
+    float v = mine / sum;
+    if (route_scale != 1.0F) v *= route_scale;
+    scores[row * top_k + lane] = bf16r(v);
+    indices[row * top_k + lane] = my_index;
   }
 }
 
 // ---- shared pieces of the two expert projections ---------------------------------------------
-// Quantises `count` FP32 values (count % 16 == 0) into INT8 + block scales in shared memory.
-__device__ __forceinline__ void quantize_row_to_shared(const float* __restrict__ x, uint32_t count, float g,
-                                                       bool round_bf16, int8_t* xi8, float* xscale) {
-  for (uint32_t blk = threadIdx.x; blk < count / 16U; blk += blockDim.x) {
-    float v[16];
-    const float4* in4 = reinterpret_cast<const float4*>(x + 16U * blk);
+// Quantises 16 FP32 values at `x16` into INT8 + a block scale, stored as block `blk` of the
+// destination row.
+__device__ __forceinline__ void quantize_block(const float* __restrict__ x16, float g, bool round_bf16, uint32_t blk,
+                                               int8_t* xi8, float* xscale) {
+  float v[16];
+  const float4* in4 = reinterpret_cast<const float4*>(x16);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 t = in4[i];
-      v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-    }
-    if (round_bf16) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = bf16r(v[i]);
-    }
-    uint4 packed;
-    float local;
-    quantize_block16_i8(v, g, packed, local);
-    reinterpret_cast<uint4*>(xi8)[blk] = packed;
-    xscale[blk] = local;
+  for (int i = 0; i < 4; ++i) {
+    const float4 t = in4[i];
+    v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
   }
+  if (round_bf16) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = bf16r(v[i]);
+  }
+  uint4 packed;
+  float local;
+  quantize_block16_i8(v, g, packed, local);
+  reinterpret_cast<uint4*>(xi8)[blk] = packed;
+  xscale[blk] = local;
 }
 
-// Exact sum over the blocks of one weight row against the quantised activations (warp-wide).
-__device__ __forceinline__ double row_dot(const ExpertMatrix& m, uint32_t row, uint32_t cols, const int8_t* xi8,
-                                          const float* xscale, uint32_t lane) {
+// Exact sums over the blocks of R consecutive weight rows against one quantised activation row.
+// A group of LANES lanes (16 or 32) strides the blocks of its rows; the loads of all R rows are
+// issued before the arithmetic.  Every lane of the group returns the full sums.
+template <int R, int LANES>
+__device__ __forceinline__ void rows_dot(const ExpertMatrix& m, uint32_t first_row, uint32_t last_row, uint32_t cols,
+                                         const int8_t* xi8, const float* xscale, uint32_t lane_in_group,
+                                         double (&acc)[R]) {
   const uint32_t blocks = cols / 16U;
-  const uint2* w = reinterpret_cast<const uint2*>(m.codes + static_cast<size_t>(row) * (cols / 2U));
-  const uint8_t* s = m.scales + static_cast<size_t>(row) * blocks;
-  double acc = 0.0;
-  for (uint32_t blk = lane; blk < blocks; blk += 32U) {
-    const int d = block16_dot(__ldg(w + blk), reinterpret_cast<const uint4*>(xi8)[blk]);
-    // exact: |d| < 2^12, the product of the two E4M3 scales has 8 significant bits
-    acc += static_cast<double>(static_cast<float>(d) * (e4m3_value(__ldg(s + blk)) * xscale[blk]) * 0.25F);
+  const uint2* w[R];
+  const uint8_t* s[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint32_t row = min(first_row + r, last_row);  // rows past the end repeat the last one (discarded)
+    w[r] = reinterpret_cast<const uint2*>(m.codes + static_cast<size_t>(row) * (cols / 2U));
+    s[r] = m.scales + static_cast<size_t>(row) * blocks;
+    acc[r] = 0.0;
   }
-  return warp_sum_f64(acc);
+#pragma unroll 2
+  for (uint32_t blk = lane_in_group; blk < blocks; blk += LANES) {
+    uint2 codes[R];
+    uint8_t scale[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      codes[r] = __ldg(w[r] + blk);
+      scale[r] = __ldg(s[r] + blk);
+    }
+    const uint4 xv = reinterpret_cast<const uint4*>(xi8)[blk];
+    const float xs = xscale[blk];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = block16_dot(codes[r], xv);
+      // exact: |d| < 2^12, the product of the two E4M3 scales has 8 significant bits
+      acc[r] += static_cast<double>(static_cast<float>(d) * (e4m3_value(scale[r]) * xs) * 0.25F);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffU, acc[r], o);
+  }
 }
 
-// ---- gate / up / SiLU: grid (ceil(expert_ffn / 8), selections), 8 warps = 8 output rows --------
+constexpr uint32_t kGateUpRows = 32;   // mid values per CTA of the gate/up kernel: two quantisation blocks
+// shared memory of one slot's quantised mid row in the down kernel (values + scales, 16-byte granules)
+__host__ __device__ inline uint32_t down_slot_bytes(uint32_t expert_ffn) {
+  return (expert_ffn + expert_ffn / 16U * 4U + 15U) & ~15U;
+}
+constexpr uint32_t kDownColumns = 16;  // hidden columns per CTA of the down kernel (one warp per slot)
+
+// ---- gate / up / SiLU: grid (ceil(expert_ffn / 32), selections), 8 warps x 4 output rows ----------
+// The CTA quantises the selection's input row once per projection (once for both when their
+// activation scales agree), every warp streams four gate rows and four up rows, and the CTA's
+// 32 mid values leave as two blocks already quantised for the down projection.
 __global__ void __launch_bounds__(256)
 moe_gate_up_kernel(MoeArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ __align__(16) float mid_tile[kGateUpRows];
   pdl_trigger();
   pdl_wait();
   const uint32_t selection = blockIdx.y, row = selection / a.route_width;
   const uint32_t expert = a.indices[selection];
   if (expert >= a.experts) return;  // the router found no candidate (non-finite logits): contributes nothing
-  const uint32_t H = a.hidden, blocks = H / 16U;
-  int8_t* gi8 = reinterpret_cast<int8_t*>(smem);
-  int8_t* ui8 = gi8 + H;
-  float* gscale = reinterpret_cast<float*>(ui8 + H);
-  float* uscale = gscale + blocks;
+  const uint32_t H = a.hidden, blocks = H / 16U, W = a.expert_ffn;
   const ExpertMatrix G = a.gate[expert], U = a.up[expert];
+  const bool shared_input = G.input_scale == U.input_scale;
+  int8_t* gi8 = reinterpret_cast<int8_t*>(smem);
+  int8_t* ui8 = shared_input ? gi8 : gi8 + H;
+  float* gscale = reinterpret_cast<float*>(gi8 + 2U * H);
+  float* uscale = shared_input ? gscale : gscale + blocks;
   const float* x = a.x + static_cast<size_t>(row) * a.x_stride;
-  quantize_row_to_shared(x, H, G.input_scale, true, gi8, gscale);
-  quantize_row_to_shared(x, H, U.input_scale, true, ui8, uscale);
+  for (uint32_t i = threadIdx.x; i < (shared_input ? blocks : 2U * blocks); i += blockDim.x) {
+    if (i < blocks) quantize_block(x + 16U * i, G.input_scale, true, i, gi8, gscale);
+    else quantize_block(x + 16U * (i - blocks), U.input_scale, true, i - blocks, ui8, uscale);
+  }
   __syncthreads();
   const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
-  const uint32_t out_row = blockIdx.x * 8U + warp;
-  if (out_row >= a.expert_ffn) return;
-  const double g = row_dot(G, out_row, H, gi8, gscale, lane);
-  const double u = row_dot(U, out_row, H, ui8, uscale, lane);
-  if (lane == 0U) {
-    const float gate = bf16r(static_cast<float>(g) * G.weight_scale / G.input_scale);
-    const float up = bf16r(static_cast<float>(u) * U.weight_scale / U.input_scale);
-    a.mid[static_cast<size_t>(selection) * a.expert_ffn + out_row] = bf16r((gate / (1.0F + expf(-gate))) * up);
+  const uint32_t first = blockIdx.x * kGateUpRows + warp * 4U;
+  double g[4], u[4];
+  rows_dot<4, 32>(G, first, W - 1U, H, gi8, gscale, lane, g);
+  rows_dot<4, 32>(U, first, W - 1U, H, ui8, uscale, lane, u);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (lane == static_cast<uint32_t>(r)) {
+      const float gate = bf16r(static_cast<float>(g[r]) * G.weight_scale / G.input_scale);
+      const float up = bf16r(static_cast<float>(u[r]) * U.weight_scale / U.input_scale);
+      mid_tile[warp * 4U + r] = bf16r((gate / (1.0F + expf(-gate))) * up);
+    }
   }
+  __syncthreads();
+  const uint32_t out_block = blockIdx.x * (kGateUpRows / 16U) + threadIdx.x;
+  if (threadIdx.x < kGateUpRows / 16U && out_block < W / 16U)
+    quantize_block(mid_tile + 16U * threadIdx.x, a.down[expert].input_scale, false, out_block,
+                   a.mid_i8 + static_cast<size_t>(selection) * W, a.mid_scale + static_cast<size_t>(selection) * (W / 16U));
 }
 
-// ---- down: grid (ceil(hidden / 8), selections) ---------------------------------------------------
+// ---- down + ordered weighted sum: grid (ceil(hidden / 16), rows), warp = slot ---------------------
+// Warp `slot` streams 16 rows of its slot's down projection against that slot's quantised mid row
+// (LANES = 16: a half warp per row, LANES = 32 when that leaves no lane idle); 16 threads then add
+// score * out over the slots in slot order.
+template <int LANES>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(MoeArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float out_tile[8][kDownColumns];
   pdl_trigger();
   pdl_wait();
-  const uint32_t selection = blockIdx.y;
-  const uint32_t expert = a.indices[selection];
-  const uint32_t W = a.expert_ffn, blocks = W / 16U;
-  const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
-  const uint32_t out_row = blockIdx.x * 8U + warp;
-  if (expert >= a.experts) {
-    if (out_row < a.hidden && lane == 0U) a.out[static_cast<size_t>(selection) * a.hidden + out_row] = 0.0F;
-    return;
+  constexpr uint32_t kGroups = 32U / LANES, kRows = 4U;  // kGroups * kRows columns per pass of a warp
+  const uint32_t row = blockIdx.y, W = a.expert_ffn, blocks = W / 16U, K = a.route_width;
+  const uint32_t slot = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
+  if (slot < K) {
+    const uint32_t selection = row * K + slot;
+    const uint32_t expert = a.indices[selection];
+    if (expert < a.experts) {
+      int8_t* mi8 = reinterpret_cast<int8_t*>(smem) + static_cast<size_t>(slot) * down_slot_bytes(W);
+      float* mscale = reinterpret_cast<float*>(mi8 + W);
+      const uint4* src = reinterpret_cast<const uint4*>(a.mid_i8 + static_cast<size_t>(selection) * W);
+      const float* src_scale = a.mid_scale + static_cast<size_t>(selection) * blocks;
+      for (uint32_t i = lane; i < blocks; i += 32U) {
+        reinterpret_cast<uint4*>(mi8)[i] = src[i];
+        mscale[i] = src_scale[i];
+      }
+      __syncwarp();
+      const ExpertMatrix D = a.down[expert];
+      const uint32_t group = lane / LANES, lane_in_group = lane % LANES;
+#pragma unroll
+      for (uint32_t pass = 0; pass < kDownColumns / (kGroups * kRows); ++pass) {
+        const uint32_t local = pass * kGroups * kRows + group * kRows;
+        double t[kRows];
+        rows_dot<kRows, LANES>(D, blockIdx.x * kDownColumns + local, a.hidden - 1U, W, mi8, mscale, lane_in_group, t);
+#pragma unroll
+        for (uint32_t r = 0; r < kRows; ++r)
+          if (lane_in_group == r) out_tile[slot][local + r] = bf16r(static_cast<float>(t[r]) * D.weight_scale / D.input_scale);
+      }
+    } else if (lane < kDownColumns) {
+      out_tile[slot][lane] = 0.0F;  // no candidate: contributes score * 0
+    }
   }
-  int8_t* mi8 = reinterpret_cast<int8_t*>(smem);
-  float* mscale = reinterpret_cast<float*>(mi8 + W);
-  const ExpertMatrix D = a.down[expert];
-  quantize_row_to_shared(a.mid + static_cast<size_t>(selection) * W, W, D.input_scale, false, mi8, mscale);
   __syncthreads();
-  if (out_row >= a.hidden) return;
-  const double t = row_dot(D, out_row, W, mi8, mscale, lane);
-  if (lane == 0U)
-    a.out[static_cast<size_t>(selection) * a.hidden + out_row] =
-        bf16r(static_cast<float>(t) * D.weight_scale / D.input_scale);
-}
-
-// ---- ordered weighted sum over the slots -------------------------------------------------------
-__global__ void __launch_bounds__(256)
-moe_aggregate_kernel(MoeArgs a) {
-  pdl_trigger();
-  pdl_wait();
-  const uint32_t index = blockIdx.x * blockDim.x + threadIdx.x;
-  if (index >= a.rows * a.hidden) return;
-  const uint32_t row = index / a.hidden, column = index % a.hidden;
-  float total = 0.0F;
-  for (uint32_t slot = 0; slot < a.route_width; ++slot) {
-    const size_t selection = static_cast<size_t>(row) * a.route_width + slot;
-    const float contribution = a.scores[selection] * a.out[selection * a.hidden + column];
-    total = total + contribution;
+  const uint32_t column = blockIdx.x * kDownColumns + threadIdx.x;
+  if (threadIdx.x < kDownColumns && column < a.hidden) {
+    float total = 0.0F;
+    for (uint32_t s = 0; s < K; ++s) {
+      const float contribution = a.scores[row * K + s] * out_tile[s][threadIdx.x];
+      total = total + contribution;
+    }
+    a.moe[static_cast<size_t>(row) * a.hidden + column] = bf16r(total);
   }
-  a.moe[index] = bf16r(total);
 }
 
 }  // namespace
 
+namespace {
+inline size_t round4(size_t n) { return (n + 3U) & ~static_cast<size_t>(3U); }  // 16-byte granules of floats
+}  // namespace
+
 size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn) {
   const size_t selections = static_cast<size_t>(rows) * route_width;
-  // scores | mid | out | moe, and the indices (same width as a float) in front
-  return 2U * selections + selections * expert_ffn + selections * hidden + static_cast<size_t>(rows) * hidden;
+  // indices | scores | quantised mid (INT8 values, then FP32 block scales) | moe
+  return round4(2U * selections) + round4(selections * (expert_ffn / 4U)) + round4(selections * (expert_ffn / 16U)) +
+         static_cast<size_t>(rows) * hidden;
+}
+
+void moe_carve_workspace(float* base, MoeArgs& a) {
+  const size_t selections = static_cast<size_t>(a.rows) * a.route_width;
+  a.indices = reinterpret_cast<uint32_t*>(base);
+  a.scores = base + selections;
+  float* mid = base + round4(2U * selections);
+  a.mid_i8 = reinterpret_cast<int8_t*>(mid);
+  a.mid_scale = mid + round4(selections * (a.expert_ffn / 4U));
+  a.moe = a.mid_scale + round4(selections * (a.expert_ffn / 16U));
 }
 
 int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream_t stream) {
@@ -211,20 +297,21 @@ int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream
 int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
   if (a.hidden % 16U || a.expert_ffn % 16U || a.x_stride % 4U || a.hidden > 16384U || a.expert_ffn > 16384U)
     return fail(QLLM_INVALID_ARGUMENT, "expert widths must be multiples of 16 (at most 16384)");
+  if (!a.route_width || a.route_width > 8U) return fail(QLLM_INVALID_ARGUMENT, "1..8 experts per token");
   const uint32_t selections = a.rows * a.route_width;
   const size_t smem_gu = 2U * (static_cast<size_t>(a.hidden) + a.hidden / 16U * sizeof(float));
-  const size_t smem_d = static_cast<size_t>(a.expert_ffn) + a.expert_ffn / 16U * sizeof(float);
+  const size_t smem_d = 8U * down_slot_bytes(a.expert_ffn);
   if (smem_gu > 48U * 1024U || smem_d > 48U * 1024U)
-    return fail(QLLM_INVALID_ARGUMENT, "expert input row does not fit the shared-memory staging");
-  int rc = check_cuda(launch_pdl(moe_gate_up_kernel, dim3((a.expert_ffn + 7U) / 8U, selections), dim3(256), smem_gu,
-                                 stream, a), "moe_gate_up");
+    return fail(QLLM_INVALID_ARGUMENT, "expert input rows do not fit the shared-memory staging");
+  int rc = check_cuda(launch_pdl(moe_gate_up_kernel, dim3((a.expert_ffn + kGateUpRows - 1U) / kGateUpRows, selections),
+                                 dim3(256), smem_gu, stream, a), "moe_gate_up");
   if (rc) return rc;
-  rc = check_cuda(launch_pdl(moe_down_kernel, dim3((a.hidden + 7U) / 8U, selections), dim3(256), smem_d, stream, a),
-                  "moe_down");
-  if (rc) return rc;
-  count_launch(3);
-  return check_cuda(launch_pdl(moe_aggregate_kernel, dim3((a.rows * a.hidden + 255U) / 256U), dim3(256), 0, stream, a),
-                    "moe_aggregate");
+  count_launch(2);
+  const dim3 grid((a.hidden + kDownColumns - 1U) / kDownColumns, a.rows);
+  // 32 lanes per column only when that leaves no lane idle
+  if ((a.expert_ffn / 16U) % 32U == 0U)
+    return check_cuda(launch_pdl(moe_down_kernel<32>, grid, dim3(256), smem_d, stream, a), "moe_down");
+  return check_cuda(launch_pdl(moe_down_kernel<16>, grid, dim3(256), smem_d, stream, a), "moe_down");
 }
 
 }  // namespace qllm

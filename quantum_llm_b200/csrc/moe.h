@@ -28,16 +28,19 @@ struct MoeArgs {
   const ExpertMatrix* gate;  // [experts], each [expert_ffn, hidden]
   const ExpertMatrix* up;    // [experts], each [expert_ffn, hidden]
   const ExpertMatrix* down;  // [experts], each [hidden, expert_ffn]
-  float* mid;              // [rows * route_width, expert_ffn]
-  float* out;              // [rows * route_width, hidden]
+  int8_t* mid_i8;          // [rows * route_width, expert_ffn] mid quantised for the down projection
+  float* mid_scale;        // [rows * route_width, expert_ffn / 16] its block scales
   float* moe;              // [rows, hidden] BF16-rounded weighted sum (added to the residual by the next norm)
 };
 
-// floats of workspace for indices, scores, mid, out and moe together
+// floats of workspace for indices, scores, quantised mid and moe together (16-byte aligned parts)
 size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn);
+// points indices, scores, mid_i8, mid_scale and moe of `a` (rows, route_width, expert_ffn set)
+// into a workspace of that size
+void moe_carve_workspace(float* base, MoeArgs& a);
 // top-K selection + normalised scores from the router GEMV result
 int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream_t stream);
-// gate/up/SiLU, down and the ordered weighted sum (three launches)
+// gate/up/SiLU, then down with the ordered weighted sum (two launches)
 int launch_moe_experts(const MoeArgs& a, cudaStream_t stream);
 
 }  // namespace qllm

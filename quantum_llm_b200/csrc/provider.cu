@@ -146,6 +146,15 @@ struct qllm_provider {
   DeviceBuffer<int8_t> q8;  // INT8 copy of the rotated queries for the Q4H attention
   DeviceBuffer<float> partial_buf, gemv_out;   // tensor-core split-K partials / CUDA-core results
   DeviceBuffer<float> moe_x, moe_ws;           // routed experts: normalised input rows, selection workspace
+  // Tensor parallelism (qllm_provider_tp_export / _attach): this provider holds one rank's shard
+  // (local head and FFN counts in cfg); the K-split projections (o, down) exchange partial sums.
+  // Shared area of a rank: [flags: 64 x u32][slot 0][slot 1], slot = ranks x tp_slot_floats.
+  uint32_t tp_ranks = 0, tp_rank = 0;
+  uint8_t* tp_area = nullptr;                  // this rank's area (cudaMalloc, exported to the peers)
+  uint8_t* tp_peer[8] = {};                    // every rank's area as mapped here (own = tp_area)
+  bool tp_attached = false;
+  size_t tp_slot_floats = 0;
+  DeviceBuffer<uint32_t> tp_words;             // [0] sequence, [1] tickets
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
@@ -298,6 +307,9 @@ struct qllm_provider {
   }
 
   ~qllm_provider() {
+    for (uint32_t r = 0; r < tp_ranks; ++r)
+      if (tp_peer[r] && tp_peer[r] != tp_area) cudaIpcCloseMemHandle(tp_peer[r]);
+    if (tp_area) cudaFree(tp_area);
     for (void* p : owned) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
   }
@@ -310,13 +322,35 @@ struct qllm_provider {
   QuantSink sink_for(const Matrix& w, uint32_t rows) {
     return make_sink(impl_for(w), quant_buf.p, rows, w.m.cols, w.m.input_scale);
   }
-  GemvOut gemv(const Matrix& w, uint32_t rows, uint32_t row_count = 0, float* final_out = nullptr) {
+  // `exchange_slot` (0 or 1) marks a K-split projection of a tensor-parallel rank: its partial
+  // sums are exchanged with the peers.  o uses slot 0 and down slot 1, so that a rank that runs
+  // ahead never writes the slot a slower peer is still reading (it cannot get two exchanges ahead:
+  // every exchange is consumed, which needs the peers' parts, before the next but one is produced).
+  GemvOut gemv(const Matrix& w, uint32_t rows, uint32_t row_count = 0, float* final_out = nullptr,
+               int exchange_slot = -1) {
     if (!row_count) row_count = w.m.rows;
     GemvOut o{};
+    GemvExchange x{};
+    const bool exchange = tp_ranks != 0U && exchange_slot >= 0;
+    if (exchange) {
+      if (!tp_attached) throw Error(QLLM_INVALID_ARGUMENT, "tensor-parallel provider used before qllm_provider_tp_attach");
+      x.ranks = tp_ranks;
+      x.rank = tp_rank;
+      for (uint32_t r = 0; r < tp_ranks; ++r) {
+        x.flags[r] = reinterpret_cast<uint32_t*>(tp_peer[r]);
+        x.inbox[r] = reinterpret_cast<float*>(tp_peer[r] + kTpFlagBytes) +
+                     static_cast<size_t>(exchange_slot) * tp_ranks * tp_slot_floats;
+      }
+      x.sequence = tp_words.p;
+      x.tickets = tp_words.p + 1;
+      x.error = kernel_error.p;
+      x.capacity_floats = static_cast<size_t>(tp_ranks) * tp_slot_floats;
+    }
     ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
-                        final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream));
+                        final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream, exchange ? &x : nullptr));
     return o;
   }
+  static constexpr size_t kTpFlagBytes = 256;
   // x' = act(x + delta) stored to `store`; operand of `next` = quantised rmsnorm(x') * weight
   void norm_quant(const float* x, uint32_t x_stride, const GemvOut* delta, float* store, const float* weight,
                   const Matrix* next, uint32_t rows, uint32_t sink_block_offset = 0,
@@ -349,7 +383,6 @@ struct qllm_provider {
     const auto& c = cfg;
     norm_quant(h, c.hidden, &attention_out, h, b.post_norm, &b.router, rows, 0U, nullptr, moe_x.p, true);
     const GemvOut logits = gemv(b.router, rows);
-    const size_t selections = static_cast<size_t>(rows) * c.route_width;
     MoeArgs a{};
     a.x = moe_x.p;
     a.x_stride = c.hidden;
@@ -359,11 +392,7 @@ struct qllm_provider {
     a.route_width = c.route_width;
     a.expert_ffn = c.expert_ffn;
     a.route_scale = c.route_scale;
-    a.indices = reinterpret_cast<uint32_t*>(moe_ws.p);
-    a.scores = moe_ws.p + selections;
-    a.mid = a.scores + selections;
-    a.out = a.mid + selections * c.expert_ffn;
-    a.moe = a.out + selections * c.hidden;
+    moe_carve_workspace(moe_ws.p, a);
     a.gate = b.expert_gate;
     a.up = b.expert_up;
     a.down = b.expert_down;
@@ -442,7 +471,7 @@ struct qllm_provider {
     cb.out = nullptr;
     cb.sink = sink_for(b.o, rows);
     ok(launch_combine_quant(cb, rows, stream));
-    const GemvOut o_out = gemv(b.o, rows);
+    const GemvOut o_out = gemv(b.o, rows, 0U, nullptr, 0);
     if (c.experts) {
       routed_experts(b, h, o_out, rows, pending);
       return;
@@ -450,7 +479,7 @@ struct qllm_provider {
     norm_quant(h, c.hidden, &o_out, h, b.post_norm, &b.gate_up, rows);
     const GemvOut gu = gemv(b.gate_up, rows);
     ok(launch_silu_quant(gu, c.ffn, bf, sink_for(b.down, rows), nullptr, stream));
-    *pending = gemv(b.down, rows);
+    *pending = gemv(b.down, rows, 0U, nullptr, 1);
   }
 
   uint32_t splits_for(uint32_t tokens) const {
@@ -502,7 +531,11 @@ struct qllm_provider {
     // the draft block runs in its own residual buffer, so the target's rows stay readable
     block(mtp_block, mtp_hidden.p, false, &pending, true, rows, c.mtp_kv_encoding, layer_off[c.layers], st,
           first_position, position_offset, 1U, splits);
-    if (!produce) return;
+    if (!produce) {
+      // a tensor-parallel rank still takes delivery of the last exchange (see gemv())
+      if (tp_ranks > 1U) norm_quant(mtp_hidden.p, c.hidden, &pending, mtp_hidden.p, nullptr, nullptr, rows);
+      return;
+    }
     // residual add of the selected row, kept as the chained passes' previous hidden, then the
     // draft norm and the head over the draft vocabulary
     norm_quant(mtp_hidden.p, c.hidden, &pending, st.mtp_last_hidden, mtp_draft_norm, &head, 1U, 0U, select_row);
@@ -891,6 +924,53 @@ int qllm_provider_set_gemv_impl(qllm_provider* p, int impl) {
   if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown GEMV implementation");
   p->gemv_impl = impl;
   return QLLM_OK;
+}
+
+int qllm_provider_tp_export(qllm_provider* p, uint32_t rank, uint32_t ranks, void* handle) {
+  if (!p || !handle || !ranks || ranks > 8U || rank >= ranks)
+    return fail(QLLM_INVALID_ARGUMENT, "tensor parallelism needs 1..8 ranks and a handle buffer");
+  if (p->tp_area) return fail(QLLM_INVALID_ARGUMENT, "the exchange area of this provider exists already");
+  if (p->cfg.experts) return fail(QLLM_INVALID_ARGUMENT, "tensor parallelism is built for the dense model only");
+  return guarded([&] {
+    const auto& c = p->cfg;
+    cu(cudaSetDevice(p->device), "select device");
+    // one slot holds every rank's partials of the larger of the two K-split projections
+    const size_t per_rank = std::max(gemv_partial_floats(qllm_provider::kMaxRows, c.hidden, c.q_heads * c.head_dim),
+                                     gemv_partial_floats(qllm_provider::kMaxRows, c.hidden, c.ffn));
+    p->tp_slot_floats = (per_rank + 63U) & ~static_cast<size_t>(63U);
+    const size_t bytes = qllm_provider::kTpFlagBytes + 2U * ranks * p->tp_slot_floats * sizeof(float);
+    void* area = nullptr;
+    cu(cudaMalloc(&area, bytes), "allocate the exchange area");
+    p->tp_area = static_cast<uint8_t*>(area);
+    cu(cudaMemset(area, 0, bytes), "clear the exchange area");
+    p->tp_words.alloc(2, "exchange counters");
+    cu(cudaMemset(p->tp_words.p, 0, 2U * sizeof(uint32_t)), "clear the exchange counters");
+    cu(cudaDeviceSynchronize(), "exchange set-up");
+    cudaIpcMemHandle_t h{};
+    static_assert(sizeof(h) == QLLM_TP_HANDLE_BYTES, "handle size");
+    cu(cudaIpcGetMemHandle(&h, area), "export the exchange area");
+    std::memcpy(handle, &h, sizeof(h));
+    p->tp_ranks = ranks;
+    p->tp_rank = rank;
+    p->tp_peer[rank] = p->tp_area;
+    p->tp_attached = ranks == 1U;
+  });
+}
+
+int qllm_provider_tp_attach(qllm_provider* p, const void* handles) {
+  if (!p || !handles || !p->tp_area) return fail(QLLM_INVALID_ARGUMENT, "call qllm_provider_tp_export first");
+  return guarded([&] {
+    cu(cudaSetDevice(p->device), "select device");
+    for (uint32_t r = 0; r < p->tp_ranks; ++r) {
+      if (r == p->tp_rank || p->tp_peer[r]) continue;
+      cudaIpcMemHandle_t h{};
+      std::memcpy(&h, static_cast<const uint8_t*>(handles) + static_cast<size_t>(r) * sizeof(h), sizeof(h));
+      void* mapped = nullptr;
+      cu(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "map a peer's exchange area");
+      p->tp_peer[r] = static_cast<uint8_t*>(mapped);
+    }
+    p->tp_attached = true;
+  });
 }
 
 int qllm_provider_set_attention_impl(qllm_provider* p, int impl) {

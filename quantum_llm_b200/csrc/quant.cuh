@@ -104,7 +104,44 @@ struct GemvOut {
   uint32_t n;       // outputs per activation row
   uint32_t batch;
   float weight_scale, input_scale;
+  // Tensor-parallel exchange (null: none).  `data` is then a slot of this rank's inbox that
+  // holds every rank's partials ([rank][split][batch][n], `split` counting all of them); the
+  // peers' parts are complete once flags[r] has reached *sequence (exchange_wait below).
+  const uint32_t* exchange_flags;     // [ranks] last exchange each source rank has delivered here
+  const uint32_t* exchange_sequence;  // exchanges this rank has produced itself
+  uint32_t* exchange_error;
+  uint32_t exchange_ranks, exchange_rank;
 };
+
+constexpr unsigned long long kExchangeTimeoutNs = 2000000000ULL;  // a peer that is 2 s late counts as lost
+
+// Blocks the CTA until the peers' partial sums of `o` have arrived (call after the wait on the
+// producing kernel of this rank, before the first gemv_value).  The wait is bounded: after the
+// time limit an error word is set, and later waits return at once.
+__device__ __forceinline__ void exchange_wait(const GemvOut& o) {
+  if (o.exchange_flags == nullptr || o.exchange_ranks < 2U) return;  // uniform over the grid
+  if (threadIdx.x == 0U && *reinterpret_cast<volatile uint32_t*>(o.exchange_error) == 0U) {
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(o.exchange_sequence);
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (uint32_t r = 0; r < o.exchange_ranks; ++r) {
+      if (r == o.exchange_rank) continue;
+      for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.exchange_flags + r) : "memory");
+        if (static_cast<int32_t>(seen - target) >= 0) break;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - start > kExchangeTimeoutNs) {
+          atomicExch(o.exchange_error, 200U + r);  // results from here on are invalid; nothing hangs
+          r = o.exchange_ranks;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
 
 __device__ __forceinline__ float gemv_value(const GemvOut& o, uint32_t row, uint32_t col) {
   const size_t i = static_cast<size_t>(row) * o.n + col;

@@ -6,6 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libqllm_b200.so")
 
 KV_F16, KV_Q4H, KV_Q8 = 0, 1, 2
+TP_HANDLE_BYTES = 64   # QLLM_TP_HANDLE_BYTES
 
 
 class QllmError(RuntimeError):
@@ -77,6 +78,8 @@ SIGNATURES = {
     "qllm_provider_set_graph_mode": (ci, [vp, ci]),
     "qllm_provider_set_gemv_impl": (ci, [vp, ci]),
     "qllm_provider_set_attention_impl": (ci, [vp, ci]),
+    "qllm_provider_tp_export": (ci, [vp, u32, u32, vp]),
+    "qllm_provider_tp_attach": (ci, [vp, vp]),
     "qllm_provider_read_logits": (ci, [vp, vp, u32]),
     "qllm_provider_read_hidden": (ci, [vp, vp, ci, vp, u32]),
     "qllm_provider_read_drafts": (ci, [vp, vp, vp, P(u32)]),

@@ -161,6 +161,17 @@ class Nvfp4MtpProvider:
     def set_attention_impl(self, impl):
         _l.check(self.L.qllm_provider_set_attention_impl(self.h, int(impl)))
 
+    def tp_export(self, rank, ranks):
+        """Allocates this rank's tensor-parallel exchange area; returns its inter-process handle."""
+        handle = C.create_string_buffer(_l.TP_HANDLE_BYTES)
+        _l.check(self.L.qllm_provider_tp_export(self.h, int(rank), int(ranks), handle))
+        return handle.raw
+
+    def tp_attach(self, handles):
+        """Maps the peers' exchange areas: `handles` = the ranks' handles concatenated in rank order."""
+        buffer = C.create_string_buffer(bytes(handles), len(handles))
+        _l.check(self.L.qllm_provider_tp_attach(self.h, buffer))
+
     def set_gemv_impl(self, impl):
         _l.check(self.L.qllm_provider_set_gemv_impl(self.h, int(impl)))
 

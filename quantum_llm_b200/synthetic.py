@@ -41,6 +41,19 @@ class DeviceMatrix:
     def nbytes(self):
         return self.codes.numel() + self.scales.numel()
 
+    def take_rows(self, ranges):
+        """The output rows of the given (start, stop) ranges, in that order (same tensor scale)."""
+        codes = torch.cat([self.codes[a:b] for a, b in ranges]).contiguous()
+        scales = torch.cat([self.scales[a:b] for a, b in ranges]).contiguous()
+        return DeviceMatrix(codes, scales, self.weight_scale, codes.shape[0], self.cols)
+
+    def take_columns(self, start, stop):
+        """Input columns [start, stop) (multiples of 16): a K-slice of the same quantised tensor."""
+        assert start % 16 == 0 and stop % 16 == 0
+        return DeviceMatrix(self.codes[:, start // 2:stop // 2].contiguous(),
+                            self.scales[:, start // 16:stop // 16].contiguous(), self.weight_scale, self.rows,
+                            stop - start)
+
 
 def _random_rows(rows, cols, seed, device, std=0.02, base_seed=None, noise=0.0):
     gen = torch.Generator(device=device)
@@ -67,10 +80,28 @@ def quantize(w):
     return DeviceMatrix(codes, scales, weight_scale, rows, cols)
 
 
+def shard_block(m, cfg, rank, ranks):
+    """Tensor-parallel shard of a dense block's projections: q/k/v head rows and gate/up rows of
+    the rank (column split of the outputs), the matching K columns of o and down."""
+    QH, KV, HD, F = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"]
+    assert QH % ranks == 0 and KV % ranks == 0 and F % (16 * ranks) == 0 and not cfg.get("experts", 0)
+    q, kv, f = QH // ranks * HD, KV // ranks * HD, F // ranks
+    k0, v0 = QH * HD, (QH + KV) * HD
+    return dict(
+        qkv=m["qkv"].take_rows([(rank * q, (rank + 1) * q), (k0 + rank * kv, k0 + (rank + 1) * kv),
+                                (v0 + rank * kv, v0 + (rank + 1) * kv)]),
+        o=m["o"].take_columns(rank * q, (rank + 1) * q),
+        gate_up=m["gate_up"].take_rows([(rank * f, (rank + 1) * f), (F + rank * f, F + (rank + 1) * f)]),
+        down=m["down"].take_columns(rank * f, (rank + 1) * f))
+
+
 class DeviceBlock:
     SHAPES = ("qkv", "o", "gate_up", "down")
 
-    def __init__(self, cfg, seed, device, base_seed=None):
+    def __init__(self, cfg, seed, device, base_seed=None, tp=None):
+        """`tp` = (rank, ranks): keep this rank's shard of every projection.  The full matrices are
+        generated and quantised exactly as without `tp`, then sliced, so the ranks together hold
+        the bytes of the unsharded model."""
         H, F = cfg["hidden"], cfg["ffn"]
         qkv_rows = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"]
         shapes = dict(qkv=(qkv_rows, H), o=(H, cfg["q_heads"] * cfg["head_dim"]), gate_up=(2 * F, H), down=(H, F))
@@ -83,6 +114,8 @@ class DeviceBlock:
                              base_seed=None if base_seed is None else base_seed * 16 + i, noise=0.004)
             self.m[name] = quantize(w)
             del w
+        if tp is not None:
+            self.m = shard_block(self.m, cfg, *tp)
         self.input_norm = torch.ones(H, dtype=torch.float32, device=device)
         self.post_norm = torch.ones(H, dtype=torch.float32, device=device)
         if self.experts:
@@ -116,8 +149,15 @@ class DeviceBlock:
 
 
 class DeviceModel:
-    def __init__(self, cfg, seed=0, device="cuda:0"):
+    def __init__(self, cfg, seed=0, device="cuda:0", tp=None):
+        """`cfg` is the whole model's geometry.  With `tp` = (rank, ranks) this object holds that
+        rank's tensor-parallel shard and `self.cfg` its local head / FFN counts."""
+        self.global_cfg = dict(cfg)
         self.cfg = dict(cfg)
+        self.tp = tp
+        if tp is not None:
+            for key in ("q_heads", "kv_heads", "ffn"):
+                self.cfg[key] = cfg[key] // tp[1]
         self.device = torch.device(device)
         H, V = cfg["hidden"], cfg["vocab"]
         with torch.cuda.device(self.device):
@@ -125,13 +165,13 @@ class DeviceModel:
             gen.manual_seed(seed * 1000 + 1)
             self.embedding = (torch.randn((V, H), generator=gen, device=self.device, dtype=torch.float32) * 0.02
                               ).to(torch.bfloat16)
-            self.layers = [DeviceBlock(cfg, seed * 1000 + 10 + l, self.device) for l in range(cfg["layers"])]
+            self.layers = [DeviceBlock(cfg, seed * 1000 + 10 + l, self.device, tp=tp) for l in range(cfg["layers"])]
             self.final_norm = torch.ones(H, dtype=torch.float32, device=self.device)
             self.head = quantize(_random_rows(V, H, seed * 1000 + 2, self.device))
             self.mtp_norms = [torch.ones(H, dtype=torch.float32, device=self.device) for _ in range(3)]
             self.mtp_fusion = quantize(_random_rows(H, 2 * H, seed * 1000 + 3, self.device))
             self.mtp_block = DeviceBlock(cfg, seed * 1000 + 4, self.device,
-                                         base_seed=seed * 1000 + 10 + cfg["layers"] - 1)
+                                         base_seed=seed * 1000 + 10 + cfg["layers"] - 1, tp=tp)
             torch.cuda.empty_cache()
 
     def config(self):
@@ -147,6 +187,22 @@ class DeviceModel:
                        self.mtp_block.c(), self.mtp_norms[2].data_ptr())
         return Nvfp4MtpProvider(self.config(), w, weights_on_device=True, device=self.device.index or 0,
                                 keepalive=(self, blocks))
+
+    def tensor_parallel_provider(self, group=None):
+        """Provider of this rank's shard with the exchange areas of all ranks attached: the
+        inter-process handles travel through `torch.distributed` (all-gather over `group`)."""
+        import torch.distributed as dist
+        rank, ranks = self.tp
+        provider = self.provider()
+        provider.set_gemv_impl(1)
+        mine = provider.tp_export(rank, ranks)
+        handles = [None] * ranks
+        if ranks > 1:
+            dist.all_gather_object(handles, mine, group=group)
+        else:
+            handles[0] = mine
+        provider.tp_attach(b"".join(handles))
+        return provider
 
     # ---- algorithmic bytes (weights streamed once per pass; scales included)
     def verify_weight_bytes(self):

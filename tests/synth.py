@@ -121,6 +121,50 @@ class SynthModel:
         return ob.Session(self.oracle_config(), w, (self, blocks))
 
 
+def _matrix_from(codes, scales, like):
+    m = SynthMatrix.__new__(SynthMatrix)
+    m.codes, m.scales = np.ascontiguousarray(codes), np.ascontiguousarray(scales)
+    m.divisor, m.weight_scale, m.input_scale = like.divisor, like.weight_scale, like.input_scale
+    m.rows, m.cols = m.codes.shape[0], m.codes.shape[1] * 2
+    return m
+
+
+def _take_rows(m, ranges):
+    return _matrix_from(np.concatenate([m.codes[a:b] for a, b in ranges]),
+                        np.concatenate([m.scales[a:b] for a, b in ranges]), m)
+
+
+def _take_columns(m, start, stop):
+    return _matrix_from(m.codes[:, start // 2:stop // 2], m.scales[:, start // 16:stop // 16], m)
+
+
+def shard_model(model, rank, ranks):
+    """Tensor-parallel shard `rank` of a dense SynthModel: the rank's q/k/v head rows and gate/up
+    rows, the matching K columns of o and down (slices of the same quantised tensors);
+    everything else is shared with `model`.  `cfg` carries the local head and FFN counts."""
+    import copy
+    c = model.cfg
+    QH, KV, HD, F = c["q_heads"], c["kv_heads"], c["head_dim"], c["ffn"]
+    assert QH % ranks == 0 and KV % ranks == 0 and F % (16 * ranks) == 0 and not c.get("experts", 0)
+    q, kv, f = QH // ranks * HD, KV // ranks * HD, F // ranks
+    k0, v0 = QH * HD, (QH + KV) * HD
+
+    def shard_block(b):
+        s = copy.copy(b)
+        s.qkv = _take_rows(b.qkv, [(rank * q, (rank + 1) * q), (k0 + rank * kv, k0 + (rank + 1) * kv),
+                                   (v0 + rank * kv, v0 + (rank + 1) * kv)])
+        s.o = _take_columns(b.o, rank * q, (rank + 1) * q)
+        s.gate_up = _take_rows(b.gate_up, [(rank * f, (rank + 1) * f), (F + rank * f, F + (rank + 1) * f)])
+        s.down = _take_columns(b.down, rank * f, (rank + 1) * f)
+        return s
+
+    out = copy.copy(model)
+    out.cfg = dict(c, q_heads=QH // ranks, kv_heads=KV // ranks, ffn=F // ranks)
+    out.layers = [shard_block(b) for b in model.layers]
+    out.mtp_block = shard_block(model.mtp_block)
+    return out
+
+
 def prompt(vocab, count, seed):
     return np.random.default_rng(seed).integers(0, vocab, count, dtype=np.uint32)
 
