@@ -297,11 +297,13 @@ struct GemvMmaParams {
   uint32_t k_chunks, k_atoms, split, stages;
   uint32_t raw;                 // 1: always write raw partials (the consumer applies the scale)
   float weight_scale, input_scale;
-  GemvExchange x;               // x.ranks != 0: the partials go to every rank's inbox
+  const GemvExchange* x;        // device memory; non-null: the partials go to every rank's inbox
 };
 
 // grid (row tiles, split, n tiles); 128 threads: thread 0 drives TMA, thread 32 drives the tensor
 // core, all four warps run the epilogue (one tensor-memory lane = one weight row per thread).
+// kExchange: the tensor-parallel form (p.x set), kept out of the single-GPU instantiation.
+template <bool kExchange>
 __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                       const __grid_constant__ CUtensorMap act_map, GemvMmaParams p) {
@@ -437,10 +439,10 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
           const uint32_t col = n_tile * 128U + c0 + j;
           if (col >= p.batch) continue;
           const float acc = __uint_as_float(v[j]);
-          if (p.x.ranks != 0U) {
+          if (kExchange) {
             // [rank][split][batch][row_count] in the slot; plain stores, also into the peers' memory
-            const size_t index = ((static_cast<size_t>(p.x.rank) * p.split + blockIdx.y) * p.batch + col) * p.row_count + row;
-            for (uint32_t r = 0; r < p.x.ranks; ++r) p.x.inbox[r][index] = acc;
+            const size_t index = ((static_cast<size_t>(p.x->rank) * p.split + blockIdx.y) * p.batch + col) * p.row_count + row;
+            for (uint32_t r = 0; r < p.x->ranks; ++r) p.x->inbox[r][index] = acc;
           } else if (p.split == 1U && !p.raw)
             p.y[static_cast<size_t>(col) * p.row_count + row] = bf16r(acc * p.weight_scale / p.input_scale);
           else
@@ -455,18 +457,19 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
   __syncthreads();
   if (warp == 0U)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
-  if (p.x.ranks != 0U && tid == 0U) {
+  if (kExchange && tid == 0U) {
     // every thread of this CTA has stored (barrier above); the last CTA of the launch tells the peers
+    const GemvExchange& x = *p.x;
     __threadfence_system();
     const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
-    if (atomicAdd(p.x.tickets, 1U) == total - 1U) {
-      *p.x.tickets = 0U;  // for the next launch (stream order)
+    if (atomicAdd(x.tickets, 1U) == total - 1U) {
+      *x.tickets = 0U;  // for the next launch (stream order)
       __threadfence_system();
-      const uint32_t sequence = *p.x.sequence + 1U;
-      *p.x.sequence = sequence;
-      for (uint32_t r = 0; r < p.x.ranks; ++r) {
-        if (r == p.x.rank) continue;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.x.flags[r] + p.x.rank), "r"(sequence) : "memory");
+      const uint32_t sequence = *x.sequence + 1U;
+      *x.sequence = sequence;
+      for (uint32_t r = 0; r < x.ranks; ++r) {
+        if (r == x.rank) continue;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.flags[r] + x.rank), "r"(sequence) : "memory");
       }
     }
   }
@@ -484,7 +487,8 @@ __global__ void gemv_mma_finalize_kernel(const float* __restrict__ partials, flo
 
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr);
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr,
+             const GemvExchange* exchange_device = nullptr);
 
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
@@ -537,7 +541,8 @@ int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_
 // the result is left as split-K partials for the consumer; otherwise split == 1 writes y.
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange) {
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange,
+             const GemvExchange* exchange_device) {
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
   const uint32_t k_chunks = m.cols / kTileK;
   const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
@@ -562,7 +567,10 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024U;
   static size_t opted = 0;
   if (smem > opted) {
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
+    if (rc) return rc;
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
     opted = smem;
@@ -584,9 +592,12 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.raw = raw ? 1U : 0U;
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
-  if (exchange) p.x = *exchange;
+  p.x = exchange ? exchange_device : nullptr;
   count_launch();
-  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+  if (p.x != nullptr)
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+                                 w.codes_map, act_map, p), "nvfp4_gemv_mma");
+  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
                                w.codes_map, act_map, p), "nvfp4_gemv_mma");
 }
 
@@ -624,7 +635,7 @@ size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                      uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
                      float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream,
-                     const GemvExchange* exchange) {
+                     const GemvExchange* exchange, const GemvExchange* exchange_device) {
   *out = GemvOut{};
   out->n = row_count;
   out->batch = batch;
@@ -634,17 +645,13 @@ int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, u
     const QuantSink s = make_sink(1, quant_buffer, batch, m.cols, m.input_scale);
     uint32_t split = 1;
     const int rc = mma_core(w, m, first_row, row_count, batch, s.codes, s.atoms, partials, nullptr, error, true,
-                            &split, stream, exchange);
+                            &split, stream, exchange, exchange_device);
     out->data = partials;
     out->split = split;
     if (exchange) {
       out->data = exchange->inbox[exchange->rank];
       out->split = exchange->ranks * split;
-      out->exchange_flags = exchange->flags[exchange->rank];
-      out->exchange_sequence = exchange->sequence;
-      out->exchange_error = exchange->error;
-      out->exchange_ranks = exchange->ranks;
-      out->exchange_rank = exchange->rank;
+      out->exchange = &exchange_device->arrival;
     }
     return rc;
   }

@@ -8,6 +8,7 @@
 #include <cstdint>
 
 #include "../../include/qllm_b200.h"
+#include "quant.cuh"
 
 namespace qllm {
 
@@ -34,14 +35,16 @@ struct MmaWeights {
 // through their mapped memory), and the last CTA of the launch raises this rank's sequence
 // number in every peer's flag array.  The consumer sums all ranks' partials in rank order
 // (exchange_wait, quant.cuh), so every rank computes the same values.
+// The struct lives in device memory (one per inbox slot, written once when the peers are
+// attached); the launch carries a pointer to it.
 struct GemvExchange {
-  uint32_t ranks = 0, rank = 0;
-  float* inbox[8] = {};      // the slot of this exchange in every rank's inbox
-  uint32_t* flags[8] = {};   // every rank's flag array [ranks]
-  uint32_t* sequence = nullptr;  // local: exchanges produced so far
-  uint32_t* tickets = nullptr;   // local: CTAs of the running launch that have stored their part
-  uint32_t* error = nullptr;     // local error word of the consumers
-  size_t capacity_floats = 0;    // floats one slot holds
+  uint32_t ranks, rank;
+  float* inbox[8];      // the slot of this exchange in every rank's inbox
+  uint32_t* flags[8];   // every rank's flag array [ranks]
+  uint32_t* sequence;   // local: exchanges produced so far
+  uint32_t* tickets;    // local: CTAs of the running launch that have stored their part
+  size_t capacity_floats;  // floats one slot holds
+  ExchangeArrival arrival;  // what this rank's consumers wait on
 };
 
 size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);

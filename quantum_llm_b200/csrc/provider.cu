@@ -155,6 +155,8 @@ struct qllm_provider {
   bool tp_attached = false;
   size_t tp_slot_floats = 0;
   DeviceBuffer<uint32_t> tp_words;             // [0] sequence, [1] tickets
+  GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down): host copy
+  DeviceBuffer<GemvExchange> tp_exchange_dev;  // and the copy the kernels read
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
@@ -330,25 +332,35 @@ struct qllm_provider {
                int exchange_slot = -1) {
     if (!row_count) row_count = w.m.rows;
     GemvOut o{};
-    GemvExchange x{};
     const bool exchange = tp_ranks != 0U && exchange_slot >= 0;
-    if (exchange) {
-      if (!tp_attached) throw Error(QLLM_INVALID_ARGUMENT, "tensor-parallel provider used before qllm_provider_tp_attach");
+    if (exchange && !tp_attached)
+      throw Error(QLLM_INVALID_ARGUMENT, "tensor-parallel provider used before qllm_provider_tp_attach");
+    ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
+                        final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream,
+                        exchange ? &tp_exchange[exchange_slot] : nullptr,
+                        exchange ? tp_exchange_dev.p + exchange_slot : nullptr));
+    return o;
+  }
+  // Fills the two per-slot exchange descriptors (host copy + device copy) once all areas are mapped.
+  void tp_describe() {
+    for (uint32_t slot = 0; slot < 2U; ++slot) {
+      GemvExchange x{};
       x.ranks = tp_ranks;
       x.rank = tp_rank;
       for (uint32_t r = 0; r < tp_ranks; ++r) {
         x.flags[r] = reinterpret_cast<uint32_t*>(tp_peer[r]);
         x.inbox[r] = reinterpret_cast<float*>(tp_peer[r] + kTpFlagBytes) +
-                     static_cast<size_t>(exchange_slot) * tp_ranks * tp_slot_floats;
+                     static_cast<size_t>(slot) * tp_ranks * tp_slot_floats;
       }
       x.sequence = tp_words.p;
       x.tickets = tp_words.p + 1;
-      x.error = kernel_error.p;
       x.capacity_floats = static_cast<size_t>(tp_ranks) * tp_slot_floats;
+      x.arrival = ExchangeArrival{x.flags[tp_rank], x.sequence, kernel_error.p, tp_ranks, tp_rank};
+      tp_exchange[slot] = x;
     }
-    ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
-                        final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream, exchange ? &x : nullptr));
-    return o;
+    tp_exchange_dev.alloc(2, "exchange descriptors");
+    cu(cudaMemcpy(tp_exchange_dev.p, tp_exchange, sizeof(tp_exchange), cudaMemcpyHostToDevice), "exchange descriptors");
+    tp_attached = true;
   }
   static constexpr size_t kTpFlagBytes = 256;
   // x' = act(x + delta) stored to `store`; operand of `next` = quantised rmsnorm(x') * weight
@@ -953,7 +965,7 @@ int qllm_provider_tp_export(qllm_provider* p, uint32_t rank, uint32_t ranks, voi
     p->tp_ranks = ranks;
     p->tp_rank = rank;
     p->tp_peer[rank] = p->tp_area;
-    p->tp_attached = ranks == 1U;
+    if (ranks == 1U) p->tp_describe();
   });
 }
 
@@ -969,7 +981,7 @@ int qllm_provider_tp_attach(qllm_provider* p, const void* handles) {
       cu(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "map a peer's exchange area");
       p->tp_peer[r] = static_cast<uint8_t*>(mapped);
     }
-    p->tp_attached = true;
+    if (!p->tp_attached) p->tp_describe();
   });
 }
 

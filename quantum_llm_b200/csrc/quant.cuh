@@ -107,10 +107,15 @@ struct GemvOut {
   // Tensor-parallel exchange (null: none).  `data` is then a slot of this rank's inbox that
   // holds every rank's partials ([rank][split][batch][n], `split` counting all of them); the
   // peers' parts are complete once flags[r] has reached *sequence (exchange_wait below).
-  const uint32_t* exchange_flags;     // [ranks] last exchange each source rank has delivered here
-  const uint32_t* exchange_sequence;  // exchanges this rank has produced itself
-  uint32_t* exchange_error;
-  uint32_t exchange_ranks, exchange_rank;
+  const struct ExchangeArrival* exchange;
+};
+
+// Device-resident description of where the peers announce their deliveries.
+struct ExchangeArrival {
+  const uint32_t* flags;     // [ranks] last exchange each source rank has delivered here
+  const uint32_t* sequence;  // exchanges this rank has produced itself
+  uint32_t* error;
+  uint32_t ranks, rank;
 };
 
 constexpr unsigned long long kExchangeTimeoutNs = 2000000000ULL;  // a peer that is 2 s late counts as lost
@@ -118,23 +123,25 @@ constexpr unsigned long long kExchangeTimeoutNs = 2000000000ULL;  // a peer that
 // Blocks the CTA until the peers' partial sums of `o` have arrived (call after the wait on the
 // producing kernel of this rank, before the first gemv_value).  The wait is bounded: after the
 // time limit an error word is set, and later waits return at once.
-__device__ __forceinline__ void exchange_wait(const GemvOut& o) {
-  if (o.exchange_flags == nullptr || o.exchange_ranks < 2U) return;  // uniform over the grid
-  if (threadIdx.x == 0U && *reinterpret_cast<volatile uint32_t*>(o.exchange_error) == 0U) {
-    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(o.exchange_sequence);
+__device__ __forceinline__ void exchange_wait(const GemvOut& out) {
+  if (out.exchange == nullptr) return;  // uniform over the grid
+  const ExchangeArrival o = *out.exchange;
+  if (o.ranks < 2U) return;
+  if (threadIdx.x == 0U && *reinterpret_cast<volatile uint32_t*>(o.error) == 0U) {
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(o.sequence);
     unsigned long long start;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
-    for (uint32_t r = 0; r < o.exchange_ranks; ++r) {
-      if (r == o.exchange_rank) continue;
+    for (uint32_t r = 0; r < o.ranks; ++r) {
+      if (r == o.rank) continue;
       for (;;) {
         uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.exchange_flags + r) : "memory");
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.flags + r) : "memory");
         if (static_cast<int32_t>(seen - target) >= 0) break;
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
         if (now - start > kExchangeTimeoutNs) {
-          atomicExch(o.exchange_error, 200U + r);  // results from here on are invalid; nothing hangs
-          r = o.exchange_ranks;
+          atomicExch(o.error, 200U + r);  // results from here on are invalid; nothing hangs
+          r = o.ranks;
           break;
         }
       }
