@@ -206,6 +206,37 @@ int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
 int qllm_provider_tp_export(qllm_provider* provider, uint32_t rank, uint32_t ranks, void* handle);
 int qllm_provider_tp_attach(qllm_provider* provider, const void* handles);
 
+/* ---- runtime-model.tsv: the artifact's model descriptor -------------------------------------
+ * Host-only.  qllm_descriptor_parse reads the descriptor text with the grammar and the validity
+ * rules of the reference's parser (parse_model_descriptor_artifact and validate_model_descriptor,
+ * runtime/src/model_descriptor.cpp:492-746, :107-341; namespace base 1): header line, tab-separated
+ * records, duplicate keys and unknown records rejected, kernel requirements, contiguous layer and
+ * operation programs, routed components, schema-3 data flow.  Rejections return
+ * QLLM_INVALID_ARGUMENT with the reference's message in qllm_last_error() ("malformed model
+ * descriptor line N", ...).
+ * qllm_descriptor_negotiate is the provider side of capability selection
+ * (runtime/tools/dense_fp4_provider.cpp:2367-2470, :2935-2966; registry rule
+ * runtime/src/execution_provider.cpp:54-97): the artifact must list this library's capability
+ * (qllm_capability_name / _abi) as a required kernel and as its exact_decode program, with
+ * source_mtp_layers = 1, draft_depth = maximum emitted tokens - 1 (at most 4),
+ * draft_vocabulary_size <= vocabulary, mtp_kv_encoding = 1, embedding_first = 1, post_norm = 1;
+ * it then fills the geometry of `config` from the model record, the attributes
+ * (attention_heads, kv_heads, head_dim, rotary_dimension, norm_epsilon_f32_bits,
+ * rope_theta_f32_bits, activation_bf16, optional intermediate_size), the layer count and the first
+ * routed component; kv_encoding, page_tokens, split_tokens and max_context stay the caller's
+ * (max_context is clamped to the model's).
+ * qllm_descriptor_tensor returns the tensor bound to a role of the exact-decode program
+ * ("token_embedding", "fusion_projection", "layer.0.query_projection", ...; roles as in
+ * dense_fp4_provider.cpp:4733-4786), else of the model, else NULL.
+ * qllm_descriptor_dump writes what was understood in a canonical text form (tests compare it
+ * with the same dump of the reference's own parser); returns the full length. */
+typedef struct qllm_descriptor qllm_descriptor;
+int qllm_descriptor_parse(const char* text, size_t bytes, qllm_descriptor** descriptor);
+void qllm_descriptor_destroy(qllm_descriptor* descriptor);
+int qllm_descriptor_negotiate(const qllm_descriptor* descriptor, qllm_config* config);
+const char* qllm_descriptor_tensor(const qllm_descriptor* descriptor, const char* role);
+size_t qllm_descriptor_dump(const qllm_descriptor* descriptor, char* out, size_t capacity);
+
 /* inspection for parity tests (device -> host copies) */
 int qllm_provider_read_logits(qllm_provider* provider, float* out, uint32_t rows);
 /* which = 0: rows retained by the last prefill chunk; 1: target rows of the last exact step. */

@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libqllm_b200.so")
 SOURCES = ["kernels_basic.cu", "kernels_attention.cu", "kernels_attention_q4h.cu", "kernels_attention_q8.cu", "kernels_attention_f16.cu","kernels_sampler.cu", "kernels_fused.cu", "kernels_moe.cu", "gemv_mma.cu",
-           "provider.cu", "c_api_kernels.cu", "no_alloc.cu"]
+           "provider.cu", "c_api_kernels.cu", "no_alloc.cu", "descriptor.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-fmad=false", "-ccbin", "/usr/bin/g++"]
 
@@ -29,7 +29,7 @@ def build(force=False, verbose=False):
     objects, procs = [], []
     for src in SOURCES:
         path = os.path.join(CSRC, src)
-        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         objects.append(obj)
         if force or _stale(obj, [path] + headers):
             cmd = [nvcc, *FLAGS, "-c", path, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])

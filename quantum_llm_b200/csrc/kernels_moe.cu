@@ -209,6 +209,147 @@ moe_gate_up_kernel(MoeArgs a) {
                    a.mid_i8 + static_cast<size_t>(selection) * W, a.mid_scale + static_cast<size_t>(selection) * (W / 16U));
 }
 
+// ---- gate / up / SiLU, weights staged through shared memory ------------------------------------
+// grid (CTAs per selection, selections), 8 warps.  A CTA works on ONE selection: it quantises the
+// row once, then walks over its share of the selection's 16-row tiles.  The 16 gate rows and the
+// 16 up rows of a tile are contiguous in the expert's tensors, so one elected thread brings a
+// tile in with four bulk asynchronous copies (codes and scales of each projection, 36 KB at
+// hidden 2048) that complete on the stage's mbarrier; two stages, so the next tile streams in
+// while the warps work on the current one (two rows of each projection per warp).  Two CTAs per
+// SM; the grid is sized to one wave.  Needs hidden % 256 == 0 (16-byte granules of the scale
+// rows) and 16-byte aligned expert tensors; other shapes use the kernel above.
+constexpr uint32_t kStagedRows = 16;
+constexpr uint32_t kStagedThreads = 256;
+constexpr uint32_t kStagedStages = 2;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void bulk_to_shared(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(shared_address(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(shared_address(bar))
+               : "memory");
+}
+// Bounded wait for the phase of `bar` with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity) {
+  const uint32_t address = shared_address(bar);
+  for (uint32_t spin = 0; spin < (1U << 22U); ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(address), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// Sums of the blocks of R staged weight rows (row-major codes / scales in shared memory).
+template <int R>
+__device__ __forceinline__ void staged_rows_dot(const uint8_t* codes, const uint8_t* scales, uint32_t first,
+                                                uint32_t cols, const int8_t* xi8, const float* xscale, uint32_t lane,
+                                                double (&acc)[R]) {
+  const uint32_t blocks = cols / 16U;
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.0;
+  for (uint32_t blk = lane; blk < blocks; blk += 32U) {
+    const uint4 xv = reinterpret_cast<const uint4*>(xi8)[blk];
+    const float xs = xscale[blk];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint2 w = reinterpret_cast<const uint2*>(codes + static_cast<size_t>(first + r) * (cols / 2U))[blk];
+      const int d = block16_dot(w, xv);
+      acc[r] += static_cast<double>(static_cast<float>(d) *
+                                    (e4m3_value(scales[static_cast<size_t>(first + r) * blocks + blk]) * xs) * 0.25F);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = warp_sum_f64(acc[r]);
+}
+
+__host__ __device__ inline uint32_t staged_stage_bytes(uint32_t hidden) {
+  return 2U * kStagedRows * (hidden / 2U + hidden / 16U);
+}
+
+__global__ void __launch_bounds__(kStagedThreads, 2)
+moe_gate_up_staged_kernel(MoeArgs a, uint32_t* error) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(16) float mid_tile[kStagedRows];
+  __shared__ __align__(8) uint64_t bar[kStagedStages];
+  pdl_trigger();
+  if (threadIdx.x == 0U) {
+    for (uint32_t s = 0; s < kStagedStages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(&bar[s])), "r"(1U));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  const uint32_t selection = blockIdx.y, row = selection / a.route_width;
+  const uint32_t H = a.hidden, blocks = H / 16U, W = a.expert_ffn;
+  const uint32_t expert = a.indices[selection];
+  if (expert >= a.experts) return;  // the router found no candidate (non-finite logits): contributes nothing
+  const ExpertMatrix G = a.gate[expert], U = a.up[expert];
+  // tiles blockIdx.x, blockIdx.x + gridDim.x, ... of this selection
+  const uint32_t tiles = W / kStagedRows;
+  const uint32_t mine = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1U) / gridDim.x : 0U;
+  const uint32_t stage_bytes = staged_stage_bytes(H);
+  const uint32_t code_bytes = kStagedRows * (H / 2U), scale_bytes = kStagedRows * blocks;
+  auto issue = [&](uint32_t k) {  // elected thread: tile k of this CTA into stage k % stages
+    uint8_t* stage = smem + static_cast<size_t>(k % kStagedStages) * stage_bytes;
+    uint64_t* full = &bar[k % kStagedStages];
+    const size_t first = static_cast<size_t>(blockIdx.x + k * gridDim.x) * kStagedRows;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(full)), "r"(stage_bytes)
+                 : "memory");
+    bulk_to_shared(stage, G.codes + first * (H / 2U), code_bytes, full);
+    bulk_to_shared(stage + code_bytes, U.codes + first * (H / 2U), code_bytes, full);
+    bulk_to_shared(stage + 2U * code_bytes, G.scales + first * blocks, scale_bytes, full);
+    bulk_to_shared(stage + 2U * code_bytes + scale_bytes, U.scales + first * blocks, scale_bytes, full);
+  };
+  if (threadIdx.x == 0U)
+    for (uint32_t k = 0; k < min(mine, kStagedStages); ++k) issue(k);
+  // the row, quantised once per projection (once for both when their activation scales agree)
+  const float* x = a.x + static_cast<size_t>(row) * a.x_stride;
+  const bool shared_input = G.input_scale == U.input_scale;
+  int8_t* gi8 = reinterpret_cast<int8_t*>(smem + static_cast<size_t>(kStagedStages) * stage_bytes);
+  int8_t* ui8 = shared_input ? gi8 : gi8 + H;
+  float* gscale = reinterpret_cast<float*>(gi8 + 2U * H);
+  float* uscale = shared_input ? gscale : gscale + blocks;
+  for (uint32_t i = threadIdx.x; i < (shared_input ? blocks : 2U * blocks); i += kStagedThreads) {
+    if (i < blocks) quantize_block(x + 16U * i, G.input_scale, true, i, gi8, gscale);
+    else quantize_block(x + 16U * (i - blocks), U.input_scale, true, i - blocks, ui8, uscale);
+  }
+  __syncthreads();
+  const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
+  const float down_scale = a.down[expert].input_scale;
+  for (uint32_t k = 0; k < mine; ++k) {
+    const uint8_t* stage = smem + static_cast<size_t>(k % kStagedStages) * stage_bytes;
+    if (!wait_phase(&bar[k % kStagedStages], (k / kStagedStages) & 1U)) {
+      // the copies did not complete within the limit: report and leave (uniform: every thread waits
+      // on the same barrier; nothing of this CTA is in flight into a stage it will touch again)
+      if (threadIdx.x == 0U && error != nullptr) atomicExch(error, 400U);
+      return;
+    }
+    double g[2], u[2];
+    staged_rows_dot<2>(stage, stage + 2U * code_bytes, warp * 2U, H, gi8, gscale, lane, g);
+    staged_rows_dot<2>(stage + code_bytes, stage + 2U * code_bytes + scale_bytes, warp * 2U, H, ui8, uscale, lane, u);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (lane == static_cast<uint32_t>(r)) {
+        const float gate = bf16r(static_cast<float>(g[r]) * G.weight_scale / G.input_scale);
+        const float up = bf16r(static_cast<float>(u[r]) * U.weight_scale / U.input_scale);
+        mid_tile[warp * 2U + r] = bf16r((gate / (1.0F + expf(-gate))) * up);
+      }
+    }
+    __syncthreads();  // the stage is free, mid_tile is complete
+    if (threadIdx.x == 0U && k + kStagedStages < mine) issue(k + kStagedStages);
+    if (threadIdx.x == 32U)
+      quantize_block(mid_tile, down_scale, false, blockIdx.x + k * gridDim.x,
+                     a.mid_i8 + static_cast<size_t>(selection) * W, a.mid_scale + static_cast<size_t>(selection) * (W / 16U));
+    __syncthreads();  // mid_tile may be overwritten
+  }
+}
+
 // ---- down + ordered weighted sum: grid (ceil(hidden / 16), rows), warp = slot ---------------------
 // Warp `slot` streams 16 rows of its slot's down projection against that slot's quantised mid row
 // (LANES = 16: a half warp per row, LANES = 32 when that leaves no lane idle); 16 threads then add
@@ -303,8 +444,25 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
   const size_t smem_d = 8U * down_slot_bytes(a.expert_ffn);
   if (smem_gu > 48U * 1024U || smem_d > 48U * 1024U)
     return fail(QLLM_INVALID_ARGUMENT, "expert input rows do not fit the shared-memory staging");
-  int rc = check_cuda(launch_pdl(moe_gate_up_kernel, dim3((a.expert_ffn + kGateUpRows - 1U) / kGateUpRows, selections),
-                                 dim3(256), smem_gu, stream, a), "moe_gate_up");
+  int rc = 0;
+  const size_t smem_staged = static_cast<size_t>(kStagedStages) * staged_stage_bytes(a.hidden) + smem_gu;
+  if (a.staged && a.hidden % 256U == 0U && smem_staged <= 110U * 1024U) {
+    static size_t opted = 48U * 1024U;
+    if (smem_staged > opted) {
+      rc = check_cuda(cudaFuncSetAttribute(moe_gate_up_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(110U * 1024U)), "expert kernel shared memory opt-in");
+      if (rc) return rc;
+      opted = 110U * 1024U;
+    }
+    // one wave: two CTAs per SM (148 SMs), shared evenly by the selections
+    const uint32_t tiles = a.expert_ffn / kStagedRows;
+    const uint32_t per_selection = std::max(1U, std::min(tiles, 296U / selections));
+    rc = check_cuda(launch_pdl(moe_gate_up_staged_kernel, dim3(per_selection, selections), dim3(kStagedThreads),
+                               smem_staged, stream, a, a.error), "moe_gate_up_staged");
+  } else {
+    rc = check_cuda(launch_pdl(moe_gate_up_kernel, dim3((a.expert_ffn + kGateUpRows - 1U) / kGateUpRows, selections),
+                               dim3(256), smem_gu, stream, a), "moe_gate_up");
+  }
   if (rc) return rc;
   count_launch(2);
   const dim3 grid((a.hidden + kDownColumns - 1U) / kDownColumns, a.rows);

@@ -31,6 +31,8 @@ struct MoeArgs {
   int8_t* mid_i8;          // [rows * route_width, expert_ffn] mid quantised for the down projection
   float* mid_scale;        // [rows * route_width, expert_ffn / 16] its block scales
   float* moe;              // [rows, hidden] BF16-rounded weighted sum (added to the residual by the next norm)
+  bool staged;             // every expert tensor is 16-byte aligned: the gate/up weights may come in by bulk copies
+  uint32_t* error;         // status word set when a bounded wait runs out
 };
 
 // floats of workspace for indices, scores, quantised mid and moe together (16-byte aligned parts)

@@ -146,6 +146,7 @@ struct qllm_provider {
   DeviceBuffer<int8_t> q8;  // INT8 copy of the rotated queries for the Q4H attention
   DeviceBuffer<float> partial_buf, gemv_out;   // tensor-core split-K partials / CUDA-core results
   DeviceBuffer<float> moe_x, moe_ws;           // routed experts: normalised input rows, selection workspace
+  bool experts_aligned = true;                 // all expert tensors start on 16-byte boundaries
   // Tensor parallelism (qllm_provider_tp_export / _attach): this provider holds one rank's shard
   // (local head and FFN counts in cfg); the K-split projections (o, down) exchange partial sums.
   // Shared area of a rank: [flags: 64 x u32][slot 0][slot 1], slot = ranks x tp_slot_floats.
@@ -218,6 +219,8 @@ struct qllm_provider {
         throw Error(QLLM_INVALID_ARGUMENT, std::string("native NVFP4 matrix geometry is invalid: ") + name);
       host[e].codes = bring(m.codes, static_cast<size_t>(rows) * cols / 2U, on_device);
       host[e].scales = bring(m.scales, static_cast<size_t>(rows) * cols / 16U, on_device);
+      if ((reinterpret_cast<uintptr_t>(host[e].codes) | reinterpret_cast<uintptr_t>(host[e].scales)) & 15U)
+        experts_aligned = false;
       host[e].weight_scale = m.weight_scale;
       host[e].input_scale = m.input_scale;
     }
@@ -405,6 +408,8 @@ struct qllm_provider {
     a.expert_ffn = c.expert_ffn;
     a.route_scale = c.route_scale;
     moe_carve_workspace(moe_ws.p, a);
+    a.staged = experts_aligned;
+    a.error = kernel_error.p;
     a.gate = b.expert_gate;
     a.up = b.expert_up;
     a.down = b.expert_down;

@@ -78,6 +78,11 @@ SIGNATURES = {
     "qllm_provider_set_graph_mode": (ci, [vp, ci]),
     "qllm_provider_set_gemv_impl": (ci, [vp, ci]),
     "qllm_provider_set_attention_impl": (ci, [vp, ci]),
+    "qllm_descriptor_parse": (ci, [C.c_char_p, sz, P(vp)]),
+    "qllm_descriptor_destroy": (None, [vp]),
+    "qllm_descriptor_negotiate": (ci, [vp, vp]),
+    "qllm_descriptor_tensor": (C.c_char_p, [vp, C.c_char_p]),
+    "qllm_descriptor_dump": (sz, [vp, vp, sz]),
     "qllm_provider_tp_export": (ci, [vp, u32, u32, vp]),
     "qllm_provider_tp_attach": (ci, [vp, vp]),
     "qllm_provider_read_logits": (ci, [vp, vp, u32]),
