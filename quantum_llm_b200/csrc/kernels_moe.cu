@@ -404,6 +404,113 @@ moe_down_kernel(MoeArgs a) {
   }
 }
 
+// ---- down + ordered weighted sum, weights staged through shared memory -------------------------
+// grid (CTAs per row, rows), warp = slot.  A CTA works on ONE row: every warp keeps its slot's
+// quantised mid row in shared memory and walks over the CTA's share of the 8-column tiles; the
+// 8 weight rows of a tile and slot are contiguous in the expert's tensor, so lane 0 of each warp
+// brings them in with two bulk copies (codes, scales) onto the stage's mbarrier, which expects
+// one arrival per warp.  Two stages: the next tile streams in while the current one is reduced.
+// Needs expert_ffn % 256 == 0 and 16-byte aligned expert tensors.
+constexpr uint32_t kDownTile = 8;
+constexpr uint32_t kDownStages = 2;
+
+__host__ __device__ inline uint32_t down_tile_bytes(uint32_t expert_ffn) {
+  return kDownTile * (expert_ffn / 2U + expert_ffn / 16U);  // one slot's codes + scales of a tile
+}
+
+template <int LANES>
+__global__ void __launch_bounds__(256, 3)
+moe_down_staged_kernel(MoeArgs a, uint32_t* error) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float out_tile[8][kDownTile];
+  __shared__ __align__(8) uint64_t bar[kDownStages];
+  pdl_trigger();
+  if (threadIdx.x == 0U) {
+    for (uint32_t s = 0; s < kDownStages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(&bar[s])), "r"(8U));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  const uint32_t row = blockIdx.y, W = a.expert_ffn, blocks = W / 16U, K = a.route_width;
+  const uint32_t slot = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
+  const uint32_t selection = row * K + min(slot, K - 1U);
+  const uint32_t expert = slot < K ? a.indices[selection] : 0xffffffffU;
+  const bool valid = expert < a.experts;
+  ExpertMatrix D{};
+  if (valid) D = a.down[expert];
+  const uint32_t tiles = a.hidden / kDownTile;
+  const uint32_t mine = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1U) / gridDim.x : 0U;
+  const uint32_t tile_bytes = down_tile_bytes(W), code_bytes = kDownTile * (W / 2U);
+  uint8_t* ring = smem;  // [stage][slot][codes | scales]
+  int8_t* mi8 = reinterpret_cast<int8_t*>(smem + static_cast<size_t>(kDownStages) * 8U * tile_bytes) +
+                static_cast<size_t>(slot) * down_slot_bytes(W);
+  float* mscale = reinterpret_cast<float*>(mi8 + W);
+  auto issue = [&](uint32_t k) {  // lane 0 of every warp: its slot's part of tile k, or a bare arrival
+    uint64_t* full = &bar[k % kDownStages];
+    if (!valid) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(shared_address(full)) : "memory");
+      return;
+    }
+    uint8_t* dst = ring + (static_cast<size_t>(k % kDownStages) * 8U + slot) * tile_bytes;
+    const size_t first = static_cast<size_t>(blockIdx.x + k * gridDim.x) * kDownTile;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(full)), "r"(tile_bytes)
+                 : "memory");
+    bulk_to_shared(dst, D.codes + first * (W / 2U), code_bytes, full);
+    bulk_to_shared(dst + code_bytes, D.scales + first * blocks, tile_bytes - code_bytes, full);
+  };
+  if (lane == 0U)
+    for (uint32_t k = 0; k < min(mine, kDownStages); ++k) issue(k);
+  if (valid) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.mid_i8 + static_cast<size_t>(selection) * W);
+    const float* src_scale = a.mid_scale + static_cast<size_t>(selection) * blocks;
+    for (uint32_t i = lane; i < blocks; i += 32U) {
+      reinterpret_cast<uint4*>(mi8)[i] = src[i];
+      mscale[i] = src_scale[i];
+    }
+  }
+  __syncwarp();
+  constexpr uint32_t kGroups = 32U / LANES;
+  const uint32_t group = lane / LANES, lane_in_group = lane % LANES;
+  for (uint32_t k = 0; k < mine; ++k) {
+    if (!wait_phase(&bar[k % kDownStages], (k / kDownStages) & 1U)) {
+      if (threadIdx.x == 0U && error != nullptr) atomicExch(error, 401U);
+      return;
+    }
+    if (valid) {
+      const uint8_t* codes = ring + (static_cast<size_t>(k % kDownStages) * 8U + slot) * tile_bytes;
+      const uint8_t* scales = codes + code_bytes;
+#pragma unroll
+      for (uint32_t pass = 0; pass < kDownTile / kGroups; ++pass) {
+        const uint32_t r = pass * kGroups + group;
+        double acc = 0.0;
+        for (uint32_t blk = lane_in_group; blk < blocks; blk += LANES) {
+          const uint2 w = reinterpret_cast<const uint2*>(codes + static_cast<size_t>(r) * (W / 2U))[blk];
+          const int d = block16_dot(w, reinterpret_cast<const uint4*>(mi8)[blk]);
+          acc += static_cast<double>(static_cast<float>(d) * (e4m3_value(scales[r * blocks + blk]) * mscale[blk]) * 0.25F);
+        }
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffU, acc, o);
+        if (lane_in_group == 0U) out_tile[slot][r] = bf16r(static_cast<float>(acc) * D.weight_scale / D.input_scale);
+      }
+    } else if (lane < kDownTile) {
+      out_tile[slot][lane] = 0.0F;  // no candidate (or no such slot): contributes score * 0
+    }
+    __syncthreads();  // the stage is free, out_tile is complete
+    if (lane == 0U && k + kDownStages < mine) issue(k + kDownStages);
+    if (threadIdx.x < kDownTile) {
+      const uint32_t column = (blockIdx.x + k * gridDim.x) * kDownTile + threadIdx.x;
+      float total = 0.0F;
+      for (uint32_t s = 0; s < K; ++s) {
+        const float contribution = a.scores[row * K + s] * out_tile[s][threadIdx.x];
+        total = total + contribution;
+      }
+      a.moe[static_cast<size_t>(row) * a.hidden + column] = bf16r(total);
+    }
+    __syncthreads();  // out_tile may be overwritten
+  }
+}
+
 }  // namespace
 
 namespace {
@@ -465,9 +572,31 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
   }
   if (rc) return rc;
   count_launch(2);
-  const dim3 grid((a.hidden + kDownColumns - 1U) / kDownColumns, a.rows);
   // 32 lanes per column only when that leaves no lane idle
-  if ((a.expert_ffn / 16U) % 32U == 0U)
+  const bool wide = (a.expert_ffn / 16U) % 32U == 0U;
+  const size_t smem_down_staged = static_cast<size_t>(kDownStages) * 8U * down_tile_bytes(a.expert_ffn) + smem_d;
+  if (a.staged && a.expert_ffn % 32U == 0U && a.hidden % kDownTile == 0U && smem_down_staged <= 72U * 1024U) {
+    static bool opted = false;
+    if (!opted) {
+      rc = check_cuda(cudaFuncSetAttribute(moe_down_staged_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(72U * 1024U)), "expert kernel shared memory opt-in");
+      if (rc) return rc;
+      rc = check_cuda(cudaFuncSetAttribute(moe_down_staged_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(72U * 1024U)), "expert kernel shared memory opt-in");
+      if (rc) return rc;
+      opted = true;
+    }
+    // one wave: three CTAs per SM, shared evenly by the rows
+    const uint32_t per_row = std::max(1U, std::min(a.hidden / kDownTile, 444U / a.rows));
+    const dim3 staged_grid(per_row, a.rows);
+    if (wide)
+      return check_cuda(launch_pdl(moe_down_staged_kernel<32>, staged_grid, dim3(256), smem_down_staged, stream, a,
+                                   a.error), "moe_down_staged");
+    return check_cuda(launch_pdl(moe_down_staged_kernel<16>, staged_grid, dim3(256), smem_down_staged, stream, a,
+                                 a.error), "moe_down_staged");
+  }
+  const dim3 grid((a.hidden + kDownColumns - 1U) / kDownColumns, a.rows);
+  if (wide)
     return check_cuda(launch_pdl(moe_down_kernel<32>, grid, dim3(256), smem_d, stream, a), "moe_down");
   return check_cuda(launch_pdl(moe_down_kernel<16>, grid, dim3(256), smem_d, stream, a), "moe_down");
 }

@@ -114,13 +114,15 @@ def test_router_kernel_matches_the_oracle(experts, top_k, scale):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("route_scale,graph,hidden", [(1.0, True, 256), (2.5, False, 256), (1.0, True, 192)])
-def test_routed_experts_step_equals_the_oracle(route_scale, graph, hidden):
+@pytest.mark.parametrize("route_scale,graph,hidden,expert_ffn",
+                         [(1.0, True, 256, 128), (2.5, False, 256, 128), (1.0, True, 192, 144)])
+def test_routed_experts_step_equals_the_oracle(route_scale, graph, hidden, expert_ffn):
     # CUDA-core GEMV + scalar attention + exact expert arithmetic: the same bits as the oracle.
-    # hidden 256: gate/up weights staged through shared memory by bulk copies; hidden 192 (scale
-    # rows that are not 16-byte granules): the kernel that loads them straight into registers
+    # hidden 256 / width 128: expert weights staged through shared memory by bulk copies;
+    # hidden 192 / width 144 (rows that are not whole 16-byte granules): the kernels that load
+    # them straight into registers
     from tests.test_gpu_step import compare, run_cpu, run_gpu
-    model = synth.SynthModel(dict(MOE, route_scale=route_scale, hidden=hidden), seed=5)
+    model = synth.SynthModel(dict(MOE, route_scale=route_scale, hidden=hidden, expert_ffn=expert_ffn), seed=5)
     prompt = synth.prompt(4096, 96, 5)
     gpu = run_gpu(model, prompt, 0, 24, graph=graph)
     cpu = run_cpu(model, prompt, 0, 24)
