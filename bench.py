@@ -302,7 +302,7 @@ def ours(args):
 
     routed = args.model == "moe35b"
     cfg = dict(MOE_35B if routed else DENSE_27B)
-    tensor_parallel = args.parallelism == "tp" and world > 1
+    tensor_parallel = args.parallelism == "tp"   # world == 1: the exchange path without peers
     assert not (tensor_parallel and (routed or args.gemv_impl != 1)), "tensor parallelism: dense27b, tcgen05 GEMV"
     # tensor parallel: every rank works on the same request (same seeds); replicas: one per rank
     replica = 0 if tensor_parallel else rank
@@ -320,7 +320,8 @@ def ours(args):
     if tensor_parallel:
         model = DeviceModel(cfg, seed=0, device=f"cuda:{local}", tp=(rank, world))
         provider = model.tensor_parallel_provider()
-        dist.barrier()   # every rank has mapped its peers' exchange areas
+        if world > 1:
+            dist.barrier()   # every rank has mapped its peers' exchange areas
     else:
         model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
         provider = model.provider()

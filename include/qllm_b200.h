@@ -200,7 +200,7 @@ int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
  *   3. every rank: qllm_provider_tp_attach(provider, all_handles)  -- maps the peers' areas.
  * Needs the tensor-core GEMV (qllm_provider_set_gemv_impl(1)), K of the local o and down
  * projections a multiple of 256, and peer access between the GPUs.  ranks == 1 runs the same
- * code path without peers.  A peer that does not deliver within 2 s sets the provider's kernel
+ * code path without peers.  A value that has not arrived after about a second of polling sets the kernel
  * error word (the step fails with QLLM_INTERNAL); nothing waits without a limit. */
 #define QLLM_TP_HANDLE_BYTES 64
 int qllm_provider_tp_export(qllm_provider* provider, uint32_t rank, uint32_t ranks, void* handle);

@@ -72,11 +72,10 @@ QuantSink make_sink(int gemv_impl, void* quant_buffer, uint32_t rows, uint32_t c
 size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols);
 // y = W . operand: CUDA-core kernel writes final values into `final_out`; the tensor-core
 // kernel writes split-K partials into `partials`.  `out` describes the result for consumers.
-// With `exchange` (tensor-core kernel only; `exchange_device` = the same struct in device memory)
-// the partials go to every rank's inbox instead.
+// With `exchange` (tensor-core kernel only) the partials go to every rank's inbox instead.
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                      uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
                      float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream,
-                     const GemvExchange* exchange = nullptr, const GemvExchange* exchange_device = nullptr);
+                     const GemvExchange* exchange = nullptr);
 
 }  // namespace qllm

@@ -297,21 +297,29 @@ struct GemvMmaParams {
   uint32_t k_chunks, k_atoms, split, stages;
   uint32_t raw;                 // 1: always write raw partials (the consumer applies the scale)
   float weight_scale, input_scale;
-  const GemvExchange* x;        // device memory; non-null: the partials go to every rank's inbox
 };
 
 // grid (row tiles, split, n tiles); 128 threads: thread 0 drives TMA, thread 32 drives the tensor
 // core, all four warps run the epilogue (one tensor-memory lane = one weight row per thread).
-// kExchange: the tensor-parallel form (p.x set), kept out of the single-GPU instantiation.
+// kExchange: the tensor-parallel form, kept out of the single-GPU instantiation together with
+// its launch parameters.
+template <bool kExchange> struct ExchangeParam {};
+template <> struct ExchangeParam<true> { GemvExchange x; };
+
 template <bool kExchange>
 __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
-                      const __grid_constant__ CUtensorMap act_map, GemvMmaParams p) {
+                      const __grid_constant__ CUtensorMap act_map, GemvMmaParams p,
+                      const ExchangeParam<kExchange> e) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_trigger();  // the consumer kernel may be scheduled; it waits for this grid to finish
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
+  __shared__ uint2* exchange_inbox[8];  // tensor parallel: this exchange's slot in every rank's inbox
+  if constexpr (kExchange) {
+    if (threadIdx.x < 8U) exchange_inbox[threadIdx.x] = e.x.inbox[threadIdx.x];
+  }
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023U) & ~uintptr_t(1023));
   const uint32_t tid = threadIdx.x, warp = tid >> 5U;
   const uint32_t n_tile = blockIdx.z;
@@ -420,6 +428,17 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
   }
   // ---- epilogue: lane = weight row, columns = activation rows
   __syncwarp();
+  uint32_t exchange_ranks = 0U, exchange_rank = 0U, exchange_sequence = 0U;
+  if constexpr (kExchange) {
+    exchange_ranks = e.x.ranks;
+    exchange_rank = e.x.rank;
+    // The number of this exchange = exchanges produced so far + 1.  Every thread waits for the
+    // kernels before this one itself (the counter was advanced by one of them), then reads it
+    // while the tensor-core pipeline is still running; the last CTA of this launch stores the
+    // new number once every CTA has taken its ticket, i.e. has read the old one.
+    pdl_wait();
+    exchange_sequence = *reinterpret_cast<const volatile uint32_t*>(e.x.words + 1) + 1U;
+  }
   const bool finished = mbar_wait(&done_bar, 0U, abort_flag);
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (finished && !*abort_flag) {
@@ -440,9 +459,14 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
           if (col >= p.batch) continue;
           const float acc = __uint_as_float(v[j]);
           if (kExchange) {
-            // [rank][split][batch][row_count] in the slot; plain stores, also into the peers' memory
-            const size_t index = ((static_cast<size_t>(p.x->rank) * p.split + blockIdx.y) * p.batch + col) * p.row_count + row;
-            for (uint32_t r = 0; r < p.x->ranks; ++r) p.x->inbox[r][index] = acc;
+            // [rank][split][batch][row_count] in the slot: one 8-byte store {value, sequence} per
+            // rank, into the peers' memory as well
+            const size_t index = ((static_cast<size_t>(exchange_rank) * p.split + blockIdx.y) * p.batch + col) * p.row_count + row;
+            const uint2 pair = make_uint2(v[j], exchange_sequence);
+            for (uint32_t r = 0; r < exchange_ranks; ++r)
+              asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(exchange_inbox[r] + index), "r"(pair.x),
+                           "r"(pair.y)
+                           : "memory");
           } else if (p.split == 1U && !p.raw)
             p.y[static_cast<size_t>(col) * p.row_count + row] = bf16r(acc * p.weight_scale / p.input_scale);
           else
@@ -458,18 +482,14 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
   if (warp == 0U)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
   if (kExchange && tid == 0U) {
-    // every thread of this CTA has stored (barrier above); the last CTA of the launch tells the peers
-    const GemvExchange& x = *p.x;
-    __threadfence_system();
-    const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
-    if (atomicAdd(x.tickets, 1U) == total - 1U) {
-      *x.tickets = 0U;  // for the next launch (stream order)
-      __threadfence_system();
-      const uint32_t sequence = *x.sequence + 1U;
-      *x.sequence = sequence;
-      for (uint32_t r = 0; r < x.ranks; ++r) {
-        if (r == x.rank) continue;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.flags[r] + x.rank), "r"(sequence) : "memory");
+    // every thread of this CTA has read the sequence number (barrier above); the last CTA of the
+    // launch advances it for the kernels that follow in the stream.  The values carry their own
+    // sequence word, so nothing here orders them.
+    if constexpr (kExchange) {
+      const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+      if (atomicAdd(e.x.words + 2, 1U) == total - 1U) {
+        e.x.words[2] = 0U;  // for the next launch (stream order)
+        e.x.words[1] = exchange_sequence;
       }
     }
   }
@@ -487,8 +507,7 @@ __global__ void gemv_mma_finalize_kernel(const float* __restrict__ partials, flo
 
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr,
-             const GemvExchange* exchange_device = nullptr);
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr);
 
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
@@ -541,15 +560,14 @@ int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_
 // the result is left as split-K partials for the consumer; otherwise split == 1 writes y.
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange,
-             const GemvExchange* exchange_device) {
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange) {
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
   const uint32_t k_chunks = m.cols / kTileK;
   const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
   const uint32_t split = pick_split(row_tiles, n_tiles, k_chunks);
   if (split_out) *split_out = split;
   if (exchange && (n_tiles != 1U || static_cast<size_t>(exchange->ranks) * split * batch * row_count >
-                                        exchange->capacity_floats))
+                                        exchange->capacity))
     return fail(QLLM_INVALID_ARGUMENT, "tensor-parallel exchange slot is too small for this projection");
   MmaWorkspace ws{};
   ws.codes = const_cast<uint8_t*>(codes);
@@ -592,13 +610,12 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.raw = raw ? 1U : 0U;
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
-  p.x = exchange ? exchange_device : nullptr;
   count_launch();
-  if (p.x != nullptr)
+  if (exchange != nullptr)
     return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
-                                 w.codes_map, act_map, p), "nvfp4_gemv_mma");
+                                 w.codes_map, act_map, p, ExchangeParam<true>{*exchange}), "nvfp4_gemv_mma");
   return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
-                               w.codes_map, act_map, p), "nvfp4_gemv_mma");
+                               w.codes_map, act_map, p, ExchangeParam<false>{}), "nvfp4_gemv_mma");
 }
 
 // ---- operand buffers and the implementation-neutral GEMV core ---------------------------
@@ -635,7 +652,7 @@ size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                      uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
                      float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream,
-                     const GemvExchange* exchange, const GemvExchange* exchange_device) {
+                     const GemvExchange* exchange) {
   *out = GemvOut{};
   out->n = row_count;
   out->batch = batch;
@@ -645,13 +662,13 @@ int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, u
     const QuantSink s = make_sink(1, quant_buffer, batch, m.cols, m.input_scale);
     uint32_t split = 1;
     const int rc = mma_core(w, m, first_row, row_count, batch, s.codes, s.atoms, partials, nullptr, error, true,
-                            &split, stream, exchange, exchange_device);
+                            &split, stream, exchange);
     out->data = partials;
     out->split = split;
     if (exchange) {
-      out->data = exchange->inbox[exchange->rank];
+      out->data = reinterpret_cast<const float*>(exchange->inbox[exchange->rank]);  // {value, sequence} pairs
       out->split = exchange->ranks * split;
-      out->exchange = &exchange_device->arrival;
+      out->exchange = exchange->words;
     }
     return rc;
   }

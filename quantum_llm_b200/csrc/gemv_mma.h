@@ -32,19 +32,17 @@ struct MmaWeights {
 
 // Tensor-parallel exchange of a K-split projection: every CTA of the GEMV stores its partial
 // sums into the same inbox slot of every rank (its own through the local pointer, the peers'
-// through their mapped memory), and the last CTA of the launch raises this rank's sequence
-// number in every peer's flag array.  The consumer sums all ranks' partials in rank order
-// (exchange_wait, quant.cuh), so every rank computes the same values.
-// The struct lives in device memory (one per inbox slot, written once when the peers are
-// attached); the launch carries a pointer to it.
+// through their mapped memory) as 8-byte pairs {FP32 bits, sequence number}, one store per
+// value, so that a reader can tell a delivered value from a stale one without any flag or fence
+// (8-byte stores are not torn).  The consumer sums all ranks' partials in rank order
+// (gemv_value4, quant.cuh), so every rank computes the same values.  The last CTA of a launch
+// (a ticket counter) advances this rank's sequence number for the kernels that follow.
+// Passed by value to the exchange form of the kernel.
 struct GemvExchange {
   uint32_t ranks, rank;
-  float* inbox[8];      // the slot of this exchange in every rank's inbox
-  uint32_t* flags[8];   // every rank's flag array [ranks]
-  uint32_t* sequence;   // local: exchanges produced so far
-  uint32_t* tickets;    // local: CTAs of the running launch that have stored their part
-  size_t capacity_floats;  // floats one slot holds
-  ExchangeArrival arrival;  // what this rank's consumers wait on
+  uint2* inbox[8];      // the slot of this exchange in every rank's inbox
+  uint32_t* words;      // local status words (GemvOut::exchange): error, sequence, tickets
+  size_t capacity;      // pairs one slot holds
 };
 
 size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);

@@ -26,6 +26,9 @@ constexpr uint32_t kNormThreads = 320;
 constexpr uint32_t kNormVecs = 3;     // up to 4 * 320 * 3 * 4 = 15360 columns
 constexpr uint32_t kNormCluster = 4;
 
+// kExchange: delta is a tensor-parallel exchange result (its own instantiation, so that the
+// single-GPU kernel carries none of the polling code).
+template <bool kExchange>
 __global__ void __launch_bounds__(kNormThreads)
 residual_norm_quant_kernel(NormQuantArgs a) {
   namespace cg = cooperative_groups;
@@ -46,7 +49,6 @@ residual_norm_quant_kernel(NormQuantArgs a) {
     w[k] = (a.weight && f < end) ? reinterpret_cast<const float4*>(a.weight)[f] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
   }
   pdl_wait();
-  if (a.has_delta) exchange_wait(a.delta);  // tensor parallel: the peers' partial sums are part of delta
   const uint32_t in_row = a.row_select ? *a.row_select : out_row;
   // x == null: the row is the GEMV result alone (0 + delta is exact)
   const float4* x4 = a.x ? reinterpret_cast<const float4*>(a.x + static_cast<size_t>(in_row) * a.x_stride) : nullptr;
@@ -59,7 +61,8 @@ residual_norm_quant_kernel(NormQuantArgs a) {
     if (f < end) {
       if (x4) v[k] = x4[f];
       if (a.has_delta) {
-        const float4 d = gemv_value4(a.delta, in_row, 4U * f);
+        const float4 d = kExchange ? gemv_exchange_value4(a.delta, in_row, 4U * f)
+                                   : gemv_value4(a.delta, in_row, 4U * f);
         v[k] = make_float4(actv(v[k].x + d.x, a.bf16), actv(v[k].y + d.y, a.bf16), actv(v[k].z + d.z, a.bf16),
                            actv(v[k].w + d.w, a.bf16));
       }
@@ -104,7 +107,11 @@ int launch_residual_norm_quant(const NormQuantArgs& a, uint32_t rows, cudaStream
       a.store_stride % 4U || a.normalized_stride % 4U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported row length for the fused norm");
   count_launch();
-  return check_cuda(launch_pdl_cluster(residual_norm_quant_kernel, dim3(rows * kNormCluster), dim3(kNormThreads),
+  if (a.has_delta && a.delta.exchange != nullptr)
+    return check_cuda(launch_pdl_cluster(residual_norm_quant_kernel<true>, dim3(rows * kNormCluster),
+                                         dim3(kNormThreads), kNormCluster, 0, stream, a),
+                      "residual_norm_quant");
+  return check_cuda(launch_pdl_cluster(residual_norm_quant_kernel<false>, dim3(rows * kNormCluster), dim3(kNormThreads),
                                        kNormCluster, 0, stream, a),
                     "residual_norm_quant");
 }

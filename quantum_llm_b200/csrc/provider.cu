@@ -149,15 +149,13 @@ struct qllm_provider {
   bool experts_aligned = true;                 // all expert tensors start on 16-byte boundaries
   // Tensor parallelism (qllm_provider_tp_export / _attach): this provider holds one rank's shard
   // (local head and FFN counts in cfg); the K-split projections (o, down) exchange partial sums.
-  // Shared area of a rank: [flags: 64 x u32][slot 0][slot 1], slot = ranks x tp_slot_floats.
+  // Shared area of a rank: [slot 0][slot 1], slot = ranks x tp_slot_pairs {value, sequence} pairs.
   uint32_t tp_ranks = 0, tp_rank = 0;
   uint8_t* tp_area = nullptr;                  // this rank's area (cudaMalloc, exported to the peers)
   uint8_t* tp_peer[8] = {};                    // every rank's area as mapped here (own = tp_area)
   bool tp_attached = false;
-  size_t tp_slot_floats = 0;
-  DeviceBuffer<uint32_t> tp_words;             // [0] sequence, [1] tickets
-  GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down): host copy
-  DeviceBuffer<GemvExchange> tp_exchange_dev;  // and the copy the kernels read
+  size_t tp_slot_pairs = 0;
+  GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down)
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
@@ -291,8 +289,9 @@ struct qllm_provider {
     }
     partial_buf.alloc(partial_floats, "split-K partial sums");
     gemv_out.alloc(static_cast<size_t>(R) * most_outputs, "GEMV results");
-    kernel_error.alloc(1, "kernel status word");
-    cu(cudaMemsetAsync(kernel_error.p, 0, sizeof(uint32_t), stream), "kernel status word");
+    // [0] status, [1] [2] the tensor-parallel exchange's sequence and ticket counters
+    kernel_error.alloc(4, "kernel status word");
+    cu(cudaMemsetAsync(kernel_error.p, 0, 4U * sizeof(uint32_t), stream), "kernel status word");
     if (c.experts) {
       moe_x.alloc(static_cast<size_t>(R) * c.hidden, "routed-expert input rows");
       moe_ws.alloc(moe_workspace_floats(R, c.route_width, c.hidden, c.expert_ffn), "routed-expert workspace");
@@ -340,32 +339,24 @@ struct qllm_provider {
       throw Error(QLLM_INVALID_ARGUMENT, "tensor-parallel provider used before qllm_provider_tp_attach");
     ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
                         final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream,
-                        exchange ? &tp_exchange[exchange_slot] : nullptr,
-                        exchange ? tp_exchange_dev.p + exchange_slot : nullptr));
+                        exchange ? &tp_exchange[exchange_slot] : nullptr));
     return o;
   }
-  // Fills the two per-slot exchange descriptors (host copy + device copy) once all areas are mapped.
+  // Fills the two per-slot exchange descriptors once all areas are mapped.
   void tp_describe() {
     for (uint32_t slot = 0; slot < 2U; ++slot) {
       GemvExchange x{};
       x.ranks = tp_ranks;
       x.rank = tp_rank;
-      for (uint32_t r = 0; r < tp_ranks; ++r) {
-        x.flags[r] = reinterpret_cast<uint32_t*>(tp_peer[r]);
-        x.inbox[r] = reinterpret_cast<float*>(tp_peer[r] + kTpFlagBytes) +
-                     static_cast<size_t>(slot) * tp_ranks * tp_slot_floats;
-      }
-      x.sequence = tp_words.p;
-      x.tickets = tp_words.p + 1;
-      x.capacity_floats = static_cast<size_t>(tp_ranks) * tp_slot_floats;
-      x.arrival = ExchangeArrival{x.flags[tp_rank], x.sequence, kernel_error.p, tp_ranks, tp_rank};
+      for (uint32_t r = 0; r < tp_ranks; ++r)
+        x.inbox[r] = reinterpret_cast<uint2*>(tp_peer[r]) + static_cast<size_t>(slot) * tp_ranks * tp_slot_pairs;
+      x.words = kernel_error.p;  // error word, then the exchange counter and the ticket counter
+      x.capacity = static_cast<size_t>(tp_ranks) * tp_slot_pairs;
       tp_exchange[slot] = x;
     }
-    tp_exchange_dev.alloc(2, "exchange descriptors");
-    cu(cudaMemcpy(tp_exchange_dev.p, tp_exchange, sizeof(tp_exchange), cudaMemcpyHostToDevice), "exchange descriptors");
     tp_attached = true;
   }
-  static constexpr size_t kTpFlagBytes = 256;
+
   // x' = act(x + delta) stored to `store`; operand of `next` = quantised rmsnorm(x') * weight
   void norm_quant(const float* x, uint32_t x_stride, const GemvOut* delta, float* store, const float* weight,
                   const Matrix* next, uint32_t rows, uint32_t sink_block_offset = 0,
@@ -954,14 +945,12 @@ int qllm_provider_tp_export(qllm_provider* p, uint32_t rank, uint32_t ranks, voi
     // one slot holds every rank's partials of the larger of the two K-split projections
     const size_t per_rank = std::max(gemv_partial_floats(qllm_provider::kMaxRows, c.hidden, c.q_heads * c.head_dim),
                                      gemv_partial_floats(qllm_provider::kMaxRows, c.hidden, c.ffn));
-    p->tp_slot_floats = (per_rank + 63U) & ~static_cast<size_t>(63U);
-    const size_t bytes = qllm_provider::kTpFlagBytes + 2U * ranks * p->tp_slot_floats * sizeof(float);
+    p->tp_slot_pairs = (per_rank + 63U) & ~static_cast<size_t>(63U);
+    const size_t bytes = 2U * ranks * p->tp_slot_pairs * sizeof(uint2);
     void* area = nullptr;
     cu(cudaMalloc(&area, bytes), "allocate the exchange area");
     p->tp_area = static_cast<uint8_t*>(area);
     cu(cudaMemset(area, 0, bytes), "clear the exchange area");
-    p->tp_words.alloc(2, "exchange counters");
-    cu(cudaMemset(p->tp_words.p, 0, 2U * sizeof(uint32_t)), "clear the exchange counters");
     cu(cudaDeviceSynchronize(), "exchange set-up");
     cudaIpcMemHandle_t h{};
     static_assert(sizeof(h) == QLLM_TP_HANDLE_BYTES, "handle size");

@@ -105,50 +105,16 @@ struct GemvOut {
   uint32_t batch;
   float weight_scale, input_scale;
   // Tensor-parallel exchange (null: none).  `data` is then a slot of this rank's inbox that
-  // holds every rank's partials ([rank][split][batch][n], `split` counting all of them); the
-  // peers' parts are complete once flags[r] has reached *sequence (exchange_wait below).
-  const struct ExchangeArrival* exchange;
+  // holds every rank's partials ([rank][split][batch][n], `split` counting all of them) as
+  // 8-byte pairs {FP32 bits, sequence number of the exchange}: a value is valid once its own
+  // sequence word equals exchange[1].  The pair is written by one 8-byte store, so no
+  // flag, fence or separate signal is involved (gemv_exchange_value4 below).
+  // exchange[0]: error word; exchange[1]: exchanges this rank has produced = the number to wait
+  // for; exchange[2]: ticket counter of the running producer launch.
+  uint32_t* exchange;
 };
 
-// Device-resident description of where the peers announce their deliveries.
-struct ExchangeArrival {
-  const uint32_t* flags;     // [ranks] last exchange each source rank has delivered here
-  const uint32_t* sequence;  // exchanges this rank has produced itself
-  uint32_t* error;
-  uint32_t ranks, rank;
-};
-
-constexpr unsigned long long kExchangeTimeoutNs = 2000000000ULL;  // a peer that is 2 s late counts as lost
-
-// Blocks the CTA until the peers' partial sums of `o` have arrived (call after the wait on the
-// producing kernel of this rank, before the first gemv_value).  The wait is bounded: after the
-// time limit an error word is set, and later waits return at once.
-__device__ __forceinline__ void exchange_wait(const GemvOut& out) {
-  if (out.exchange == nullptr) return;  // uniform over the grid
-  const ExchangeArrival o = *out.exchange;
-  if (o.ranks < 2U) return;
-  if (threadIdx.x == 0U && *reinterpret_cast<volatile uint32_t*>(o.error) == 0U) {
-    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(o.sequence);
-    unsigned long long start;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
-    for (uint32_t r = 0; r < o.ranks; ++r) {
-      if (r == o.rank) continue;
-      for (;;) {
-        uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.flags + r) : "memory");
-        if (static_cast<int32_t>(seen - target) >= 0) break;
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (now - start > kExchangeTimeoutNs) {
-          atomicExch(o.error, 200U + r);  // results from here on are invalid; nothing hangs
-          r = o.ranks;
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-}
+constexpr uint32_t kExchangePolls = 1U << 21U;  // about a second of polling: the peer counts as lost
 
 __device__ __forceinline__ float gemv_value(const GemvOut& o, uint32_t row, uint32_t col) {
   const size_t i = static_cast<size_t>(row) * o.n + col;
@@ -169,6 +135,54 @@ __device__ __forceinline__ float4 gemv_value4(const GemvOut& o, uint32_t row, ui
   for (uint32_t s = 1; s < o.split; ++s) {
     const float4 t = data[s * stride + i];
     sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+  }
+  return make_float4(bf16r(sum.x * o.weight_scale / o.input_scale), bf16r(sum.y * o.weight_scale / o.input_scale),
+                     bf16r(sum.z * o.weight_scale / o.input_scale), bf16r(sum.w * o.weight_scale / o.input_scale));
+}
+
+// The same four outputs of an exchanged result (o.exchange set): every partial is an 8-byte pair
+// {value, sequence}.  The loads of four partials go out together (one memory round trip when
+// everything has arrived); a batch is read again until all of its sequence words match.  The
+// wait is bounded: after the limit the error word is set and whatever is there is used; once
+// the error word is set nobody waits any more.  Partials are added in storage order (rank,
+// split), the same on every rank.
+__device__ __forceinline__ float4 gemv_exchange_value4(const GemvOut& o, uint32_t row, uint32_t col) {
+  const uint32_t sequence = *reinterpret_cast<const volatile uint32_t*>(o.exchange + 1);
+  const uint4* slot = reinterpret_cast<const uint4*>(o.data);  // two pairs per 16 bytes
+  const size_t stride = static_cast<size_t>(o.batch) * o.n / 2U, first = (static_cast<size_t>(row) * o.n + col) / 2U;
+  float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+  constexpr uint32_t kBatch = 4;
+  for (uint32_t s0 = 0; s0 < o.split; s0 += kBatch) {
+    uint4 lo[kBatch], hi[kBatch];
+    for (uint32_t poll = 0;; ++poll) {
+      bool complete = true;
+#pragma unroll
+      for (uint32_t k = 0; k < kBatch; ++k) {
+        if (s0 + k >= o.split) break;
+        const uint4* p = slot + (s0 + k) * stride + first;
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(lo[k].x), "=r"(lo[k].y), "=r"(lo[k].z), "=r"(lo[k].w) : "l"(p) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(hi[k].x), "=r"(hi[k].y), "=r"(hi[k].z), "=r"(hi[k].w) : "l"(p + 1) : "memory");
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < kBatch; ++k) {
+        if (s0 + k >= o.split) break;
+        complete = complete && lo[k].y == sequence && lo[k].w == sequence && hi[k].y == sequence && hi[k].w == sequence;
+      }
+      if (complete) break;
+      if (poll >= kExchangePolls ||
+          ((poll & 1023U) == 1023U && *reinterpret_cast<volatile uint32_t*>(o.exchange) != 0U)) {
+        atomicCAS(o.exchange, 0U, 200U);  // results from here on are invalid; nothing hangs
+        break;
+      }
+    }
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) {
+      if (s0 + k >= o.split) break;
+      sum.x += __uint_as_float(lo[k].x); sum.y += __uint_as_float(lo[k].z);
+      sum.z += __uint_as_float(hi[k].x); sum.w += __uint_as_float(hi[k].z);
+    }
   }
   return make_float4(bf16r(sum.x * o.weight_scale / o.input_scale), bf16r(sum.y * o.weight_scale / o.input_scale),
                      bf16r(sum.z * o.weight_scale / o.input_scale), bf16r(sum.w * o.weight_scale / o.input_scale));
