@@ -310,7 +310,7 @@ template <bool kExchange>
 __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                       const __grid_constant__ CUtensorMap act_map, GemvMmaParams p,
-                      const ExchangeParam<kExchange> e) {
+                      const __grid_constant__ ExchangeParam<kExchange> e) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_trigger();  // the consumer kernel may be scheduled; it waits for this grid to finish
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
@@ -318,7 +318,9 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
   __shared__ uint32_t abort_word;
   __shared__ uint2* exchange_inbox[8];  // tensor parallel: this exchange's slot in every rank's inbox
   if constexpr (kExchange) {
-    if (threadIdx.x < 8U) exchange_inbox[threadIdx.x] = e.x.inbox[threadIdx.x];
+#pragma unroll
+    for (uint32_t r = 0; r < 8U; ++r)  // constant indices: the parameter struct stays in the parameter space
+      if (threadIdx.x == r) exchange_inbox[r] = e.x.inbox[r];
   }
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023U) & ~uintptr_t(1023));
   const uint32_t tid = threadIdx.x, warp = tid >> 5U;
@@ -452,22 +454,29 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
             "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
           : "r"(lane_base + c0));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.row_count) {
+      if (kExchange) {
+        // [rank][split][batch][row_count] in the slot: one 8-byte store {value, sequence} per
+        // value and rank, into the peers' memory as well (rank loop outside, so that the
+        // accumulator registers keep constant indices)
+        if (row < p.row_count) {
+          const size_t first = (static_cast<size_t>(exchange_rank) * p.split + blockIdx.y) * p.batch;
+          for (uint32_t r = 0; r < exchange_ranks; ++r) {
+            uint2* slot = exchange_inbox[r];
+#pragma unroll
+            for (uint32_t j = 0; j < 16U; ++j) {
+              const uint32_t col = n_tile * 128U + c0 + j;
+              // one 8-byte store that bypasses L1 (st.global.cg.v2)
+              if (col < p.batch) __stcg(slot + (first + col) * p.row_count + row, make_uint2(v[j], exchange_sequence));
+            }
+          }
+        }
+      } else if (row < p.row_count) {
 #pragma unroll
         for (uint32_t j = 0; j < 16U; ++j) {
           const uint32_t col = n_tile * 128U + c0 + j;
           if (col >= p.batch) continue;
           const float acc = __uint_as_float(v[j]);
-          if (kExchange) {
-            // [rank][split][batch][row_count] in the slot: one 8-byte store {value, sequence} per
-            // rank, into the peers' memory as well
-            const size_t index = ((static_cast<size_t>(exchange_rank) * p.split + blockIdx.y) * p.batch + col) * p.row_count + row;
-            const uint2 pair = make_uint2(v[j], exchange_sequence);
-            for (uint32_t r = 0; r < exchange_ranks; ++r)
-              asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(exchange_inbox[r] + index), "r"(pair.x),
-                           "r"(pair.y)
-                           : "memory");
-          } else if (p.split == 1U && !p.raw)
+          if (p.split == 1U && !p.raw)
             p.y[static_cast<size_t>(col) * p.row_count + row] = bf16r(acc * p.weight_scale / p.input_scale);
           else
             p.partials[(static_cast<size_t>(blockIdx.y) * p.batch + col) * p.row_count + row] = acc;

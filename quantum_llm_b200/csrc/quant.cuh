@@ -141,7 +141,7 @@ __device__ __forceinline__ float4 gemv_value4(const GemvOut& o, uint32_t row, ui
 }
 
 // The same four outputs of an exchanged result (o.exchange set): every partial is an 8-byte pair
-// {value, sequence}.  The loads of four partials go out together (one memory round trip when
+// {value, sequence}.  The loads of eight partials go out together (one memory round trip when
 // everything has arrived); a batch is read again until all of its sequence words match.  The
 // wait is bounded: after the limit the error word is set and whatever is there is used; once
 // the error word is set nobody waits any more.  Partials are added in storage order (rank,
@@ -151,7 +151,7 @@ __device__ __forceinline__ float4 gemv_exchange_value4(const GemvOut& o, uint32_
   const uint4* slot = reinterpret_cast<const uint4*>(o.data);  // two pairs per 16 bytes
   const size_t stride = static_cast<size_t>(o.batch) * o.n / 2U, first = (static_cast<size_t>(row) * o.n + col) / 2U;
   float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-  constexpr uint32_t kBatch = 4;
+  constexpr uint32_t kBatch = 8;
   for (uint32_t s0 = 0; s0 < o.split; s0 += kBatch) {
     uint4 lo[kBatch], hi[kBatch];
     for (uint32_t poll = 0;; ++poll) {
