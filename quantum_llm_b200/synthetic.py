@@ -95,6 +95,17 @@ def shard_block(m, cfg, rank, ranks):
         down=m["down"].take_columns(rank * f, (rank + 1) * f))
 
 
+def gather_handles(mine, ranks, group=None):
+    """All ranks' exchange-area handles concatenated in rank order (what tp_attach takes)."""
+    if ranks == 1:
+        return bytes(mine)
+    import torch.distributed as dist
+    handles = [None] * ranks
+    dist.all_gather_object(handles, bytes(mine), group=group)
+    assert all(len(h) == _l.TP_HANDLE_BYTES for h in handles)
+    return b"".join(handles)
+
+
 class DeviceBlock:
     SHAPES = ("qkv", "o", "gate_up", "down")
 
@@ -191,17 +202,10 @@ class DeviceModel:
     def tensor_parallel_provider(self, group=None):
         """Provider of this rank's shard with the exchange areas of all ranks attached: the
         inter-process handles travel through `torch.distributed` (all-gather over `group`)."""
-        import torch.distributed as dist
         rank, ranks = self.tp
         provider = self.provider()
         provider.set_gemv_impl(1)
-        mine = provider.tp_export(rank, ranks)
-        handles = [None] * ranks
-        if ranks > 1:
-            dist.all_gather_object(handles, mine, group=group)
-        else:
-            handles[0] = mine
-        provider.tp_attach(b"".join(handles))
+        provider.tp_attach(gather_handles(provider.tp_export(rank, ranks), ranks, group))
         return provider
 
     # ---- algorithmic bytes (weights streamed once per pass; scales included)

@@ -68,6 +68,51 @@ def test_device_shards_match_the_host_rule():
     assert parts[1]["o"].cols == 64 and parts[1]["gate_up"].rows == 64 and parts[0]["o"].weight_scale == 0.5
 
 
+def test_two_gloo_ranks_gather_the_handles_in_rank_order(tmp_path):
+    # host side of the attach step on CPU: every rank ends up with [handle of rank 0 | handle of rank 1]
+    import json
+    import socket
+    import textwrap
+    script = tmp_path / "rank.py"
+    script.write_text(textwrap.dedent(f"""
+        import json, os, sys
+        sys.path.insert(0, {ROOT!r})
+        import torch.distributed as dist
+        from quantum_llm_b200 import synthetic
+        from tests import synth
+        from tests.test_tensor_parallel import TP_MODEL
+        rank = int(os.environ["RANK"])
+        dist.init_process_group("gloo")
+        mine = bytes([17 * (rank + 1)]) * 64
+        both = synthetic.gather_handles(mine, 2)
+        shard = synth.shard_model(synth.SynthModel(TP_MODEL, seed=3), rank, 2)
+        dist.barrier()
+        dist.destroy_process_group()
+        print(json.dumps({{"rank": rank, "handles": list(both), "o_cols": shard.layers[0].o.cols,
+                          "kv_heads": shard.cfg["kv_heads"]}}))
+    """))
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    for proc in procs:
+        out, err = proc.communicate(timeout=300)
+        assert proc.returncode == 0, err[-2000:]
+        got = json.loads(out.strip().splitlines()[-1])
+        assert got["handles"] == [17] * 64 + [34] * 64
+        assert got["o_cols"] == 256 and got["kv_heads"] == 1
+
+
+def test_single_rank_gather_needs_no_process_group():
+    from quantum_llm_b200 import synthetic
+    assert synthetic.gather_handles(b"\x05" * 64, 1) == b"\x05" * 64
+
+
 def _decode(p, model, generate, graph=True):
     from tests.gpu_util import request_pair
     prq, _ = request_pair(seed=1234, temperature_ppm=0, context_limit=model.cfg["max_context"])
