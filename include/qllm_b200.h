@@ -237,6 +237,37 @@ int qllm_descriptor_negotiate(const qllm_descriptor* descriptor, qllm_config* co
 const char* qllm_descriptor_tensor(const qllm_descriptor* descriptor, const char* role);
 size_t qllm_descriptor_dump(const qllm_descriptor* descriptor, char* out, size_t capacity);
 
+/* ---- dense QPack records: the on-disk form of the weights ---------------------------------------
+ * Host-only.  One dense tensor of the artifact manifest's index (the fields the reference's
+ * runtime takes from it, runtime/src/model_tensor_store.cpp:146-166) and the checks the reference's
+ * validator applies to its record (compiler/expert_pack/validate.py:131-318; record layout
+ * docs/expert-pack-v1.md:20-40, header compiler/expert_pack/constants.py:72-97): 4 KiB record
+ * alignment, 256-byte little-endian header with zero padding, magic and version, row-major flag,
+ * rank and shape, SHA-256 of the tensor name, data and scale sections equal to the index's, and per
+ * encoding: raw F32 / BF16 / I64 (ABI 0: no scale section, byte count = elements x width) or native
+ * NVFP4 (ABI 5: symmetric flag, matrix, columns % 16 == 0, rows x columns / 2 code bytes, scale
+ * section 256-byte aligned holding rows x columns / 16 finite E4M3FN bytes, the FP32 weight divisor
+ * and the FP32 or BF16 activation divisor, both finite and positive); with verify_payload the
+ * SHA-256 of everything after the header against the header's and the index's digests.  Other
+ * encodings (INT8, FP4 block-32, MXFP6) are rejected: this provider does not read them.
+ * qllm_pack_nvfp4_matrix additionally returns the matrix as the provider takes it: host pointers
+ * into the pack, weight_scale = 1 / weight divisor, input_scale = activation divisor
+ * (runtime/tools/dense_fp4_provider.cpp:3534-3568). */
+enum { QLLM_PACK_F32 = 0, QLLM_PACK_BF16 = 1, QLLM_PACK_I64 = 2, QLLM_PACK_FP4_E2M1 = 3 };
+typedef struct qllm_pack_entry {
+  const char* name;                 /* tensor name (its SHA-256 is in the record header) */
+  uint64_t offset, stored_bytes;    /* record position and size inside the pack */
+  uint32_t rank, shape[5];          /* logical shape ("source_shape") */
+  uint64_t data_offset, data_bytes; /* sections, relative to the record start */
+  uint64_t scale_offset, scale_bytes;
+  uint32_t stored_dtype;            /* QLLM_PACK_* ("stored_dtype") */
+  uint8_t payload_sha256[32];
+} qllm_pack_entry;
+int qllm_pack_check_dense(const void* pack, size_t pack_bytes, const qllm_pack_entry* entry, int verify_payload);
+int qllm_pack_nvfp4_matrix(const void* pack, size_t pack_bytes, const qllm_pack_entry* entry, int verify_payload,
+                           qllm_matrix* matrix);
+void qllm_sha256(const void* bytes, size_t count, uint8_t digest[32]);
+
 /* inspection for parity tests (device -> host copies) */
 int qllm_provider_read_logits(qllm_provider* provider, float* out, uint32_t rows);
 /* which = 0: rows retained by the last prefill chunk; 1: target rows of the last exact step. */

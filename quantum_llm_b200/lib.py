@@ -20,6 +20,16 @@ class Matrix(C.Structure):
                 ("input_scale", C.c_float), ("rows", C.c_uint32), ("cols", C.c_uint32)]
 
 
+class PackEntry(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("offset", C.c_uint64), ("stored_bytes", C.c_uint64), ("rank", C.c_uint32),
+                ("shape", C.c_uint32 * 5), ("data_offset", C.c_uint64), ("data_bytes", C.c_uint64),
+                ("scale_offset", C.c_uint64), ("scale_bytes", C.c_uint64), ("stored_dtype", C.c_uint32),
+                ("payload_sha256", C.c_uint8 * 32)]
+
+
+PACK_DTYPES = {"F32": 0, "BF16": 1, "I64": 2, "FP4_E2M1": 3}
+
+
 class Block(C.Structure):
     _fields_ = [("input_norm", C.c_void_p), ("qkv", Matrix), ("o", Matrix), ("post_norm", C.c_void_p),
                 ("gate_up", Matrix), ("down", Matrix),
@@ -78,6 +88,9 @@ SIGNATURES = {
     "qllm_provider_set_graph_mode": (ci, [vp, ci]),
     "qllm_provider_set_gemv_impl": (ci, [vp, ci]),
     "qllm_provider_set_attention_impl": (ci, [vp, ci]),
+    "qllm_pack_check_dense": (ci, [vp, sz, vp, ci]),
+    "qllm_pack_nvfp4_matrix": (ci, [vp, sz, vp, ci, vp]),
+    "qllm_sha256": (None, [vp, sz, vp]),
     "qllm_descriptor_parse": (ci, [C.c_char_p, sz, P(vp)]),
     "qllm_descriptor_destroy": (None, [vp]),
     "qllm_descriptor_negotiate": (ci, [vp, vp]),
