@@ -58,6 +58,8 @@ def parse():
     ap.add_argument("--split-tokens", type=int, default=0,
                     help="cached tokens per attention CTA (multiple of 64; 0 = the model configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--microbench", action="store_true",
+                    help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 160, 640")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
     args = ap.parse_args()
@@ -495,9 +497,80 @@ def ours(args):
         dist.destroy_process_group()
 
 
+def microbench(args):
+    """Kernel microbenchmark of the NVFP4 GEMV / skinny GEMM on the verify-step shapes: the 27B
+    projections (N x K: qkv 7168x5120, o 5120x5120, gate/up 34816x5120, down 5120x17408, lm-head
+    151936x5120) at M = 5, 40, 160, 640 activation rows.  Random NVFP4 weights, N(0,1)
+    activations; enough distinct matrices per shape to stream at least 1 GB (far beyond L2) per
+    timed pass; the tensor-core kernel alone, CUDA events on the launching stream.  One JSON line
+    per (shape, M): time, algorithmic GB/s (weights 0.5625 B/element + BF16 rows in and out) against
+    the measured HBM peak, and FP4 TFLOP/s (2 M N K) against the nominal dense 9 PFLOP/s."""
+    import torch
+    from quantum_llm_b200 import build as qbuild
+    qbuild.build()
+    from quantum_llm_b200 import lib as ql
+    from quantum_llm_b200 import synthetic
+    L = ql.load()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    try:
+        hbm_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs", 6650.0))
+    except OSError:
+        hbm_peak = 6650.0
+    shapes = [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate_up", 34816, 5120), ("down", 5120, 17408),
+              ("lm_head", 151936, 5120)]
+    stream = torch.cuda.Stream(device=dev)
+    sp = C.c_void_p(stream.cuda_stream)
+    for name, n, k in shapes:
+        weight_bytes = n * k * 9 // 16
+        copies = max(1, -(-(1 << 30) // weight_bytes))
+        mats, handles = [], []
+        for i in range(copies):
+            m = synthetic.quantize(synthetic._random_rows(n, k, 7000 + i, dev))
+            h, cm = C.c_void_p(), m.c()
+            ql.check(L.qllm_k_matrix_prepare(C.byref(cm), sp, C.byref(h)))
+            mats.append(m)
+            handles.append(h)
+        stream.synchronize()
+        for rows in (5, 40, 160, 640):
+            x = torch.randn((rows, k), device=dev, dtype=torch.float32)
+            y = torch.empty((rows, n), device=dev, dtype=torch.float32)
+            ws_bytes = L.qllm_k_nvfp4_gemv_workspace_bytes(rows, n, k)
+            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+            best = None
+            with torch.cuda.stream(stream):
+                # one full call quantises the activations into the workspace
+                ql.check(L.qllm_k_nvfp4_gemv_prepared(handles[0], x.data_ptr(), y.data_ptr(), rows, ws.data_ptr(),
+                                                     ws_bytes, 1, sp))
+                for rep in range(4):
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(stream)
+                    for h in handles:
+                        ql.check(L.qllm_k_nvfp4_gemv_prepared_core(h, rows, ws.data_ptr(), ws_bytes, sp))
+                    stop.record(stream)
+                    stop.synchronize()
+                    ms = start.elapsed_time(stop) / len(handles)
+                    if rep > 0:
+                        best = ms if best is None else min(best, ms)
+            algorithmic = weight_bytes + rows * k * 2 + rows * n * 2
+            gbs = algorithmic / (best * 1e-3) / 1e9
+            tflops = 2.0 * rows * n * k / (best * 1e-3) / 1e12
+            print(json.dumps({"microbench": "nvfp4_gemv_mma", "shape": name, "n": n, "k": k, "m": rows,
+                              "us": best * 1e3, "algorithmic_bytes": algorithmic, "gbs": gbs,
+                              "frac_of_hbm": gbs / hbm_peak, "fp4_tflops": tflops,
+                              "frac_of_nominal_fp4": tflops / 9000.0, "matrices": copies}), flush=True)
+            del x, y, ws
+        for h in handles:
+            L.qllm_k_matrix_release(h)
+        del mats, handles
+        torch.cuda.empty_cache()
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.impl == "reference":
+    if a.microbench:
+        microbench(a)
+    elif a.impl == "reference":
         reference_arm(a)
     else:
         ours(a)

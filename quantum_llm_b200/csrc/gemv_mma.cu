@@ -555,10 +555,11 @@ int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_ro
 // the same workspace, matrix and batch left behind; leaves split-K partials in the workspace.
 int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_t batch, void* workspace,
                               size_t workspace_bytes, cudaStream_t stream) {
-  if (!w.ready || m.cols % kTileK || !batch || batch > 128U)
-    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, rows <= 128)");
+  if (!w.ready || m.cols % kTileK || !batch)
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
   const uint32_t row_tiles = (m.rows + kTileRows - 1U) / kTileRows;
-  const uint32_t split = pick_split(row_tiles, 1U, m.cols / kTileK);
+  const uint32_t n_tiles = ((batch + 15U) / 16U * 16U + 127U) / 128U;  // 128 activation rows per CTA
+  const uint32_t split = pick_split(row_tiles, n_tiles, m.cols / kTileK);
   size_t need = 0;
   const MmaWorkspace ws = carve(workspace, batch, m.rows, m.cols, split, &need);
   if (need > workspace_bytes) return fail(QLLM_INVALID_ARGUMENT, "tensor-core GEMV workspace is too small");
@@ -589,8 +590,10 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   if (rc) return rc;
   const uint32_t b_bytes = std::min(n_pad, 128U) * 128U;
   const uint32_t stage_bytes = kABytes + kSfBytes + ((b_bytes + 1023U) & ~1023U) + kSfBytes;
-  uint32_t stages = stage_bytes * 4U <= 100U * 1024U ? 4U : std::min(6U, (200U * 1024U) / stage_bytes);
-  stages = std::max(2U, std::min(stages, 8U));
+  // as many stages (at most 4) as leave room for two CTAs per SM: the split-K rule above sizes
+  // the grid to one wave of two CTAs per SM, whatever the width of the activation tile
+  uint32_t stages = 4U;
+  while (stages > 2U && stages * stage_bytes > 108U * 1024U) --stages;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024U;
   static size_t opted = 0;
   if (smem > opted) {
