@@ -214,13 +214,15 @@ moe_gate_up_kernel(MoeArgs a) {
 // row once, then walks over its share of the selection's 16-row tiles.  The 16 gate rows and the
 // 16 up rows of a tile are contiguous in the expert's tensors, so one elected thread brings a
 // tile in with four bulk asynchronous copies (codes and scales of each projection, 36 KB at
-// hidden 2048) that complete on the stage's mbarrier; two stages, so the next tile streams in
-// while the warps work on the current one (two rows of each projection per warp).  Two CTAs per
-// SM; the grid is sized to one wave.  Needs hidden % 256 == 0 (16-byte granules of the scale
-// rows) and 16-byte aligned expert tensors; other shapes use the kernel above.
+// hidden 2048) that complete on the stage's mbarrier (two rows of each projection per warp).
+// One stage and five CTAs per SM: the kernel spends its time at CTA barriers and on the integer
+// pipe, so what pays is occupancy (other CTAs stream and compute meanwhile), not a deeper ring
+// inside a CTA (two stages at two CTAs per SM were 10 % slower in the whole step).  The grid is
+// sized to one wave.  Needs hidden % 256 == 0 (16-byte granules of the scale rows) and 16-byte
+// aligned expert tensors; other shapes use the kernel above.
 constexpr uint32_t kStagedRows = 16;
 constexpr uint32_t kStagedThreads = 256;
-constexpr uint32_t kStagedStages = 2;
+constexpr uint32_t kStagedStages = 1;
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -272,7 +274,7 @@ __host__ __device__ inline uint32_t staged_stage_bytes(uint32_t hidden) {
   return 2U * kStagedRows * (hidden / 2U + hidden / 16U);
 }
 
-__global__ void __launch_bounds__(kStagedThreads, 2)
+__global__ void __launch_bounds__(kStagedThreads, 5)
 moe_gate_up_staged_kernel(MoeArgs a, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) float mid_tile[kStagedRows];
@@ -409,17 +411,17 @@ moe_down_kernel(MoeArgs a) {
 // quantised mid row in shared memory and walks over the CTA's share of the 8-column tiles; the
 // 8 weight rows of a tile and slot are contiguous in the expert's tensor, so lane 0 of each warp
 // brings them in with two bulk copies (codes, scales) onto the stage's mbarrier, which expects
-// one arrival per warp.  Two stages: the next tile streams in while the current one is reduced.
-// Needs expert_ffn % 256 == 0 and 16-byte aligned expert tensors.
+// one arrival per warp.  One stage, four CTAs per SM (occupancy over ring depth, as above).
+// Needs expert_ffn % 32 == 0 and 16-byte aligned expert tensors.
 constexpr uint32_t kDownTile = 8;
-constexpr uint32_t kDownStages = 2;
+constexpr uint32_t kDownStages = 1;
 
 __host__ __device__ inline uint32_t down_tile_bytes(uint32_t expert_ffn) {
   return kDownTile * (expert_ffn / 2U + expert_ffn / 16U);  // one slot's codes + scales of a tile
 }
 
 template <int LANES>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
 moe_down_staged_kernel(MoeArgs a, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float out_tile[8][kDownTile];
@@ -561,9 +563,9 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
       if (rc) return rc;
       opted = 110U * 1024U;
     }
-    // one wave: two CTAs per SM (148 SMs), shared evenly by the selections
+    // one wave: five CTAs per SM (148 SMs), shared evenly by the selections
     const uint32_t tiles = a.expert_ffn / kStagedRows;
-    const uint32_t per_selection = std::max(1U, std::min(tiles, 296U / selections));
+    const uint32_t per_selection = std::max(1U, std::min(tiles, 740U / selections));
     rc = check_cuda(launch_pdl(moe_gate_up_staged_kernel, dim3(per_selection, selections), dim3(kStagedThreads),
                                smem_staged, stream, a, a.error), "moe_gate_up_staged");
   } else {
@@ -586,8 +588,8 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
       if (rc) return rc;
       opted = true;
     }
-    // one wave: three CTAs per SM, shared evenly by the rows
-    const uint32_t per_row = std::max(1U, std::min(a.hidden / kDownTile, 444U / a.rows));
+    // one wave: four CTAs per SM, shared evenly by the rows
+    const uint32_t per_row = std::max(1U, std::min(a.hidden / kDownTile, 592U / a.rows));
     const dim3 staged_grid(per_row, a.rows);
     if (wide)
       return check_cuda(launch_pdl(moe_down_staged_kernel<32>, staged_grid, dim3(256), smem_down_staged, stream, a,
