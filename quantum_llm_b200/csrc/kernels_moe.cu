@@ -25,19 +25,22 @@ namespace qllm {
 
 namespace {
 
+template <int R, int LANES>
+__device__ __forceinline__ void rows_dot(const ExpertMatrix& m, uint32_t first_row, uint32_t last_row, uint32_t cols,
+                                         const int8_t* xi8, const float* xscale, uint32_t lane_in_group,
+                                         double (&acc)[R]);  // defined with the expert projections below
+
 // ---- router: one warp per row -------------------------------------------------------------
-__global__ void __launch_bounds__(32)
-moe_router_select_kernel(GemvOut logits, uint32_t experts, uint32_t top_k, float route_scale, uint32_t* indices,
-                         float* scores) {
-  pdl_trigger();
-  pdl_wait();
-  const uint32_t row = blockIdx.x, lane = threadIdx.x;
+// Selection and scores of one row by one warp; logit(e) returns the router logit of expert e.
+template <class Logit>
+__device__ __forceinline__ void route_row(Logit logit, uint32_t row, uint32_t lane, uint32_t experts, uint32_t top_k,
+                                          float route_scale, uint32_t* indices, float* scores) {
   constexpr uint32_t kPerLane = 8;  // up to 256 experts
   float value[kPerLane];
 #pragma unroll
   for (uint32_t i = 0; i < kPerLane; ++i) {
     const uint32_t e = lane + 32U * i;
-    value[i] = e < experts ? bf16r(gemv_value(logits, row, e)) : kNegInf;
+    value[i] = e < experts ? bf16r(logit(e)) : kNegInf;
   }
   uint32_t taken = 0U;  // bit i: this lane's i-th expert is already selected
   float chosen_value[8];
@@ -89,6 +92,61 @@ moe_router_select_kernel(GemvOut logits, uint32_t experts, uint32_t top_k, float
     scores[row * top_k + lane] = bf16r(v);
     indices[row * top_k + lane] = my_index;
   }
+}
+
+// Selection from a router GEMV result that some earlier kernel left behind.
+__global__ void __launch_bounds__(32)
+moe_router_select_kernel(GemvOut logits, uint32_t experts, uint32_t top_k, float route_scale, uint32_t* indices,
+                         float* scores) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t row = blockIdx.x;
+  route_row([&](uint32_t e) { return gemv_value(logits, row, e); }, row, threadIdx.x, experts, top_k, route_scale,
+            indices, scores);
+}
+
+// Router projection and selection in one launch: grid (chunks of 16 experts, rows), 8 warps.
+// The row's quantised operand (INT8 values + block scales, written by the norm kernel before) is
+// dotted with the experts' router rows, two per warp, with the exact block arithmetic of the
+// CUDA-core GEMV (logit = bf16(float(S) * weight_scale / input_scale)).  The CTAs of a row leave
+// their logits in the workspace and take a ticket; the last one to arrive selects (every other
+// CTA's logits are visible to it: fence before the ticket, fence after).  Replaces a GEMV launch,
+// its split-K partials and a selection launch.
+constexpr uint32_t kRouterChunk = 16;
+
+__global__ void __launch_bounds__(256)
+moe_router_kernel(ExpertMatrix router, const int8_t* xi8, const float* xscale, MoeArgs a) {
+  __shared__ uint32_t last;
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t row = blockIdx.y, warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
+  const uint32_t H = a.hidden, blocks = H / 16U;
+  const int8_t* x = xi8 + static_cast<size_t>(row) * H;
+  const float* xs = xscale + static_cast<size_t>(row) * blocks;
+  float* logits = a.router_logits + static_cast<size_t>(row) * 256U;
+  const uint32_t first = blockIdx.x * kRouterChunk + warp * 2U;
+  if (first < a.experts) {
+    double sum[2];
+    rows_dot<2, 32>(router, first, a.experts - 1U, H, x, xs, lane, sum);
+#pragma unroll
+    for (uint32_t r = 0; r < 2U; ++r)
+      if (lane == r && first + r < a.experts)
+        logits[first + r] = bf16r(static_cast<float>(sum[r]) * router.weight_scale / router.input_scale);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0U) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(a.router_tickets + row, 1U);
+    last = ticket == gridDim.x - 1U ? 1U : 0U;
+    if (last) {
+      a.router_tickets[row] = 0U;  // for the next launch (stream order)
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  if (last && warp == 0U)
+    route_row([&](uint32_t e) { return __ldcg(logits + e); }, row, lane, a.experts, a.route_width, a.route_scale,
+              a.indices, a.scores);
 }
 
 // ---- shared pieces of the two expert projections ---------------------------------------------
@@ -521,13 +579,17 @@ inline size_t round4(size_t n) { return (n + 3U) & ~static_cast<size_t>(3U); }  
 
 size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn) {
   const size_t selections = static_cast<size_t>(rows) * route_width;
-  // indices | scores | quantised mid (INT8 values, then FP32 block scales) | moe
-  return round4(2U * selections) + round4(selections * (expert_ffn / 4U)) + round4(selections * (expert_ffn / 16U)) +
-         static_cast<size_t>(rows) * hidden;
+  // router tickets (fixed place) | router logits | indices | scores | quantised mid (INT8 values,
+  // then FP32 block scales) | moe
+  return 8U + static_cast<size_t>(rows) * 256U + round4(2U * selections) + round4(selections * (expert_ffn / 4U)) +
+         round4(selections * (expert_ffn / 16U)) + static_cast<size_t>(rows) * hidden;
 }
 
 void moe_carve_workspace(float* base, MoeArgs& a) {
   const size_t selections = static_cast<size_t>(a.rows) * a.route_width;
+  a.router_tickets = reinterpret_cast<uint32_t*>(base);  // zero between launches, whatever the row count
+  a.router_logits = base + 8U;
+  base += 8U + static_cast<size_t>(a.rows) * 256U;
   a.indices = reinterpret_cast<uint32_t*>(base);
   a.scores = base + selections;
   float* mid = base + round4(2U * selections);
@@ -542,6 +604,19 @@ int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream
   count_launch();
   return check_cuda(launch_pdl(moe_router_select_kernel, dim3(a.rows), dim3(32), 0, stream, logits, a.experts,
                                a.route_width, a.route_scale, a.indices, a.scores), "moe_router_select");
+}
+
+int launch_moe_router(const ExpertMatrix& router, const QuantSink& operand, const MoeArgs& a, cudaStream_t stream) {
+  if (!a.rows || !a.route_width || a.route_width > 8U || a.route_width > a.experts || a.experts > 256U)
+    return fail(QLLM_INVALID_ARGUMENT, "router needs 1..8 selections out of at most 256 experts");
+  if (operand.kind != 0 || operand.cols != a.hidden || a.hidden % 16U)
+    return fail(QLLM_INVALID_ARGUMENT, "the router reads the CUDA-core operand form of the normalised row");
+  count_launch();
+  if (!a.router_logits || !a.router_tickets) return fail(QLLM_INVALID_ARGUMENT, "router workspace is missing");
+  return check_cuda(launch_pdl(moe_router_kernel, dim3((a.experts + kRouterChunk - 1U) / kRouterChunk, a.rows),
+                               dim3(256), 0, stream, router,
+                               static_cast<const int8_t*>(operand.xi8), static_cast<const float*>(operand.xscale), a),
+                    "moe_router");
 }
 
 int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {

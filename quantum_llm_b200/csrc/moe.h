@@ -31,6 +31,8 @@ struct MoeArgs {
   int8_t* mid_i8;          // [rows * route_width, expert_ffn] mid quantised for the down projection
   float* mid_scale;        // [rows * route_width, expert_ffn / 16] its block scales
   float* moe;              // [rows, hidden] BF16-rounded weighted sum (added to the residual by the next norm)
+  float* router_logits;    // [rows, 256] BF16-rounded router logits (fused router kernel)
+  uint32_t* router_tickets;  // [8] arrival counters of that kernel's CTAs per row, zero between launches
   bool staged;             // every expert tensor is 16-byte aligned: the gate/up weights may come in by bulk copies
   uint32_t* error;         // status word set when a bounded wait runs out
 };
@@ -42,6 +44,9 @@ size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden
 void moe_carve_workspace(float* base, MoeArgs& a);
 // top-K selection + normalised scores from the router GEMV result
 int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream_t stream);
+// router projection (exact CUDA-core arithmetic over the INT8 operand `operand`, kind 0) and
+// selection in one launch
+int launch_moe_router(const ExpertMatrix& router, const QuantSink& operand, const MoeArgs& a, cudaStream_t stream);
 // gate/up/SiLU, then down with the ordered weighted sum (two launches)
 int launch_moe_experts(const MoeArgs& a, cudaStream_t stream);
 

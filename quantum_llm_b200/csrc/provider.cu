@@ -202,6 +202,7 @@ struct qllm_provider {
     }
     if (!b.expert_gate || !b.expert_up || !b.expert_down) throw Error(QLLM_INVALID_ARGUMENT, "missing expert tensors");
     out.router = bring(b.router, on_device, c.experts, c.hidden, "router");
+    out.router.mma.release();  // consumed by moe_router_kernel (CUDA cores) whatever the GEMV implementation
     out.expert_gate = bring_experts(b.expert_gate, on_device, c.expert_ffn, c.hidden, "expert gate");
     out.expert_up = bring_experts(b.expert_up, on_device, c.expert_ffn, c.hidden, "expert up");
     out.expert_down = bring_experts(b.expert_down, on_device, c.hidden, c.expert_ffn, "expert down");
@@ -294,7 +295,10 @@ struct qllm_provider {
     cu(cudaMemsetAsync(kernel_error.p, 0, 4U * sizeof(uint32_t), stream), "kernel status word");
     if (c.experts) {
       moe_x.alloc(static_cast<size_t>(R) * c.hidden, "routed-expert input rows");
-      moe_ws.alloc(moe_workspace_floats(R, c.route_width, c.hidden, c.expert_ffn), "routed-expert workspace");
+      const size_t moe_floats = moe_workspace_floats(R, c.route_width, c.hidden, c.expert_ffn);
+      moe_ws.alloc(moe_floats, "routed-expert workspace");
+      // the router kernel's arrival counters at its start count from zero
+      cu(cudaMemsetAsync(moe_ws.p, 0, moe_floats * sizeof(float), stream), "routed-expert workspace");
     }
     mtp_emb.alloc(static_cast<size_t>(R) * c.hidden, "draft embedding");
     draft_logits.alloc(c.draft_vocab, "draft logits");
@@ -388,7 +392,6 @@ struct qllm_provider {
   void routed_experts(const Block& b, float* h, const GemvOut& attention_out, uint32_t rows, GemvOut* pending) {
     const auto& c = cfg;
     norm_quant(h, c.hidden, &attention_out, h, b.post_norm, &b.router, rows, 0U, nullptr, moe_x.p, true);
-    const GemvOut logits = gemv(b.router, rows);
     MoeArgs a{};
     a.x = moe_x.p;
     a.x_stride = c.hidden;
@@ -404,7 +407,10 @@ struct qllm_provider {
     a.gate = b.expert_gate;
     a.up = b.expert_up;
     a.down = b.expert_down;
-    ok(launch_moe_router_select(logits, a, stream));
+    // router projection + selection in one launch over the INT8 operand the norm kernel left
+    // (the router always takes the CUDA-core operand form: its matrix has no tensor-core view)
+    ok(launch_moe_router(ExpertMatrix{b.router.m.codes, b.router.m.scales, b.router.m.weight_scale, b.router.m.input_scale},
+                         sink_for(b.router, rows), a, stream));
     ok(launch_moe_experts(a, stream));
     GemvOut result{};
     result.data = a.moe;  // final values: the next norm kernel adds them to the residual stream
