@@ -147,6 +147,23 @@ def test_head_dim_128_caches(kv_encoding, attention_impl):
         assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
 
 
+def test_group_8_tensor_core_attention_inside_a_step():
+    # 8 query heads on one kv head (the routed model's grouping: 40 matrix rows per kv head),
+    # two layers, so that the second layer's records sit at a non-zero layer offset
+    cfg = dict(WIDE, q_heads=8, kv_heads=1, kv_encoding=ob.KV_Q4H)
+    model = synth.SynthModel(cfg, seed=6)
+    prompt = synth.prompt(4096, 128, 6)
+    gpu = run_gpu(model, prompt, 0, 24, graph=True, attention_impl=1)
+    cpu = run_cpu(model, prompt, 0, 24)
+    c = compare(gpu, cpu, len(prompt))
+    print("group 8 parity", c)
+    assert gpu["stream"][0] == cpu["stream"][0]
+    assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
+    exact = run_gpu(model, prompt, 0, 24, graph=True, attention_impl=0)
+    e = compare(exact, cpu, len(prompt))
+    assert e["prefix"] == 25 and e["exact"] == e["shared"]
+
+
 def test_greedy_stream_equals_plain_target_decoding_on_gpu():
     # property that needs no oracle: speculative greedy output does not depend on the drafts,
     # so a provider with a different draft block emits the same tokens
