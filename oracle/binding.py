@@ -57,6 +57,16 @@ class StepResult(C.Structure):
                 ("rejected", C.c_uint32)]
 
 
+def _makefile_reference():
+    for line in open(os.path.join(HERE, "Makefile")):
+        if line.startswith("REFERENCE ?="):
+            return line.split("=", 1)[1].strip()
+    return ""
+
+
+REFERENCE_DEFAULT = _makefile_reference()
+
+
 def build(force=False):
     """Compile the oracle (and oracle/_ref when the reference tree exists)."""
     lib = os.path.join(HERE, "libqllm_oracle.so")
@@ -65,9 +75,12 @@ def build(force=False):
     if force or not os.path.exists(lib) or os.path.getmtime(lib) < src_time:
         subprocess.run(["make", "-C", HERE, "libqllm_oracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
-    ref = os.path.join(HERE, "_ref", "libqllm_ref_sampler.so")
-    if (force or not os.path.exists(ref)) and os.path.isdir("/root/reference"):
-        subprocess.run(["make", "-C", HERE, "ref"], check=True, stdout=subprocess.DEVNULL)
+    # the reference's own sampler and descriptor parser, where the reference tree is present
+    # (QLLM_REFERENCE, else the Makefile's default location); prebuilt files are kept otherwise
+    refs = [os.path.join(HERE, "_ref", name) for name in ("libqllm_ref_sampler.so", "libqllm_ref_descriptor.so")]
+    reference = os.environ.get("QLLM_REFERENCE", REFERENCE_DEFAULT)
+    if (force or not all(os.path.exists(r) for r in refs)) and os.path.isdir(reference):
+        subprocess.run(["make", "-C", HERE, "ref", f"REFERENCE={reference}"], check=True, stdout=subprocess.DEVNULL)
     return lib
 
 

@@ -1,5 +1,6 @@
-"""Regenerates tests/golden/*.json.  Run in a container that has the reference
-tree at /root/reference; the parity tests only read the committed JSON.
+"""Regenerates tests/golden/*.json.  Run where the reference tree is present (its location:
+QLLM_REFERENCE, else the default of oracle/Makefile); the parity tests only read the committed
+JSON.
 
   fp4_tables.json     decode tables produced by importing the reference's Python
                       decoders (compiler/expert_pack/fp4_reference.py)
@@ -16,7 +17,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, "/root/reference/compiler")
+from oracle.binding import REFERENCE_DEFAULT  # noqa: E402
+sys.path.insert(0, os.path.join(os.environ.get("QLLM_REFERENCE", REFERENCE_DEFAULT), "compiler"))
 
 
 def fp4_tables():

@@ -19,7 +19,9 @@ from pathlib import Path
 import numpy as np
 
 ROOT = Path(__file__).resolve().parents[2]
-REFERENCE = Path(os.environ.get("QLLM_REFERENCE", "/root/reference"))
+sys.path.insert(0, str(ROOT))
+from oracle.binding import REFERENCE_DEFAULT  # noqa: E402
+REFERENCE = Path(os.environ.get("QLLM_REFERENCE", REFERENCE_DEFAULT))
 
 
 def bf16_bytes(x):
