@@ -13,6 +13,9 @@ GPU (their rows are not batched into one pass).  `--parallelism tp` shards ONE s
 over the N GPUs instead (q/k/v heads and FFN columns per rank, partial sums of the o and down
 projections exchanged through peer memory inside the GEMV kernel).
 
+`--microbench` times the tensor-core GEMV alone on the verify-step projection shapes at
+M = 5, 40, 160, 640 rows (one JSON line per shape and M).
+
   python bench.py --gpus N --steps K --warmup W [--impl reference]
 """
 import argparse
