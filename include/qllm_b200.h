@@ -266,6 +266,28 @@ typedef struct qllm_pack_entry {
 int qllm_pack_check_dense(const void* pack, size_t pack_bytes, const qllm_pack_entry* entry, int verify_payload);
 int qllm_pack_nvfp4_matrix(const void* pack, size_t pack_bytes, const qllm_pack_entry* entry, int verify_payload,
                            qllm_matrix* matrix);
+/* One routed expert of the manifest's expert index and its record (magic EPEXPR01; header
+ * compiler/expert_pack/constants.py:88-92, writer compiler/expert_pack/writer.py:417-552, checks
+ * compiler/expert_pack/validate.py:328-482), native NVFP4 (ABI 5) only: flags row-major | symmetric |
+ * gate-up-fused, layer / expert identity, four 256-byte aligned, ordered, non-overlapping
+ * sections equal to the index's — gate+up codes (gate then up, intermediate x hidden / 2 bytes
+ * each), gate+up sidecars, down codes, down sidecars — where a matrix's sidecar is its E4M3FN
+ * block scales followed by the FP32 weight divisor and the FP32 activation divisor (finite,
+ * positive), decoded size 3 x hidden x intermediate x 4, and optionally the payload SHA-256.
+ * qllm_pack_nvfp4_expert returns the three projections as the provider takes them
+ * (qllm_block.expert_gate / expert_up / expert_down entries): gate and up [intermediate, hidden],
+ * down [hidden, intermediate], pointers into the pack. */
+typedef struct qllm_pack_expert_entry {
+  int32_t layer, expert;
+  uint64_t offset, stored_bytes;
+  uint64_t section_offset[4], section_bytes[4]; /* gate_up_q, gate_up_scales, down_q, down_scales */
+  uint64_t decoded_bytes;
+  uint8_t payload_sha256[32];
+} qllm_pack_expert_entry;
+int qllm_pack_check_expert(const void* pack, size_t pack_bytes, const qllm_pack_expert_entry* entry,
+                           int verify_payload);
+int qllm_pack_nvfp4_expert(const void* pack, size_t pack_bytes, const qllm_pack_expert_entry* entry,
+                           int verify_payload, qllm_matrix* gate, qllm_matrix* up, qllm_matrix* down);
 void qllm_sha256(const void* bytes, size_t count, uint8_t digest[32]);
 
 /* inspection for parity tests (device -> host copies) */

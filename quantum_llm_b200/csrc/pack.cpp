@@ -191,9 +191,131 @@ int check_dense(const uint8_t* pack, size_t pack_bytes, const qllm_pack_entry& e
   return QLLM_OK;
 }
 
+// ---- routed-expert records (EPEXPR01), native NVFP4 ----------------------------------------------
+// Header: magic, version, header bytes, flags, quant ABI, layer, expert, hidden, intermediate,
+// rows of the first section, reserved, record bytes, four (offset, bytes) pairs — gate+up codes,
+// gate+up sidecars, down codes, down sidecars — and the payload SHA-256
+// (compiler/expert_pack/constants.py:88-92, writer.py:417-552).  A native NVFP4 matrix's sidecars are its
+// E4M3FN block scales, the FP32 weight divisor and the FP32 activation divisor; the first section
+// holds gate then up.  Rules of validate_expert_record (validate.py:328-482) for ABI 5.
+constexpr uint32_t kGateUpFused = 1U << 1;
+
+struct ExpertHeader {
+  uint32_t flags, quant_abi, hidden, intermediate, fused_rows, reserved;
+  int32_t layer, expert;
+  uint64_t record_bytes, offset[4], bytes[4];
+  uint8_t payload_hash[32];
+};
+
+int check_expert(const uint8_t* pack, size_t pack_bytes, const qllm_pack_expert_entry& e, bool verify_payload,
+                 ExpertHeader& h) {
+  if (e.stored_bytes < kHeaderBytes) return bad("invalid expert size");
+  if (e.offset % kPackAlignment || e.stored_bytes % kPackAlignment) return bad("unaligned expert record");
+  if (e.offset > pack_bytes || pack_bytes - e.offset < kHeaderBytes) return bad("short expert header");
+  const uint8_t* raw = pack + e.offset;
+  for (size_t i = kHeaderFields; i < kHeaderBytes; ++i)
+    if (raw[i]) return bad("expert header padding is nonzero");
+  const uint8_t* p = raw + 8;
+  const uint16_t version = little<uint16_t>(p), header_bytes = little<uint16_t>(p);
+  h.flags = little<uint32_t>(p);
+  h.quant_abi = little<uint32_t>(p);
+  h.layer = static_cast<int32_t>(little<uint32_t>(p));
+  h.expert = static_cast<int32_t>(little<uint32_t>(p));
+  h.hidden = little<uint32_t>(p);
+  h.intermediate = little<uint32_t>(p);
+  h.fused_rows = little<uint32_t>(p);
+  h.reserved = little<uint32_t>(p);
+  h.record_bytes = little<uint64_t>(p);
+  for (int i = 0; i < 4; ++i) {
+    h.offset[i] = little<uint64_t>(p);
+    h.bytes[i] = little<uint64_t>(p);
+  }
+  std::memcpy(h.payload_hash, p, 32);
+  if (std::memcmp(raw, "EPEXPR01", 8) != 0 || version != 1U) return bad("unknown expert record ABI");
+  if (header_bytes != kHeaderBytes || h.reserved != 0U) return bad("invalid expert header fields");
+  if (h.quant_abi != 5U) {
+    // INT8 (1), FP4 block-32 (3) and its ReLU2 layout (4) are other providers' encodings
+    if (h.quant_abi == 1U || h.quant_abi == 3U || h.quant_abi == 4U)
+      return bad("expert quantization ABI is not read by this provider");
+    return bad("unknown expert quant/layout ABI");
+  }
+  if (h.flags != (kRowMajor | kSymmetric | kGateUpFused)) return bad("unknown expert quant/layout ABI");
+  if (h.layer != e.layer || h.expert != e.expert) return bad("expert identity mismatch");
+  if (h.record_bytes != e.stored_bytes) return bad("expert record/manifest size mismatch");
+  if (h.fused_rows != 2ULL * h.intermediate) return bad("expert first-section row count mismatch");
+  const uint64_t elements = static_cast<uint64_t>(h.hidden) * h.intermediate, local = elements / 16U;
+  if (h.hidden % 16U || h.intermediate % 16U) return bad("NVFP4 expert geometry is not block-aligned");
+  if (h.bytes[0] != elements) return bad("NVFP4 gate+up byte count mismatch");
+  if (h.bytes[1] != 2U * (local + 8U)) return bad("NVFP4 gate+up scale byte count mismatch");
+  if (h.bytes[2] != elements / 2U) return bad("NVFP4 down byte count mismatch");
+  if (h.bytes[3] != local + 8U) return bad("NVFP4 down scale byte count mismatch");
+  for (int i = 0; i < 4; ++i)
+    if (e.section_offset[i] != h.offset[i] || e.section_bytes[i] != h.bytes[i]) return bad("expert section index mismatch");
+  uint64_t previous_end = kHeaderBytes;
+  for (int i = 0; i < 4; ++i) {
+    if (h.offset[i] % kSectionAlignment) return bad("unaligned expert section");
+    if (h.offset[i] < previous_end) return bad("overlapping expert section");
+    if (h.offset[i] > h.record_bytes || h.bytes[i] > h.record_bytes - h.offset[i]) return bad("expert section exceeds record");
+    previous_end = h.offset[i] + h.bytes[i];
+  }
+  if (pack_bytes - e.offset < h.record_bytes) return bad("short record read");
+  const uint64_t sidecars[3] = {h.offset[1], h.offset[1] + local + 8U, h.offset[3]};
+  static const char* const kNonFinite[3] = {"non-finite gate E4M3FN scale", "non-finite up E4M3FN scale",
+                                            "non-finite down E4M3FN scale"};
+  static const char* const kWeight[3] = {"invalid gate weight global scale", "invalid up weight global scale",
+                                         "invalid down weight global scale"};
+  static const char* const kInput[3] = {"invalid gate input global scale", "invalid up input global scale",
+                                        "invalid down input global scale"};
+  for (int m = 0; m < 3; ++m) {
+    const uint8_t* scales = raw + sidecars[m];
+    for (uint64_t i = 0; i < local; ++i)
+      if ((scales[i] & 0x7fU) == 0x7fU) return bad(kNonFinite[m]);
+    const float weight = positive_scalar(scales + local, false), input = positive_scalar(scales + local + 4U, false);
+    if (!std::isfinite(weight) || !(weight > 0.0F)) return bad(kWeight[m]);
+    if (!std::isfinite(input) || !(input > 0.0F)) return bad(kInput[m]);
+  }
+  if (e.decoded_bytes != 3U * elements * 4U) return bad("expert decoded byte mismatch");
+  if (verify_payload) {
+    uint8_t digest[32];
+    qllm_sha256(raw + kHeaderBytes, h.record_bytes - kHeaderBytes, digest);
+    if (std::memcmp(digest, h.payload_hash, 32) != 0) return bad("expert payload/header checksum mismatch");
+    if (std::memcmp(digest, e.payload_sha256, 32) != 0) return bad("expert payload/manifest checksum mismatch");
+  }
+  return QLLM_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int qllm_pack_check_expert(const void* pack, size_t pack_bytes, const qllm_pack_expert_entry* entry,
+                           int verify_payload) {
+  if (!pack || !entry) return bad("null pack or entry");
+  ExpertHeader h{};
+  return check_expert(static_cast<const uint8_t*>(pack), pack_bytes, *entry, verify_payload != 0, h);
+}
+
+int qllm_pack_nvfp4_expert(const void* pack, size_t pack_bytes, const qllm_pack_expert_entry* entry, int verify_payload,
+                           qllm_matrix* gate, qllm_matrix* up, qllm_matrix* down) {
+  if (!pack || !entry || !gate || !up || !down) return bad("null pack, entry or matrix");
+  ExpertHeader h{};
+  const int rc = check_expert(static_cast<const uint8_t*>(pack), pack_bytes, *entry, verify_payload != 0, h);
+  if (rc) return rc;
+  const uint8_t* record = static_cast<const uint8_t*>(pack) + entry->offset;
+  const uint64_t elements = static_cast<uint64_t>(h.hidden) * h.intermediate, local = elements / 16U;
+  const auto fill = [&](qllm_matrix* m, const uint8_t* codes, const uint8_t* sidecar, uint32_t rows, uint32_t cols) {
+    m->codes = codes;
+    m->scales = sidecar;
+    m->weight_scale = 1.0F / positive_scalar(sidecar + local, false);
+    m->input_scale = positive_scalar(sidecar + local + 4U, false);
+    m->rows = rows;
+    m->cols = cols;
+  };
+  fill(gate, record + h.offset[0], record + h.offset[1], h.intermediate, h.hidden);
+  fill(up, record + h.offset[0] + elements / 2U, record + h.offset[1] + local + 8U, h.intermediate, h.hidden);
+  fill(down, record + h.offset[2], record + h.offset[3], h.hidden, h.intermediate);
+  return QLLM_OK;
+}
 
 void qllm_sha256(const void* bytes, size_t count, uint8_t digest[32]) {
   Sha256 s;

@@ -27,6 +27,12 @@ class PackEntry(C.Structure):
                 ("payload_sha256", C.c_uint8 * 32)]
 
 
+class PackExpertEntry(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("expert", C.c_int32), ("offset", C.c_uint64), ("stored_bytes", C.c_uint64),
+                ("section_offset", C.c_uint64 * 4), ("section_bytes", C.c_uint64 * 4), ("decoded_bytes", C.c_uint64),
+                ("payload_sha256", C.c_uint8 * 32)]
+
+
 PACK_DTYPES = {"F32": 0, "BF16": 1, "I64": 2, "FP4_E2M1": 3}
 
 
@@ -90,6 +96,8 @@ SIGNATURES = {
     "qllm_provider_set_attention_impl": (ci, [vp, ci]),
     "qllm_pack_check_dense": (ci, [vp, sz, vp, ci]),
     "qllm_pack_nvfp4_matrix": (ci, [vp, sz, vp, ci, vp]),
+    "qllm_pack_check_expert": (ci, [vp, sz, vp, ci]),
+    "qllm_pack_nvfp4_expert": (ci, [vp, sz, vp, ci, vp, vp, vp]),
     "qllm_sha256": (None, [vp, sz, vp]),
     "qllm_descriptor_parse": (ci, [C.c_char_p, sz, P(vp)]),
     "qllm_descriptor_destroy": (None, [vp]),

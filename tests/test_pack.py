@@ -137,3 +137,103 @@ def test_matrix_read_from_the_pack_runs_through_the_gemv(impl):
         assert np.array_equal(got, want)
     else:   # tensor-core path: FP32 accumulation order differs -> at most one BF16 step on single values
         assert np.max(np.abs(got - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
+
+
+# ------------------------------------------------------------------ routed-expert records
+EXPERT_META = json.load(open(os.path.join(GOLDEN, "expert_pack.json")))
+EXPERT_PACK = open(os.path.join(GOLDEN, "expert_pack.bin"), "rb").read()
+SECTIONS = ("gate_up_q", "gate_up_scales", "down_q", "down_scales")
+
+
+def expert_entry_of(e):
+    offsets = (C.c_uint64 * 4)(*[e["sections"][s]["offset"] for s in SECTIONS])
+    sizes = (C.c_uint64 * 4)(*[e["sections"][s]["bytes"] for s in SECTIONS])
+    digest = (C.c_uint8 * 32)(*bytes.fromhex(e["payload_sha256"]))
+    return ql.PackExpertEntry(e["layer"], e["expert"], e["offset"], e["stored_bytes"], offsets, sizes,
+                              e["decoded_bytes"], digest)
+
+
+def expert_matrices(pack, e, verify=1):
+    L = ql.load()
+    buffer = C.create_string_buffer(pack, len(pack))
+    entry = expert_entry_of(e)
+    gate, up, down = ql.Matrix(), ql.Matrix(), ql.Matrix()
+    rc = L.qllm_pack_nvfp4_expert(buffer, len(pack), C.byref(entry), verify, C.byref(gate), C.byref(up), C.byref(down))
+    return rc, buffer, {"gate": gate, "up": up, "down": down}
+
+
+def test_expert_records_of_the_reference_writer_are_accepted_and_decoded():
+    assert hashlib.sha256(EXPERT_PACK).hexdigest() == EXPERT_META["pack_sha256"]
+    for e in EXPERT_META["records"]:
+        rc, buffer, matrices = expert_matrices(EXPERT_PACK, e)
+        assert rc == 0, ql.load().qllm_last_error()
+        base = C.addressof(buffer)
+        for role, m in matrices.items():
+            g = e["golden"][role]
+            rows, cols = g["shape"]
+            assert (m.rows, m.cols) == (rows, cols)
+            codes, scales = m.codes - base, m.scales - base
+            assert hashlib.sha256(EXPERT_PACK[codes:codes + rows * cols // 2]).hexdigest() == g["codes_sha256"]
+            assert hashlib.sha256(EXPERT_PACK[scales:scales + rows * cols // 16]).hexdigest() == g["scale_sha256"]
+            assert np.float32(m.weight_scale) == np.float32(1.0) / np.float32(g["weight_divisor"])
+            assert m.input_scale == g["input_divisor"]
+
+
+@pytest.mark.parametrize("case", EXPERT_META["corruptions"], ids=lambda c: c["name"].replace(" ", "_"))
+def test_expert_corruptions_get_the_reference_validator_s_verdict(case):
+    L = ql.load()
+    data = bytearray(EXPERT_PACK)
+    base = EXPERT_META["records"][case["record"]]["offset"]
+    for offset, raw in case["patches"]:
+        raw = bytes.fromhex(raw)
+        data[base + offset:base + offset + len(raw)] = raw
+    e = json.loads(json.dumps(EXPERT_META["records"][case["record"]]))
+    for key, value in case["overrides"].items():
+        node, parts = e, key.split(".")
+        for part in parts[:-1]:
+            node = node[part]
+        node[parts[-1]] = value
+    buffer = C.create_string_buffer(bytes(data), len(data))
+    entry = expert_entry_of(e)
+    rc = L.qllm_pack_check_expert(buffer, len(data), C.byref(entry), 1)
+    message = L.qllm_last_error().decode()
+    assert (rc == 0) == case["accepted"], (case["name"], message, case["message"])
+    if rc != 0:
+        assert rc == -4
+        if not case["name"].startswith(("abi 1", "abi 3", "abi 4")):     # other providers' encodings: refused as such
+            assert case["message"].startswith(message), (case["name"], message, case["message"])
+
+
+def test_expert_payload_check_is_optional():
+    bad = bytearray(EXPERT_PACK)
+    bad[300] ^= 0xFF
+    e = EXPERT_META["records"][0]
+    assert expert_matrices(bytes(bad), e, verify=1)[0] == -4
+    assert expert_matrices(bytes(bad), e, verify=0)[0] == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("role", ["gate", "up", "down"])
+def test_expert_matrices_read_from_the_pack_run_through_the_gemv(role):
+    # each projection of a record goes to the device as it lies in the pack; the CUDA-core GEMV
+    # over it equals the oracle's GEMV over the same bytes
+    import torch
+    from oracle import binding as ob
+    L = ql.load()
+    rc, buffer, matrices = expert_matrices(EXPERT_PACK, EXPERT_META["records"][1])
+    assert rc == 0
+    m, base = matrices[role], C.addressof(buffer)
+    rows, cols = m.rows, m.cols
+    codes = np.frombuffer(EXPERT_PACK, np.uint8, rows * cols // 2, m.codes - base).reshape(rows, cols // 2).copy()
+    scales = np.frombuffer(EXPERT_PACK, np.uint8, rows * cols // 16, m.scales - base).reshape(rows, cols // 16).copy()
+    x = np.random.default_rng(5).normal(0, 1, (5, cols)).astype(np.float32)
+    want = ob.gemv(ob.matrix(codes, scales, m.weight_scale, m.input_scale), x)
+    dc, ds, dx = (torch.from_numpy(a).cuda() for a in (codes, scales, x))
+    y = torch.empty((5, rows), dtype=torch.float32, device="cuda")
+    ws_bytes = L.qllm_k_nvfp4_gemv_workspace_bytes(5, rows, cols)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    cm = ql.Matrix(dc.data_ptr(), ds.data_ptr(), m.weight_scale, m.input_scale, rows, cols)
+    rc = L.qllm_k_nvfp4_gemv(C.byref(cm), 0, rows, dx.data_ptr(), y.data_ptr(), 5, ws.data_ptr(), ws_bytes, 0, None)
+    assert rc == 0, L.qllm_last_error().decode()
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), want)
