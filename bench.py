@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--microbench", action="store_true",
                     help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 160, 640")
+    ap.add_argument("--prefill-bench", type=int, default=0, metavar="TOKENS",
+                    help="time the prompt path (8-row target chunks + draft priming) over TOKENS prompt tokens")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
     args = ap.parse_args()
@@ -569,9 +571,46 @@ def microbench(args):
         torch.cuda.empty_cache()
 
 
+def prefill_bench(args):
+    """Prompt path on one GPU: target chunks of 8 rows (the reference's microbatch limit), each
+    followed by its draft-priming batch, from an empty cache; host tokens in, first token out.
+    Every chunk streams the whole model once, so the rate is about 8 tokens per weight pass."""
+    import numpy as np
+    import torch
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
+    from quantum_llm_b200 import build as qbuild
+    qbuild.build()
+    from quantum_llm_b200.provider import RequestParameters
+    from quantum_llm_b200.synthetic import DENSE_27B, MOE_35B, DeviceModel
+    cfg = dict(MOE_35B if args.model == "moe35b" else DENSE_27B)
+    if args.small:
+        cfg["layers"] = 4
+    tokens = args.prefill_bench
+    cfg["max_context"] = tokens + 1024
+    model = DeviceModel(cfg, seed=0, device="cuda:0")
+    provider = model.provider()
+    provider.set_gemv_impl(args.gemv_impl)
+    request = RequestParameters(sampling_seed=1, sampling_temperature_ppm=0, reserved_context_tokens=cfg["max_context"])
+    prompt = np.random.default_rng(1).integers(0, cfg["vocab"], tokens, dtype=np.uint32)
+    times = []
+    for trial in range(3):          # the first pass warms the code paths up
+        state = provider.create_request_state()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first = provider.prefill(state, request, prompt, first_position=0, chunk_rows=8)   # synchronous per chunk
+        times.append(time.perf_counter() - t0)
+        state.close()
+    best = min(times[1:])
+    print(json.dumps({"prefill_bench": args.model, "prompt_tokens": tokens, "chunk_rows": 8,
+                      "time_to_first_token_ms": round(best * 1e3, 2), "prompt_tokens_per_s": round(tokens / best, 1),
+                      "first_token": int(first), "layers": cfg["layers"]}))
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.microbench:
+    if a.prefill_bench:
+        prefill_bench(a)
+    elif a.microbench:
         microbench(a)
     elif a.impl == "reference":
         reference_arm(a)
