@@ -64,7 +64,8 @@ def parse():
     ap.add_argument("--microbench", action="store_true",
                     help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 160, 640")
     ap.add_argument("--prefill-bench", type=int, default=0, metavar="TOKENS",
-                    help="time the prompt path (8-row target chunks + draft priming) over TOKENS prompt tokens")
+                    help="time the prompt path (target chunks + draft priming) over TOKENS prompt tokens")
+    ap.add_argument("--chunk-rows", type=int, default=40, help="rows per prompt chunk of --prefill-bench (1..40)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
     args = ap.parse_args()
@@ -572,9 +573,9 @@ def microbench(args):
 
 
 def prefill_bench(args):
-    """Prompt path on one GPU: target chunks of 8 rows (the reference's microbatch limit), each
-    followed by its draft-priming batch, from an empty cache; host tokens in, first token out.
-    Every chunk streams the whole model once, so the rate is about 8 tokens per weight pass."""
+    """Prompt path on one GPU: target chunks of --chunk-rows rows (8 is the reference's microbatch
+    limit, 40 the widest chunk here), each followed by its draft-priming batch, from an empty
+    cache; host tokens in, first token out.  Every chunk streams the whole model once."""
     import numpy as np
     import torch
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
@@ -597,11 +598,11 @@ def prefill_bench(args):
         state = provider.create_request_state()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        first = provider.prefill(state, request, prompt, first_position=0, chunk_rows=8)   # synchronous per chunk
+        first = provider.prefill(state, request, prompt, first_position=0, chunk_rows=args.chunk_rows)   # synchronous per chunk
         times.append(time.perf_counter() - t0)
         state.close()
     best = min(times[1:])
-    print(json.dumps({"prefill_bench": args.model, "prompt_tokens": tokens, "chunk_rows": 8,
+    print(json.dumps({"prefill_bench": args.model, "prompt_tokens": tokens, "chunk_rows": args.chunk_rows,
                       "time_to_first_token_ms": round(best * 1e3, 2), "prompt_tokens_per_s": round(tokens / best, 1),
                       "first_token": int(first), "layers": cfg["layers"]}))
 

@@ -143,7 +143,8 @@ void qllm_provider_destroy_request_state(qllm_provider* provider, qllm_request_s
 /* One prefill chunk of the target program (execute_program_sequence,
  * dense_fp4_provider.cpp:8854-9200 as driven by moe_vm_runner.cpp:679-778): stores
  * target KV for positions first_position.. and retains the hidden rows for the
- * following synchronisation batch. tokens: host. */
+ * following synchronisation batch. tokens: host. count <= qllm_provider_max_chunk_rows;
+ * the results do not depend on how a prompt is cut into chunks. */
 int qllm_provider_prefill_chunk(qllm_provider* provider, qllm_request_state* state,
                                 const uint32_t* tokens, uint32_t count, uint32_t first_position);
 /* Token selected by the head for the last retained row (run_head sampling
@@ -178,6 +179,13 @@ int qllm_provider_telemetry(qllm_provider* provider, qllm_request_state* state, 
                             uint32_t count);
 /* The cudaStream_t every call of this provider launches on (for event timing). */
 void* qllm_provider_stream(qllm_provider* provider);
+/* Most rows qllm_provider_prefill_chunk / _synchronize_exact_decode_batch take at once. The
+ * reference's microbatch paths stop at kMaximumWorkspaceRows = 8 (dense_fp4_provider.cpp:8854-9200)
+ * and its wider prompt batches go through fp4_gemm_block32_kernel; here a chunk of up to 40 rows
+ * is one operand of the block-scaled tensor-core kernel (one pass over the weights per chunk),
+ * attention takes it in tiles of 8 rows and only its last row reaches the head. A tensor-parallel
+ * provider stays at 8 (the size of its exchange slots). */
+uint32_t qllm_provider_max_chunk_rows(const qllm_provider* provider);
 /* 0 = launch kernels one by one, 1 = replay the captured CUDA graph of the step. */
 int qllm_provider_set_graph_mode(qllm_provider* provider, int enabled);
 /* GEMV implementation: 0 = CUDA-core kernel, 1 = tcgen05 block-scaled MMA kernel. */

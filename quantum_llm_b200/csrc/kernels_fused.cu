@@ -243,7 +243,7 @@ combine_quant_kernel(CombineArgs c) {
                       actv(static_cast<float>(r[2]) / gsum, c.bf16), actv(static_cast<float>(r[3]) / gsum, c.bf16));
     if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(row) * c.q_heads + head) * hd)[f] = out;
   }
-  if (c.sink.kind >= 0) quant_store_quad(c.sink, row, (head * hd + 4U * f) / 16U, out, valid);
+  if (c.sink.kind >= 0) quant_store_quad(c.sink, row + c.sink_row_offset, (head * hd + 4U * f) / 16U, out, valid);
 }
 
 int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t stream) {

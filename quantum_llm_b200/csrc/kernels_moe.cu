@@ -577,19 +577,22 @@ namespace {
 inline size_t round4(size_t n) { return (n + 3U) & ~static_cast<size_t>(3U); }  // 16-byte granules of floats
 }  // namespace
 
+// one arrival counter of the router kernel per row: the widest pass holds fewer rows than this
+constexpr uint32_t kRouterTickets = 64;
+
 size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn) {
   const size_t selections = static_cast<size_t>(rows) * route_width;
   // router tickets (fixed place) | router logits | indices | scores | quantised mid (INT8 values,
   // then FP32 block scales) | moe
-  return 8U + static_cast<size_t>(rows) * 256U + round4(2U * selections) + round4(selections * (expert_ffn / 4U)) +
+  return kRouterTickets + static_cast<size_t>(rows) * 256U + round4(2U * selections) + round4(selections * (expert_ffn / 4U)) +
          round4(selections * (expert_ffn / 16U)) + static_cast<size_t>(rows) * hidden;
 }
 
 void moe_carve_workspace(float* base, MoeArgs& a) {
   const size_t selections = static_cast<size_t>(a.rows) * a.route_width;
   a.router_tickets = reinterpret_cast<uint32_t*>(base);  // zero between launches, whatever the row count
-  a.router_logits = base + 8U;
-  base += 8U + static_cast<size_t>(a.rows) * 256U;
+  a.router_logits = base + kRouterTickets;
+  base += kRouterTickets + static_cast<size_t>(a.rows) * 256U;
   a.indices = reinterpret_cast<uint32_t*>(base);
   a.scores = base + selections;
   float* mid = base + round4(2U * selections);
@@ -607,6 +610,7 @@ int launch_moe_router_select(const GemvOut& logits, const MoeArgs& a, cudaStream
 }
 
 int launch_moe_router(const ExpertMatrix& router, const QuantSink& operand, const MoeArgs& a, cudaStream_t stream) {
+  if (a.rows > kRouterTickets) return fail(QLLM_INVALID_ARGUMENT, "router pass is wider than its arrival counters");
   if (!a.rows || !a.route_width || a.route_width > 8U || a.route_width > a.experts || a.experts > 256U)
     return fail(QLLM_INVALID_ARGUMENT, "router needs 1..8 selections out of at most 256 experts");
   if (operand.kind != 0 || operand.cols != a.hidden || a.hidden % 16U)

@@ -103,7 +103,8 @@ struct qllm_request_state {
   StepState* state = nullptr;       // device
   StepRecord* results = nullptr;    // device ring
   StepRecord* host_records = nullptr;  // pinned landing area of the ring
-  float* retained_hidden = nullptr; // [kMaxRows, hidden] rows of the last prefill chunk
+  float* retained_hidden = nullptr; // [kChunkRows, hidden] rows of the last prefill chunk
+  uint32_t retained_logits_row = 0; // row of the logits buffer that holds the chunk's last position
   float* mtp_last_hidden = nullptr; // [hidden]
   // host mirror of the invocation stream invariants
   uint32_t mtp_length = 0;
@@ -122,6 +123,10 @@ struct qllm_request_state {
 
 struct qllm_provider {
   static constexpr uint32_t kMaxRows = 8;      // kMaximumWorkspaceRows of the microbatch paths
+  // widest prompt chunk: the projections see it as one operand (one pass over the weights),
+  // attention takes it in tiles of kMaxRows rows, and only its last row goes through the head
+  static constexpr uint32_t kChunkRows = 40;
+  uint32_t chunk_limit() const { return tp_ranks ? kMaxRows : kChunkRows; }  // exchange slots hold kMaxRows rows
   static constexpr uint32_t kResultRing = 64;
   qllm_config cfg{};
   int device = 0;
@@ -269,14 +274,14 @@ struct qllm_provider {
     off += kv_layer_bytes(c.mtp_kv_encoding, c.page_tokens, c.kv_heads, c.head_dim);
     page_bytes = (off + 255U) & ~static_cast<size_t>(255U);
 
-    const uint32_t R = kMaxRows;
+    const uint32_t R = kChunkRows, H = kMaxRows;  // rows of a pass; rows that reach the head and the sampler
     const uint32_t qkv_w = (c.q_heads + 2U * c.kv_heads) * c.head_dim;
     hidden.alloc(static_cast<size_t>(R) * c.hidden, "hidden");
     mtp_hidden.alloc(static_cast<size_t>(R) * c.hidden, "draft residual stream");
     qkv.alloc(static_cast<size_t>(R) * qkv_w, "rotated queries");
     q8.alloc(static_cast<size_t>(R) * c.q_heads * c.head_dim, "INT8 queries");
     q8_scale.alloc(static_cast<size_t>(R) * c.q_heads, "INT8 query scales");
-    logits.alloc(static_cast<size_t>(R) * c.vocab, "logits");
+    logits.alloc(static_cast<size_t>(H) * c.vocab, "logits");
     const uint32_t widest = std::max(std::max(2U * c.hidden, c.ffn), c.q_heads * c.head_dim);
     quant_buf.alloc(quant_buffer_bytes(R, widest), "quantised GEMV operand");
     size_t partial_floats = 0;
@@ -285,7 +290,7 @@ struct qllm_provider {
                                    {c.experts ? c.experts : 16U, c.hidden}};
     uint32_t most_outputs = 0;
     for (const auto& s : shapes) {
-      partial_floats = std::max(partial_floats, gemv_partial_floats(R, s[0], s[1]));
+      partial_floats = std::max(partial_floats, gemv_partial_floats(s[0] == c.vocab ? H : R, s[0], s[1]));
       most_outputs = std::max(most_outputs, s[0] == c.vocab ? 0U : s[0]);
     }
     partial_buf.alloc(partial_floats, "split-K partial sums");
@@ -304,11 +309,11 @@ struct qllm_provider {
     draft_logits.alloc(c.draft_vocab, "draft logits");
     // the page pool keeps a few slots of slack past max_context for speculative rows
     max_splits = (c.max_context + 2U * kMaxRows + c.split_tokens - 1U) / c.split_tokens;
-    attn_ws.alloc(attention_workspace_bytes(R, c.q_heads, c.head_dim, max_splits), "attention partials");
-    topk_ws.alloc(topk_workspace_bytes(R, c.vocab, 64), "top-k partials");
-    argmax_out.alloc(R, "argmax");
-    top_tokens.alloc(static_cast<size_t>(R) * 64U, "top-k tokens");
-    top_values.alloc(static_cast<size_t>(R) * 64U, "top-k values");
+    attn_ws.alloc(attention_workspace_bytes(H, c.q_heads, c.head_dim, max_splits), "attention partials");
+    topk_ws.alloc(topk_workspace_bytes(H, c.vocab, 64), "top-k partials");
+    argmax_out.alloc(H, "argmax");
+    top_tokens.alloc(static_cast<size_t>(H) * 64U, "top-k tokens");
+    top_values.alloc(static_cast<size_t>(H) * 64U, "top-k values");
     tokens_dev.alloc(R, "token upload");
     first_token_dev.alloc(1, "first token");
     cu(cudaStreamSynchronize(stream), "provider set-up");
@@ -438,53 +443,60 @@ struct qllm_provider {
     rs.base = RopeStoreArgs{nullptr, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
                             first_position, position_offset, rotary_offset, st.page_table, layer_offset,
                             c.page_tokens, enc, bf};
+    // a chunk wider than kMaxRows rows goes through attention in row tiles: every row sees the
+    // cache up to its own position, and the records of the whole chunk are stored before the first tile
+    const uint32_t tile_rows = std::min(rows, kMaxRows);
     const bool tensor_attention = attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
-                                  rows * (c.q_heads / c.kv_heads) <= 64U;
+                                  tile_rows * (c.q_heads / c.kv_heads) <= 64U;
     rs.q8_out = tensor_attention ? q8.p : nullptr;
     rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
     ok(launch_rope_kv_store_fused(rs, stream));
     const uint32_t qkv_w = c.q_heads * c.head_dim;  // rotated queries only
-    AttentionArgs at{};
-    at.encoding = enc;
-    at.page_table = st.page_table;
-    at.layer_offset = layer_offset;
-    at.page_tokens = c.page_tokens;
-    at.query = qkv.p;
-    at.query_row_stride = qkv_w;
-    at.rows = rows;
-    at.first_position = first_position;
-    at.position_offset = position_offset;
-    at.q_heads = c.q_heads;
-    at.kv_heads = c.kv_heads;
-    at.head_dim = c.head_dim;
-    at.split_tokens = c.split_tokens;
-    at.max_splits = splits;
-    at.bf16 = bf;
-    at.workspace = attn_ws.p;
-    at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
-    at.impl = tensor_attention ? 1 : 0;
-    if (attention_impl == 1 && enc == QLLM_KV_Q8 && attention_q8_mma_supported(at)) at.impl = 1;
-    if (attention_impl == 1 && enc == QLLM_KV_F16 && attention_f16_mma_supported(at)) at.impl = 1;
-    at.query_q8 = rs.q8_out;
-    at.query_q8_scale = rs.q8_scale;
-    at.error = kernel_error.p;
-    at.skip_combine = true;
-    ok(launch_attention(at, stream));
-    CombineArgs cb{};
-    const size_t items = static_cast<size_t>(rows) * splits * c.q_heads;
-    cb.maxima = reinterpret_cast<const float*>(attn_ws.p);
-    cb.sums = cb.maxima + items;
-    cb.outputs = cb.maxima + 2U * items;
-    cb.first_position = first_position;
-    cb.position_offset = position_offset;
-    cb.q_heads = c.q_heads;
-    cb.head_dim = c.head_dim;
-    cb.split_tokens = c.split_tokens;
-    cb.max_splits = splits;
-    cb.bf16 = bf;
-    cb.out = nullptr;
-    cb.sink = sink_for(b.o, rows);
-    ok(launch_combine_quant(cb, rows, stream));
+    for (uint32_t r0 = 0; r0 < rows; r0 += tile_rows) {
+      const uint32_t n = std::min(tile_rows, rows - r0);
+      AttentionArgs at{};
+      at.encoding = enc;
+      at.page_table = st.page_table;
+      at.layer_offset = layer_offset;
+      at.page_tokens = c.page_tokens;
+      at.query = qkv.p + static_cast<size_t>(r0) * qkv_w;
+      at.query_row_stride = qkv_w;
+      at.rows = n;
+      at.first_position = first_position;
+      at.position_offset = position_offset + r0;
+      at.q_heads = c.q_heads;
+      at.kv_heads = c.kv_heads;
+      at.head_dim = c.head_dim;
+      at.split_tokens = c.split_tokens;
+      at.max_splits = splits;
+      at.bf16 = bf;
+      at.workspace = attn_ws.p;
+      at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
+      at.impl = tensor_attention ? 1 : 0;
+      if (attention_impl == 1 && enc == QLLM_KV_Q8 && attention_q8_mma_supported(at)) at.impl = 1;
+      if (attention_impl == 1 && enc == QLLM_KV_F16 && attention_f16_mma_supported(at)) at.impl = 1;
+      at.query_q8 = rs.q8_out ? rs.q8_out + static_cast<size_t>(r0) * qkv_w : nullptr;
+      at.query_q8_scale = rs.q8_scale ? rs.q8_scale + static_cast<size_t>(r0) * c.q_heads : nullptr;
+      at.error = kernel_error.p;
+      at.skip_combine = true;
+      ok(launch_attention(at, stream));
+      CombineArgs cb{};
+      const size_t items = static_cast<size_t>(n) * splits * c.q_heads;
+      cb.maxima = reinterpret_cast<const float*>(attn_ws.p);
+      cb.sums = cb.maxima + items;
+      cb.outputs = cb.maxima + 2U * items;
+      cb.first_position = first_position;
+      cb.position_offset = position_offset + r0;
+      cb.q_heads = c.q_heads;
+      cb.head_dim = c.head_dim;
+      cb.split_tokens = c.split_tokens;
+      cb.max_splits = splits;
+      cb.bf16 = bf;
+      cb.out = nullptr;
+      cb.sink = sink_for(b.o, rows);
+      cb.sink_row_offset = r0;
+      ok(launch_combine_quant(cb, n, stream));
+    }
     const GemvOut o_out = gemv(b.o, rows, 0U, nullptr, 0);
     if (c.experts) {
       routed_experts(b, h, o_out, rows, pending);
@@ -511,6 +523,15 @@ struct qllm_provider {
             0U, 0U, splits);
     last_rows = rows;
     // last residual add (+ final norm and the head's operand)
+    if (with_head && rows > kMaxRows) {
+      // a wide prompt chunk: residual add of every row, then the norm and the head of the last
+      // row alone (the only logits the caller can ask for); they land in row 0 of the buffer
+      norm_quant(hidden.p, c.hidden, &pending, hidden.p, nullptr, nullptr, rows);
+      norm_quant(hidden.p + static_cast<size_t>(rows - 1U) * c.hidden, c.hidden, nullptr, nullptr, final_norm, &head, 1U);
+      const GemvOut lg = gemv(head, 1U, 0U, logits.p);
+      ok(launch_gemv_finalize(lg, logits.p, stream));
+      return;
+    }
     norm_quant(hidden.p, c.hidden, &pending, hidden.p, with_head ? final_norm : nullptr, with_head ? &head : nullptr,
                rows);
     if (with_head) {
@@ -686,7 +707,7 @@ int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** ou
     cu(cudaMalloc(&st->results, qllm_provider::kResultRing * sizeof(StepRecord)), "result ring");
     cu(cudaMemsetAsync(st->results, 0, qllm_provider::kResultRing * sizeof(StepRecord), p->stream), "result ring");
     cu(cudaMallocHost(&st->host_records, qllm_provider::kResultRing * sizeof(StepRecord)), "pinned result ring");
-    cu(cudaMalloc(&st->retained_hidden, static_cast<size_t>(qllm_provider::kMaxRows) * c.hidden * sizeof(float)), "retained hidden");
+    cu(cudaMalloc(&st->retained_hidden, static_cast<size_t>(qllm_provider::kChunkRows) * c.hidden * sizeof(float)), "retained hidden");
     cu(cudaMalloc(&st->mtp_last_hidden, c.hidden * sizeof(float)), "draft hidden");
     cu(cudaStreamSynchronize(p->stream), "request state set-up");
   });
@@ -719,7 +740,7 @@ int qllm_provider_prefill_chunk(qllm_provider* p, qllm_request_state* st, const 
     std::lock_guard<std::mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
-    if (!count || count > qllm_provider::kMaxRows || first_position + count > c.max_context)
+    if (!count || count > p->chunk_limit() || first_position + count > c.max_context)
       throw Error(QLLM_INVALID_ARGUMENT, "invalid target-model microbatch");
     for (uint32_t r = 0; r < count; ++r)
       if (tokens[r] >= c.vocab) throw Error(QLLM_INVALID_ARGUMENT, "target token exceeds vocabulary");
@@ -731,6 +752,7 @@ int qllm_provider_prefill_chunk(qllm_provider* p, qllm_request_state* st, const 
     cu(cudaStreamSynchronize(p->stream), "prefill chunk");
     st->retained_rows = count;
     st->retained_first = first_position;
+    st->retained_logits_row = count > qllm_provider::kMaxRows ? 0U : count - 1U;
   });
 }
 
@@ -744,7 +766,7 @@ int qllm_provider_first_token(qllm_provider* p, qllm_request_state* st, const ql
     if (!st->retained_rows) throw Error(QLLM_INVALID_ARGUMENT, "no prefill rows retained");
     p->bind_request(*st, *rq);
     const bool sampled = rq->sampling_temperature_ppm != 0U;
-    const float* row = p->logits.p + static_cast<size_t>(st->retained_rows - 1U) * c.vocab;
+    const float* row = p->logits.p + static_cast<size_t>(st->retained_logits_row) * c.vocab;
     p->select_candidates(row, 1, c.vocab, c.vocab, sampled, rq->sampling_top_k);
     ok(launch_first_token(st->state, p->argmax_out.p, p->top_values.p, p->top_tokens.p, sample_position,
                           p->first_token_dev.p, p->stream));
@@ -762,7 +784,7 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
     std::lock_guard<std::mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
-    if (!count || count > qllm_provider::kMaxRows || count != st->retained_rows ||
+    if (!count || count > p->chunk_limit() || count != st->retained_rows ||
         first_target_position != st->retained_first || st->mtp_length != first_target_position ||
         first_target_position + count + 1U > c.max_context)
       throw Error(QLLM_INVALID_ARGUMENT, "MTP synchronization stream is invalid");
@@ -928,6 +950,7 @@ int qllm_provider_telemetry(qllm_provider* p, qllm_request_state* st, uint64_t* 
 }
 
 void* qllm_provider_stream(qllm_provider* p) { return p ? static_cast<void*>(p->stream) : nullptr; }
+uint32_t qllm_provider_max_chunk_rows(const qllm_provider* p) { return p ? p->chunk_limit() : 0U; }
 
 int qllm_provider_set_graph_mode(qllm_provider* p, int enabled) {
   if (!p) return fail(QLLM_INVALID_ARGUMENT, "null provider");

@@ -91,6 +91,7 @@ SIGNATURES = {
     "qllm_provider_execute_exact_decode_steps": (ci, [vp, vp, P(Request), u32, u32, P(ExactResult)]),
     "qllm_provider_telemetry": (ci, [vp, vp, P(u64), u32]),
     "qllm_provider_stream": (vp, [vp]),
+    "qllm_provider_max_chunk_rows": (u32, [vp]),
     "qllm_provider_set_graph_mode": (ci, [vp, ci]),
     "qllm_provider_set_gemv_impl": (ci, [vp, ci]),
     "qllm_provider_set_attention_impl": (ci, [vp, ci]),

@@ -155,6 +155,10 @@ class Nvfp4MtpProvider:
         """The provider's cudaStream_t as an integer handle."""
         return int(self.L.qllm_provider_stream(self.h) or 0)
 
+    def max_chunk_rows(self):
+        """Most rows one prefill chunk / synchronisation batch may hold."""
+        return int(self.L.qllm_provider_max_chunk_rows(self.h))
+
     def set_graph_mode(self, enabled):
         _l.check(self.L.qllm_provider_set_graph_mode(self.h, int(enabled)))
 

@@ -1,0 +1,93 @@
+"""Prompt chunks wider than the reference's 8-row microbatch: one operand of the projections,
+attention in row tiles, head on the last row.  On the exact path (CUDA-core GEMV, scalar
+attention) the result must not depend on how the prompt is cut: same cache pages, same first
+token, same drafts, same continuation as with 5-row chunks and as the oracle."""
+import numpy as np
+import pytest
+
+from oracle import binding as ob
+from tests import synth
+from tests.gpu_util import provider_from_synth, request_pair
+
+pytestmark = pytest.mark.gpu
+
+MOE = dict(synth.TINY, experts=8, route_width=2, expert_ffn=128, route_scale=1.0)
+
+
+def decode(p, st, prq, first, position, count):
+    out, tok = [first], first
+    while len(out) < count + 1:
+        r = p.execute_exact_decode(st, prq, tok, position, prq.reserved_context_tokens)
+        out += r.emitted_tokens[1:] + [r.next_token]
+        position += r.positions_advanced
+        tok = r.next_token
+    return out[:count + 1]
+
+
+def run(model, prompt, chunk_rows, gemv_impl, attention_impl, temperature=0):
+    prq, _ = request_pair(seed=99, temperature_ppm=temperature, context_limit=model.cfg["max_context"])
+    p = provider_from_synth(model)
+    p.set_gemv_impl(gemv_impl)
+    p.set_attention_impl(attention_impl)
+    st = p.create_request_state()
+    first = p.prefill(st, prq, prompt, chunk_rows=chunk_rows)
+    drafts = [int(t) for t in p.read_drafts(st)]
+    return dict(first=first, drafts=drafts, stream=decode(p, st, prq, first, len(prompt), 24), provider=p, state=st)
+
+
+@pytest.mark.parametrize("cfg", [synth.TINY, MOE], ids=["dense", "routed"])
+@pytest.mark.parametrize("chunk_rows", [8, 13, 40])
+def test_exact_path_does_not_depend_on_the_chunk_width(cfg, chunk_rows):
+    model = synth.SynthModel(cfg, seed=3)
+    prompt = synth.prompt(4096, 97, 5)      # 97 = 2 x 40 + 17: a ragged last chunk at every width
+    narrow = run(model, prompt, 5, 0, 0)
+    wide = run(model, prompt, chunk_rows, 0, 0)
+    assert wide["first"] == narrow["first"] and wide["drafts"] == narrow["drafts"]
+    assert wide["stream"] == narrow["stream"]
+    # and the oracle, which only knows the narrow form
+    _, orq = request_pair(seed=99, temperature_ppm=0, context_limit=model.cfg["max_context"])
+    o = model.oracle_session()
+    assert o.prefill(prompt, 5, orq) == wide["first"]
+    assert [int(t) for t in o.drafts()] == wide["drafts"]
+
+
+def test_wide_chunks_write_the_same_cache_pages():
+    model = synth.SynthModel(synth.TINY, seed=4)
+    prompt = synth.prompt(4096, 80, 6)
+    a, b = run(model, prompt, 5, 0, 0), run(model, prompt, 40, 0, 0)
+    # the pool is cleared at creation and both runs issue the same writes: whole pages compare
+    pages = (80 + 24 + 16 + model.cfg["page_tokens"] - 1) // model.cfg["page_tokens"]
+    for page in range(pages):
+        assert np.array_equal(a["provider"].read_page(a["state"], page), b["provider"].read_page(b["state"], page))
+
+
+@pytest.mark.parametrize("kv_encoding", [ob.KV_Q4H, ob.KV_F16])
+def test_tensor_core_paths_take_wide_chunks(kv_encoding):
+    # head_dim 128 so that the tensor-core attention kernels run on the 8-row tiles
+    cfg = dict(synth.TINY, head_dim=128, rotary_dim=64, kv_encoding=kv_encoding)
+    model = synth.SynthModel(cfg, seed=5)
+    prompt = synth.prompt(4096, 90, 7)
+    exact = run(model, prompt, 5, 0, 0)
+    fast = run(model, prompt, 40, 1, 1)
+    # different accumulation order: the greedy stream may only part at a near-tie, after which
+    # the two runs see different inputs; the prompt's first token and most of the stream agree
+    same = 0
+    for x, y in zip(exact["stream"], fast["stream"]):
+        if x != y:
+            break
+        same += 1
+    assert same >= 8, (exact["stream"], fast["stream"])
+
+
+def test_chunk_limits():
+    from quantum_llm_b200 import QllmError
+    model = synth.SynthModel(synth.TINY, seed=0)
+    prq, _ = request_pair(context_limit=256)
+    p = provider_from_synth(model)
+    assert p.max_chunk_rows() == 40
+    st = p.create_request_state()
+    with pytest.raises(QllmError):
+        p.prefill_chunk(st, synth.prompt(4096, 41, 0), 0)
+    p.prefill_chunk(st, synth.prompt(4096, 40, 0), 0)
+    with pytest.raises(QllmError):          # the synchronisation batch must cover the retained chunk
+        p.synchronize_exact_decode_batch(st, prq, synth.prompt(4096, 8, 1), 0, True)
