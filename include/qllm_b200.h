@@ -144,7 +144,10 @@ void qllm_provider_destroy_request_state(qllm_provider* provider, qllm_request_s
  * dense_fp4_provider.cpp:8854-9200 as driven by moe_vm_runner.cpp:679-778): stores
  * target KV for positions first_position.. and retains the hidden rows for the
  * following synchronisation batch. tokens: host. count <= qllm_provider_max_chunk_rows;
- * the results do not depend on how a prompt is cut into chunks. */
+ * the results do not depend on how a prompt is cut into chunks. The chunk is enqueued on the
+ * provider's stream and the call returns (tokens are staged before it does), so that the host
+ * prepares the next chunk while this one runs; qllm_provider_first_token and the producing
+ * synchronisation batch wait for the stream and report any device-side error. */
 int qllm_provider_prefill_chunk(qllm_provider* provider, qllm_request_state* state,
                                 const uint32_t* tokens, uint32_t count, uint32_t first_position);
 /* Token selected by the head for the last retained row (run_head sampling

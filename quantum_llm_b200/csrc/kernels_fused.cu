@@ -154,7 +154,8 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
 // independent of the visiting order) and writes the o-projection operand.
 constexpr uint32_t kCombineSplits = 512;
 
-__global__ void __launch_bounds__(256)
+// two CTAs per SM (128 registers): rows x heads CTAs of a verify pass then fit one wave
+__global__ void __launch_bounds__(256, 2)
 combine_quant_kernel(CombineArgs c) {
   // CTA = (row, query head), 8 warps: warp w merges the splits s = w (mod 8); a lane owns
   // 4 (head_dim 128) or 8 (head_dim 256) output dims.

@@ -638,6 +638,8 @@ struct qllm_provider {
     st.request_bound = true;
   }
 
+  // Inspection calls read on the default stream, which does not order with this one.
+  void settle() { cu(cudaStreamSynchronize(stream), "wait for the provider's stream"); }
   template <typename T>
   void poke(T* device_field, const T& value) {
     cu(cudaMemcpyAsync(device_field, &value, sizeof(T), cudaMemcpyHostToDevice, stream), "state update");
@@ -722,6 +724,7 @@ int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** ou
 void qllm_provider_destroy_request_state(qllm_provider* p, qllm_request_state* st) {
   if (!st) return;
   if (p) cudaSetDevice(p->device);
+  if (p) cudaStreamSynchronize(p->stream);  // chunks may still be in flight
   if (st->step_graph) cudaGraphExecDestroy(st->step_graph);
   cudaFree(st->slab);
   cudaFree(st->page_table);
@@ -749,7 +752,8 @@ int qllm_provider_prefill_chunk(qllm_provider* p, qllm_request_state* st, const 
     p->run_target(*st, p->tokens_dev.p, count, &st->state->position, p->splits_for(first_position + count), true);
     cu(cudaMemcpyAsync(st->retained_hidden, p->hidden.p, static_cast<size_t>(count) * c.hidden * sizeof(float),
                        cudaMemcpyDeviceToDevice, p->stream), "retain target hidden rows");
-    cu(cudaStreamSynchronize(p->stream), "prefill chunk");
+    // no wait here: the next chunk is enqueued while this one runs; the call that returns a
+    // token or a draft (first_token, the producing synchronisation batch) waits and reports
     st->retained_rows = count;
     st->retained_first = first_position;
     st->retained_logits_row = count > qllm_provider::kMaxRows ? 0U : count - 1U;
@@ -820,8 +824,7 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
       st->draft_count = drafts;
       st->draft_valid = drafts != 0U;
     } else {
-      p->poke(&s->position, first_target_position + count);
-      cu(cudaStreamSynchronize(p->stream), "MTP synchronization");
+      p->poke(&s->position, first_target_position + count);  // stream-ordered, like the pass itself
     }
     st->mtp_length = first_target_position + count;
     st->retained_rows = 0;
@@ -940,6 +943,7 @@ int qllm_provider_telemetry(qllm_provider* p, qllm_request_state* st, uint64_t* 
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
     StepState host;
+    p->settle();
     cu(cudaMemcpy(&host, st->state, offsetof(StepState, drafts), cudaMemcpyDeviceToHost), "read counters");
     std::memset(out, 0, count * sizeof(uint64_t));
     out[0] = host.exact_calls;
@@ -1019,6 +1023,7 @@ int qllm_provider_read_logits(qllm_provider* p, float* out, uint32_t rows) {
   return guarded([&] {
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
+    p->settle();
     cu(cudaMemcpy(out, p->logits.p, static_cast<size_t>(rows) * p->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost), "read logits");
   });
 }
@@ -1028,6 +1033,7 @@ int qllm_provider_read_hidden(qllm_provider* p, qllm_request_state* st, int whic
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
     const float* src = which ? p->hidden.p : st->retained_hidden;
+    p->settle();
     cu(cudaMemcpy(out, src, static_cast<size_t>(rows) * p->cfg.hidden * sizeof(float), cudaMemcpyDeviceToHost), "read hidden");
   });
 }
@@ -1037,6 +1043,7 @@ int qllm_provider_read_drafts(qllm_provider* p, qllm_request_state* st, uint32_t
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
     StepState host;
+    p->settle();
     cu(cudaMemcpy(&host, st->state, offsetof(StepState, drafts), cudaMemcpyDeviceToHost), "read drafts");
     *count = host.draft_count;
     for (uint32_t i = 0; i < host.draft_count && i < 4U; ++i) tokens[i] = host.verify_tokens[i + 1U];
@@ -1051,6 +1058,7 @@ int qllm_provider_read_page(qllm_provider* p, qllm_request_state* st, uint32_t p
   return guarded([&] {
     cu(cudaSetDevice(p->device), "select device");
     cu(cudaStreamSynchronize(p->stream), "sync");
+    p->settle();
     cu(cudaMemcpy(out, st->slab + static_cast<size_t>(page) * p->page_bytes, p->page_bytes, cudaMemcpyDeviceToHost), "read page");
   });
 }
