@@ -77,7 +77,29 @@ struct AttentionArgs {
   // [rows, q_heads, head_dim] codes and [rows, q_heads] scales; null = quantise from `query`
   const int8_t* query_q8;
   const float* query_q8_scale;
+  // > 1: one launch over `tiles` consecutive row tiles of `rows` rows each (grid z): tile z holds
+  // rows z*rows.. of the pass (queries, positions) and its partials follow tile z-1's in the workspace
+  uint32_t tiles;
 };
+#ifdef __CUDACC__
+// Entry of every attention kernel: moves the arguments to the row tile of this block.
+template <typename P>
+__device__ __forceinline__ void attention_row_tile(AttentionArgs& a, P& part) {
+  const uint32_t z = blockIdx.z;
+  if (z == 0U) return;
+  const uint32_t r0 = z * a.rows;
+  const size_t shift = static_cast<size_t>(r0) * a.max_splits * a.q_heads * (2U + a.head_dim);
+  part.maxima += shift;
+  part.sums += shift;
+  part.outputs += shift;
+  a.query += static_cast<size_t>(r0) * a.query_row_stride;
+  if (a.query_q8) {
+    a.query_q8 += static_cast<size_t>(r0) * a.q_heads * a.head_dim;
+    a.query_q8_scale += static_cast<size_t>(r0) * a.q_heads;
+  }
+  a.position_offset += r0;
+}
+#endif
 int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
                                    uint32_t* error, cudaStream_t stream);
 // BF16 tensor-core kernel over the Q8 cache (head_dim 128, at most 8 kv heads).

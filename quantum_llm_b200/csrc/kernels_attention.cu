@@ -346,12 +346,13 @@ __device__ __forceinline__ void load_kv_tile(const AttentionArgs& a, uint32_t kv
   }
 }
 
-template <uint32_t ENC>
+template <uint32_t ENC, bool kTiled>
 __global__ void __launch_bounds__(256)
 attention_scalar_kernel(AttentionArgs a, Partials part) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
+  if constexpr (kTiled) attention_row_tile(a, part);
   const uint32_t hd = a.head_dim, group = a.q_heads / a.kv_heads;
   const uint32_t MR = a.rows * group;
   float* qs = smem;
@@ -545,7 +546,8 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
       a.split_tokens % 32U || !a.split_tokens || a.page_tokens % 32U || !a.max_splits || MR > 64U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported attention geometry");
   const Partials part = partials_of(a);
-  const dim3 grid(a.kv_heads, a.max_splits);
+  const dim3 grid(a.kv_heads, a.max_splits, a.tiles > 1U ? a.tiles : 1U);
+  if (a.tiles > 1U && !a.skip_combine) return fail(QLLM_INVALID_ARGUMENT, "row tiles are merged by the caller");
   if (a.impl == 1 && a.encoding == QLLM_KV_F16) {
     if (!attention_f16_mma_supported(a))
       return fail(QLLM_INVALID_ARGUMENT,
@@ -573,7 +575,9 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
     // raised (to the largest geometry the kernel accepts), because launches captured into a
     // graph earlier keep their own, possibly larger, shared-memory size.
     constexpr size_t kLargest = (64U * 256U + 32U * 257U + 2U * 64U * 33U + 5U * 64U + 64U) * sizeof(float);
-    static bool configured[64][3] = {};  // per device, per instantiation
+    static bool configured[64][3] = {};  // per device, per encoding (both forms of the kernel)
+    const bool tiled = a.tiles > 1U;
+    bool both = true;
     int device = 0;
     cudaGetDevice(&device);
     auto set = [&](auto kernel) {
@@ -581,27 +585,37 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
       if (done) return cudaSuccess;
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(kLargest));
-      done = e == cudaSuccess;
+      both = both && e == cudaSuccess;
       return e;
     };
     cudaError_t e;
     switch (a.encoding) {
       case QLLM_KV_Q4H:
-        e = set(attention_scalar_kernel<QLLM_KV_Q4H>);
-        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_Q4H>, grid, dim3(256), smem, stream, a, part);
+        e = set(attention_scalar_kernel<QLLM_KV_Q4H, false>);
+        if (e == cudaSuccess) e = set(attention_scalar_kernel<QLLM_KV_Q4H, true>);
+        if (e == cudaSuccess)
+          e = tiled ? launch_ordered(attention_scalar_kernel<QLLM_KV_Q4H, true>, grid, dim3(256), smem, stream, a, part)
+                    : launch_ordered(attention_scalar_kernel<QLLM_KV_Q4H, false>, grid, dim3(256), smem, stream, a, part);
         break;
       case QLLM_KV_Q8:
-        e = set(attention_scalar_kernel<QLLM_KV_Q8>);
-        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_Q8>, grid, dim3(256), smem, stream, a, part);
+        e = set(attention_scalar_kernel<QLLM_KV_Q8, false>);
+        if (e == cudaSuccess) e = set(attention_scalar_kernel<QLLM_KV_Q8, true>);
+        if (e == cudaSuccess)
+          e = tiled ? launch_ordered(attention_scalar_kernel<QLLM_KV_Q8, true>, grid, dim3(256), smem, stream, a, part)
+                    : launch_ordered(attention_scalar_kernel<QLLM_KV_Q8, false>, grid, dim3(256), smem, stream, a, part);
         break;
       case QLLM_KV_F16:
-        e = set(attention_scalar_kernel<QLLM_KV_F16>);
-        if (e == cudaSuccess) e = launch_ordered(attention_scalar_kernel<QLLM_KV_F16>, grid, dim3(256), smem, stream, a, part);
+        e = set(attention_scalar_kernel<QLLM_KV_F16, false>);
+        if (e == cudaSuccess) e = set(attention_scalar_kernel<QLLM_KV_F16, true>);
+        if (e == cudaSuccess)
+          e = tiled ? launch_ordered(attention_scalar_kernel<QLLM_KV_F16, true>, grid, dim3(256), smem, stream, a, part)
+                    : launch_ordered(attention_scalar_kernel<QLLM_KV_F16, false>, grid, dim3(256), smem, stream, a, part);
         break;
       default:
         return fail(QLLM_INVALID_ARGUMENT, "unknown KV encoding");
     }
     if (e != cudaSuccess) return check_cuda(e, "attention shared memory opt-in");
+    if (both) configured[device & 63][a.encoding == QLLM_KV_Q4H ? 0 : a.encoding == QLLM_KV_Q8 ? 1 : 2] = true;
   }
   count_launch();
   if (a.skip_combine) return check_launch("attention");  // the caller merges the splits itself

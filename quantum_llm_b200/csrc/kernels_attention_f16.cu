@@ -91,6 +91,7 @@ struct F16Partials {
 };
 
 // grid (kv heads, context splits), block 64; dynamic shared memory kStages * kStageBytes.
+template <bool kTiled>  // grid z = row tile of a wide pass
 __global__ void __launch_bounds__(128)
 attention_f16_mma_kernel(AttentionArgs a, F16Partials part, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t ring[];
@@ -98,6 +99,7 @@ attention_f16_mma_kernel(AttentionArgs a, F16Partials part, uint32_t* error) {
   __shared__ uint32_t abort_word;
   pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
   pdl_wait();     // queries and the newest records come from the RoPE kernel before this one
+  if constexpr (kTiled) attention_row_tile(a, part);
   const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
   const uint32_t g = lane >> 2U, t = lane & 3U;
   const uint32_t kvh = blockIdx.x, split = blockIdx.y;
@@ -317,14 +319,20 @@ int launch_attention_f16_mma(const AttentionArgs& a, float* maxima, float* sums,
   int device = 0;
   cudaGetDevice(&device);
   if (!configured[device & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(attention_f16_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(attention_f16_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_f16_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem));
     if (e != cudaSuccess) return check_cuda(e, "F16 attention shared memory opt-in");
     configured[device & 63] = true;
   }
   const uint32_t mtiles = (a.rows * (a.q_heads / a.kv_heads) + 15U) / 16U;  // one warp per 16 matrix rows
-  return check_cuda(launch_ordered(attention_f16_mma_kernel, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), smem, stream, a,
-                                   part, error), "attention_f16_mma");
+  if (a.tiles > 1U)
+    return check_cuda(launch_ordered(attention_f16_mma_kernel<true>, dim3(a.kv_heads, a.max_splits, a.tiles),
+                                     dim3(32U * mtiles), smem, stream, a, part, error), "attention_f16_mma");
+  return check_cuda(launch_ordered(attention_f16_mma_kernel<false>, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), smem,
+                                   stream, a, part, error), "attention_f16_mma");
 }
 
 }  // namespace qllm

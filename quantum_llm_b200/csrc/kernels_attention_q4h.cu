@@ -223,6 +223,7 @@ struct Q4hPartials {
   float* outputs;
 };
 
+template <bool kTiled>  // grid z = row tile of a wide pass
 __global__ void __launch_bounds__(128)
 attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* error) {
   __shared__ __align__(128) uint8_t ring[kStages][kStageBytes];
@@ -235,6 +236,7 @@ attention_q4h_pipelined_kernel(AttentionArgs a, Q4hPartials part, uint32_t* erro
   __shared__ uint32_t abort_word;
   pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
   pdl_wait();     // queries and the newest records come from the RoPE kernel before this one
+  if constexpr (kTiled) attention_row_tile(a, part);
   const uint32_t tid = threadIdx.x, warp = tid >> 5U, lane = tid & 31U;
   const uint32_t g = lane >> 2U, t = lane & 3U;
   const uint32_t kvh = blockIdx.x, split = blockIdx.y;
@@ -432,8 +434,11 @@ int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float*
   // Ordinary stream order on purpose: started early, the thousand CTAs of this grid (and, behind
   // them, those of the next GEMVs) sit on the SMs waiting; measured 0.5 ms per step slower.
   const uint32_t mtiles = (a.rows * (a.q_heads / a.kv_heads) + 15U) / 16U;  // one warp per 16 matrix rows
-  return check_cuda(launch_ordered(attention_q4h_pipelined_kernel, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), 0, stream,
-                                   a, part, error), "attention_q4h");
+  if (a.tiles > 1U)
+    return check_cuda(launch_ordered(attention_q4h_pipelined_kernel<true>, dim3(a.kv_heads, a.max_splits, a.tiles),
+                                     dim3(32U * mtiles), 0, stream, a, part, error), "attention_q4h");
+  return check_cuda(launch_ordered(attention_q4h_pipelined_kernel<false>, dim3(a.kv_heads, a.max_splits), dim3(32U * mtiles), 0,
+                                   stream, a, part, error), "attention_q4h");
 }
 
 }  // namespace qllm

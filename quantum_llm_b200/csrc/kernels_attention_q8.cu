@@ -82,6 +82,7 @@ struct Q8Partials {
 
 // grid (context splits, 16-row matrix tiles), block 32 * kv_heads; dynamic shared memory =
 // kStages * 2 * kTile * kv_heads * 130 bytes.
+template <bool kTiled>  // grid z = row tile of a wide pass
 __global__ void __launch_bounds__(256)
 attention_q8_mma_kernel(AttentionArgs a, Q8Partials part, uint32_t* error) {
   extern __shared__ __align__(128) uint8_t ring[];
@@ -89,6 +90,7 @@ attention_q8_mma_kernel(AttentionArgs a, Q8Partials part, uint32_t* error) {
   __shared__ uint32_t abort_word;
   pdl_trigger();  // the combine kernel may be scheduled; it waits for this grid
   pdl_wait();     // queries and the newest records come from the RoPE kernel before this one
+  if constexpr (kTiled) attention_row_tile(a, part);
   const uint32_t tid = threadIdx.x, kvh = tid >> 5U, lane = tid & 31U;
   const uint32_t g = lane >> 2U, t = lane & 3U;
   const uint32_t split = blockIdx.x, mtile = blockIdx.y;
@@ -317,12 +319,18 @@ int launch_attention_q8_mma(const AttentionArgs& a, float* maxima, float* sums, 
   int device = 0;
   cudaGetDevice(&device);
   if (!configured[device & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(attention_q8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(kStages * 2U * kTile * 8U * kRecord));
+    cudaError_t e = cudaFuncSetAttribute(attention_q8_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kStages * 2U * kTile * 8U * kRecord));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_q8_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kStages * 2U * kTile * 8U * kRecord));
     if (e != cudaSuccess) return check_cuda(e, "Q8 attention shared memory opt-in");
     configured[device & 63] = true;
   }
-  return check_cuda(launch_ordered(attention_q8_mma_kernel, dim3(a.max_splits, mtiles), dim3(32U * a.kv_heads), smem,
+  if (a.tiles > 1U)
+    return check_cuda(launch_ordered(attention_q8_mma_kernel<true>, dim3(a.max_splits, mtiles, a.tiles), dim3(32U * a.kv_heads),
+                                     smem, stream, a, part, error), "attention_q8_mma");
+  return check_cuda(launch_ordered(attention_q8_mma_kernel<false>, dim3(a.max_splits, mtiles), dim3(32U * a.kv_heads), smem,
                                    stream, a, part, error), "attention_q8_mma");
 }
 

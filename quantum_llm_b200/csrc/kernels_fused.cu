@@ -155,6 +155,7 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
 constexpr uint32_t kCombineSplits = 512;
 
 // two CTAs per SM (128 registers): rows x heads CTAs of a verify pass then fit one wave
+template <bool kTiled>  // grid z = row tile of a wide pass
 __global__ void __launch_bounds__(256, 2)
 combine_quant_kernel(CombineArgs c) {
   // CTA = (row, query head), 8 warps: warp w merges the splits s = w (mod 8); a lane owns
@@ -168,7 +169,15 @@ combine_quant_kernel(CombineArgs c) {
   pdl_wait();
   const uint32_t warp = threadIdx.x >> 5U, lane = threadIdx.x & 31U;
   const uint32_t head = blockIdx.x, row = blockIdx.y, hd = c.head_dim;
-  const uint32_t ctx = *c.first_position + c.position_offset + 1U + row;
+  // grid z = row tile of a wide pass: gridDim.y rows each, partials one tile after the other
+  const uint32_t tile_row0 = kTiled ? blockIdx.z * gridDim.y : 0U;
+  if constexpr (kTiled) {
+    const size_t tile_shift = static_cast<size_t>(tile_row0) * c.max_splits * c.q_heads * (2U + hd);
+    c.maxima += tile_shift;
+    c.sums += tile_shift;
+    c.outputs += tile_shift;
+  }
+  const uint32_t ctx = *c.first_position + c.position_offset + 1U + tile_row0 + row;
   const uint32_t active = (ctx + c.split_tokens - 1U) / c.split_tokens;
   const size_t base = static_cast<size_t>(row) * c.max_splits * c.q_heads + head;
   const uint32_t vecs = hd / 4U;  // float4s per head: 16, 32 or 64
@@ -242,16 +251,20 @@ combine_quant_kernel(CombineArgs c) {
     const float gsum = static_cast<float>(total);
     out = make_float4(actv(static_cast<float>(r[0]) / gsum, c.bf16), actv(static_cast<float>(r[1]) / gsum, c.bf16),
                       actv(static_cast<float>(r[2]) / gsum, c.bf16), actv(static_cast<float>(r[3]) / gsum, c.bf16));
-    if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(row) * c.q_heads + head) * hd)[f] = out;
+    if (c.out) reinterpret_cast<float4*>(c.out + (static_cast<size_t>(tile_row0 + row) * c.q_heads + head) * hd)[f] = out;
   }
-  if (c.sink.kind >= 0) quant_store_quad(c.sink, row + c.sink_row_offset, (head * hd + 4U * f) / 16U, out, valid);
+  if (c.sink.kind >= 0)
+    quant_store_quad(c.sink, tile_row0 + row + c.sink_row_offset, (head * hd + 4U * f) / 16U, out, valid);
 }
 
 int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t stream) {
   if (c.max_splits > kCombineSplits || c.head_dim > 256U || c.head_dim % 16U)
     return fail(QLLM_INVALID_ARGUMENT, "unsupported split count or head_dim for the combine");
   count_launch();
-  return check_cuda(launch_pdl(combine_quant_kernel, dim3(c.q_heads, rows), dim3(256), 0, stream, c), "combine_quant");
+  if (c.tiles > 1U)
+    return check_cuda(launch_pdl(combine_quant_kernel<true>, dim3(c.q_heads, rows, c.tiles), dim3(256), 0, stream, c),
+                      "combine_quant");
+  return check_cuda(launch_pdl(combine_quant_kernel<false>, dim3(c.q_heads, rows), dim3(256), 0, stream, c), "combine_quant");
 }
 
 // --------------------------------------------------------- materialise a GEMV result

@@ -309,7 +309,7 @@ struct qllm_provider {
     draft_logits.alloc(c.draft_vocab, "draft logits");
     // the page pool keeps a few slots of slack past max_context for speculative rows
     max_splits = (c.max_context + 2U * kMaxRows + c.split_tokens - 1U) / c.split_tokens;
-    attn_ws.alloc(attention_workspace_bytes(H, c.q_heads, c.head_dim, max_splits), "attention partials");
+    attn_ws.alloc(attention_workspace_bytes(R, c.q_heads, c.head_dim, max_splits), "attention partials");
     topk_ws.alloc(topk_workspace_bytes(H, c.vocab, 64), "top-k partials");
     argmax_out.alloc(H, "argmax");
     top_tokens.alloc(static_cast<size_t>(H) * 64U, "top-k tokens");
@@ -452,8 +452,13 @@ struct qllm_provider {
     rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
     ok(launch_rope_kv_store_fused(rs, stream));
     const uint32_t qkv_w = c.q_heads * c.head_dim;  // rotated queries only
-    for (uint32_t r0 = 0; r0 < rows; r0 += tile_rows) {
-      const uint32_t n = std::min(tile_rows, rows - r0);
+    // the full tiles go out as one launch (grid z = tile), a ragged last tile as a second one
+    const uint32_t full_tiles = rows / tile_rows;
+    for (uint32_t pass = 0; pass < 2U; ++pass) {
+      const uint32_t r0 = pass ? full_tiles * tile_rows : 0U;
+      const uint32_t n = pass ? rows - r0 : tile_rows;
+      const uint32_t tiles = pass ? 1U : full_tiles;
+      if (!n) continue;
       AttentionArgs at{};
       at.encoding = enc;
       at.page_table = st.page_table;
@@ -479,6 +484,7 @@ struct qllm_provider {
       at.query_q8_scale = rs.q8_scale ? rs.q8_scale + static_cast<size_t>(r0) * c.q_heads : nullptr;
       at.error = kernel_error.p;
       at.skip_combine = true;
+      at.tiles = tiles;
       ok(launch_attention(at, stream));
       CombineArgs cb{};
       const size_t items = static_cast<size_t>(n) * splits * c.q_heads;
@@ -495,6 +501,7 @@ struct qllm_provider {
       cb.out = nullptr;
       cb.sink = sink_for(b.o, rows);
       cb.sink_row_offset = r0;
+      cb.tiles = tiles;
       ok(launch_combine_quant(cb, n, stream));
     }
     const GemvOut o_out = gemv(b.o, rows, 0U, nullptr, 0);
