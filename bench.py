@@ -65,7 +65,7 @@ def parse():
                     help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 160, 640")
     ap.add_argument("--prefill-bench", type=int, default=0, metavar="TOKENS",
                     help="time the prompt path (target chunks + draft priming) over TOKENS prompt tokens")
-    ap.add_argument("--chunk-rows", type=int, default=40, help="rows per prompt chunk of --prefill-bench (1..40)")
+    ap.add_argument("--chunk-rows", type=int, default=128, help="rows per prompt chunk of --prefill-bench (1..128)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph (profiler captures)")
     args = ap.parse_args()
@@ -574,7 +574,7 @@ def microbench(args):
 
 def prefill_bench(args):
     """Prompt path on one GPU: target chunks of --chunk-rows rows (8 is the reference's microbatch
-    limit, 40 the widest chunk here), each followed by its draft-priming batch, from an empty
+    limit, 128 the widest chunk here), each followed by its draft-priming batch, from an empty
     cache; host tokens in, first token out.  Every chunk streams the whole model once."""
     import numpy as np
     import torch

@@ -184,7 +184,7 @@ int qllm_provider_telemetry(qllm_provider* provider, qllm_request_state* state, 
 void* qllm_provider_stream(qllm_provider* provider);
 /* Most rows qllm_provider_prefill_chunk / _synchronize_exact_decode_batch take at once. The
  * reference's microbatch paths stop at kMaximumWorkspaceRows = 8 (dense_fp4_provider.cpp:8854-9200)
- * and its wider prompt batches go through fp4_gemm_block32_kernel; here a chunk of up to 40 rows
+ * and its wider prompt batches go through fp4_gemm_block32_kernel; here a chunk of up to 128 rows
  * is one operand of the block-scaled tensor-core kernel (one pass over the weights per chunk),
  * attention takes it in tiles of 8 rows and only its last row reaches the head. A tensor-parallel
  * provider stays at 8 (the size of its exchange slots). */

@@ -578,7 +578,7 @@ inline size_t round4(size_t n) { return (n + 3U) & ~static_cast<size_t>(3U); }  
 }  // namespace
 
 // one arrival counter of the router kernel per row: the widest pass holds fewer rows than this
-constexpr uint32_t kRouterTickets = 64;
+constexpr uint32_t kRouterTickets = 128;
 
 size_t moe_workspace_floats(uint32_t rows, uint32_t route_width, uint32_t hidden, uint32_t expert_ffn) {
   const size_t selections = static_cast<size_t>(rows) * route_width;

@@ -125,7 +125,7 @@ struct qllm_provider {
   static constexpr uint32_t kMaxRows = 8;      // kMaximumWorkspaceRows of the microbatch paths
   // widest prompt chunk: the projections see it as one operand (one pass over the weights),
   // attention takes it in tiles of kMaxRows rows, and only its last row goes through the head
-  static constexpr uint32_t kChunkRows = 40;
+  static constexpr uint32_t kChunkRows = 128;  // one activation tile of the tensor-core kernel
   uint32_t chunk_limit() const { return tp_ranks ? kMaxRows : kChunkRows; }  // exchange slots hold kMaxRows rows
   static constexpr uint32_t kResultRing = 64;
   qllm_config cfg{};

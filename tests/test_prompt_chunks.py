@@ -36,10 +36,10 @@ def run(model, prompt, chunk_rows, gemv_impl, attention_impl, temperature=0):
 
 
 @pytest.mark.parametrize("cfg", [synth.TINY, MOE], ids=["dense", "routed"])
-@pytest.mark.parametrize("chunk_rows", [8, 13, 40])
+@pytest.mark.parametrize("chunk_rows", [8, 13, 40, 128])
 def test_exact_path_does_not_depend_on_the_chunk_width(cfg, chunk_rows):
     model = synth.SynthModel(cfg, seed=3)
-    prompt = synth.prompt(4096, 97, 5)      # 97 = 2 x 40 + 17: a ragged last chunk at every width
+    prompt = synth.prompt(4096, 97, 5)      # 97 = 2 x 40 + 17 = 12 x 8 + 1: ragged chunks and row tiles
     narrow = run(model, prompt, 5, 0, 0)
     wide = run(model, prompt, chunk_rows, 0, 0)
     assert wide["first"] == narrow["first"] and wide["drafts"] == narrow["drafts"]
@@ -61,14 +61,15 @@ def test_wide_chunks_write_the_same_cache_pages():
         assert np.array_equal(a["provider"].read_page(a["state"], page), b["provider"].read_page(b["state"], page))
 
 
+@pytest.mark.parametrize("chunk_rows", [40, 128])
 @pytest.mark.parametrize("kv_encoding", [ob.KV_Q4H, ob.KV_F16])
-def test_tensor_core_paths_take_wide_chunks(kv_encoding):
+def test_tensor_core_paths_take_wide_chunks(kv_encoding, chunk_rows):
     # head_dim 128 so that the tensor-core attention kernels run on the 8-row tiles
     cfg = dict(synth.TINY, head_dim=128, rotary_dim=64, kv_encoding=kv_encoding)
     model = synth.SynthModel(cfg, seed=5)
     prompt = synth.prompt(4096, 90, 7)
     exact = run(model, prompt, 5, 0, 0)
-    fast = run(model, prompt, 40, 1, 1)
+    fast = run(model, prompt, chunk_rows, 1, 1)
     # different accumulation order: the greedy stream may only part at a near-tie, after which
     # the two runs see different inputs; the prompt's first token and most of the stream agree
     same = 0
@@ -84,10 +85,10 @@ def test_chunk_limits():
     model = synth.SynthModel(synth.TINY, seed=0)
     prq, _ = request_pair(context_limit=256)
     p = provider_from_synth(model)
-    assert p.max_chunk_rows() == 40
+    assert p.max_chunk_rows() == 128
     st = p.create_request_state()
     with pytest.raises(QllmError):
-        p.prefill_chunk(st, synth.prompt(4096, 41, 0), 0)
+        p.prefill_chunk(st, synth.prompt(4096, 129, 0), 0)
     p.prefill_chunk(st, synth.prompt(4096, 40, 0), 0)
     with pytest.raises(QllmError):          # the synchronisation batch must cover the retained chunk
         p.synchronize_exact_decode_batch(st, prq, synth.prompt(4096, 8, 1), 0, True)
