@@ -14,7 +14,7 @@ over the N GPUs instead (q/k/v heads and FFN columns per rank, partial sums of t
 projections exchanged through peer memory inside the GEMV kernel).
 
 `--microbench` times the tensor-core GEMV alone on the verify-step projection shapes at
-M = 5, 40, 160, 640 rows (one JSON line per shape and M).
+M = 5, 40, 128, 160, 640 rows (one JSON line per shape and M).
 
   python bench.py --gpus N --steps K --warmup W [--impl reference]
 """
@@ -62,7 +62,7 @@ def parse():
                     help="cached tokens per attention CTA (multiple of 64; 0 = the model configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--microbench", action="store_true",
-                    help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 160, 640")
+                    help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 128, 160, 640")
     ap.add_argument("--prefill-bench", type=int, default=0, metavar="TOKENS",
                     help="time the prompt path (target chunks + draft priming) over TOKENS prompt tokens")
     ap.add_argument("--chunk-rows", type=int, default=128, help="rows per prompt chunk of --prefill-bench (1..128)")
@@ -506,7 +506,7 @@ def ours(args):
 def microbench(args):
     """Kernel microbenchmark of the NVFP4 GEMV / skinny GEMM on the verify-step shapes: the 27B
     projections (N x K: qkv 7168x5120, o 5120x5120, gate/up 34816x5120, down 5120x17408, lm-head
-    151936x5120) at M = 5, 40, 160, 640 activation rows.  Random NVFP4 weights, N(0,1)
+    151936x5120) at M = 5, 40, 128, 160, 640 activation rows.  Random NVFP4 weights, N(0,1)
     activations; enough distinct matrices per shape to stream at least 1 GB (far beyond L2) per
     timed pass; the tensor-core kernel alone, CUDA events on the launching stream.  One JSON line
     per (shape, M): time, algorithmic GB/s (weights 0.5625 B/element + BF16 rows in and out) against
@@ -538,7 +538,7 @@ def microbench(args):
             mats.append(m)
             handles.append(h)
         stream.synchronize()
-        for rows in (5, 40, 160, 640):
+        for rows in (5, 40, 128, 160, 640):
             x = torch.randn((rows, k), device=dev, dtype=torch.float32)
             y = torch.empty((rows, n), device=dev, dtype=torch.float32)
             ws_bytes = L.qllm_k_nvfp4_gemv_workspace_bytes(rows, n, k)
