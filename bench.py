@@ -14,7 +14,8 @@ over the N GPUs instead (q/k/v heads and FFN columns per rank, partial sums of t
 projections exchanged through peer memory inside the GEMV kernel).
 
 `--microbench` times the tensor-core GEMV alone on the verify-step projection shapes at
-M = 5, 40, 128, 160, 640 rows (one JSON line per shape and M).
+M = 5, 40, 128, 160, 640 rows (one JSON line per shape and M).  `--prefill-bench TOKENS` times the
+prompt path (target chunks of `--chunk-rows` rows + draft priming, host tokens in, first token out).
 
   python bench.py --gpus N --steps K --warmup W [--impl reference]
 """
