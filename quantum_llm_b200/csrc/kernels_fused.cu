@@ -189,10 +189,17 @@ combine_quant_kernel(CombineArgs c) {
     const uint32_t s = lane + 32U * i;
     mine[i] = s < active ? c.maxima[base + static_cast<size_t>(s) * c.q_heads] : kNegInf;
   }
+  // The splits are merged in eight classes s = cls (mod 8), one partial sum per class, whatever
+  // the number of warps: eight warps take one class each; the row-tiled form (thousands of CTAs
+  // with one or two splits each at prompt lengths) runs two warps that take four classes each,
+  // so that more CTAs fit an SM.  Same additions in the same order either way.
+  constexpr uint32_t kWarps = kTiled ? 2U : 8U;
+  bool have_max = false;
+  uint32_t cls = warp;
+  do {
   double r[2][4] = {{0.0, 0.0, 0.0, 0.0}, {0.0, 0.0, 0.0, 0.0}};
   double sum = 0.0;
-  bool have_max = false;
-  for (uint32_t s0 = warp; s0 < active; s0 += 8U * kBatch) {
+  for (uint32_t s0 = cls; s0 < active; s0 += 8U * kBatch) {
     float4 o[kBatch][2];
     float ssum[kBatch], smax[kBatch];
 #pragma unroll
@@ -229,11 +236,13 @@ combine_quant_kernel(CombineArgs c) {
   for (int h = 0; h < 2; ++h) {
     const uint32_t f = lane + 32U * h;
     if (f < vecs) {
-      partial[warp][0][f] = r[h][0]; partial[warp][1][f] = r[h][1];
-      partial[warp][2][f] = r[h][2]; partial[warp][3][f] = r[h][3];
+      partial[cls][0][f] = r[h][0]; partial[cls][1][f] = r[h][1];
+      partial[cls][2][f] = r[h][2]; partial[cls][3][f] = r[h][3];
     }
   }
-  if (lane == 0U) sums[warp] = sum;
+  if (lane == 0U) sums[cls] = sum;
+  cls += kWarps;
+  } while (kTiled && cls < 8U);
   __syncthreads();
   if (warp >= (vecs + 31U) / 32U) return;  // warps 0 (and 1 for head_dim 256) finish
   const uint32_t f = warp * 32U + lane;
@@ -262,7 +271,7 @@ int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t strea
     return fail(QLLM_INVALID_ARGUMENT, "unsupported split count or head_dim for the combine");
   count_launch();
   if (c.tiles > 1U)
-    return check_cuda(launch_pdl(combine_quant_kernel<true>, dim3(c.q_heads, rows, c.tiles), dim3(256), 0, stream, c),
+    return check_cuda(launch_pdl(combine_quant_kernel<true>, dim3(c.q_heads, rows, c.tiles), dim3(64), 0, stream, c),
                       "combine_quant");
   return check_cuda(launch_pdl(combine_quant_kernel<false>, dim3(c.q_heads, rows), dim3(256), 0, stream, c), "combine_quant");
 }
