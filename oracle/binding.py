@@ -57,14 +57,17 @@ class StepResult(C.Structure):
                 ("rejected", C.c_uint32)]
 
 
-def _makefile_reference():
-    for line in open(os.path.join(HERE, "Makefile")):
-        if line.startswith("REFERENCE ?="):
-            return line.split("=", 1)[1].strip()
-    return ""
+def reference_root():
+    """Where the reference's source tree lies: QLLM_REFERENCE, else a directory named
+    `reference` beside this repository; "" when neither exists."""
+    env = os.environ.get("QLLM_REFERENCE", "")
+    if env:
+        return env
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(os.path.join(sibling, "runtime")) else ""
 
 
-REFERENCE_DEFAULT = _makefile_reference()
+REFERENCE_DEFAULT = reference_root()
 
 
 def build(force=False):
@@ -76,11 +79,18 @@ def build(force=False):
         subprocess.run(["make", "-C", HERE, "libqllm_oracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
     # the reference's own sampler and descriptor parser, where the reference tree is present
-    # (QLLM_REFERENCE, else the Makefile's default location); prebuilt files are kept otherwise
+    # (reference_root()); prebuilt files are kept otherwise
     refs = [os.path.join(HERE, "_ref", name) for name in ("libqllm_ref_sampler.so", "libqllm_ref_descriptor.so")]
-    reference = os.environ.get("QLLM_REFERENCE", REFERENCE_DEFAULT)
-    if (force or not all(os.path.exists(r) for r in refs)) and os.path.isdir(reference):
+    reference = reference_root()
+    if (force or not all(os.path.exists(r) for r in refs)) and reference and os.path.isdir(reference):
         subprocess.run(["make", "-C", HERE, "ref", f"REFERENCE={reference}"], check=True, stdout=subprocess.DEVNULL)
+    # the reference's own CUDA kernels (GPU pins of the oracle): built once, where the reference tree lies
+    kernels = os.path.join(HERE, "_ref", "libqllm_ref_kernels.so")
+    shim = os.path.join(HERE, "ref_kernels_shim.cu")
+    if reference and os.path.isdir(reference) and (
+            force or not os.path.exists(kernels) or os.path.getmtime(kernels) < os.path.getmtime(shim)):
+        subprocess.run(["make", "-C", HERE, "ref_kernels", f"REFERENCE={reference}"], check=True,
+                       stdout=subprocess.DEVNULL)
     return lib
 
 
@@ -153,6 +163,39 @@ def ref_sampler():
         R.ref_rejection_sample.argtypes = [u32, vp, vp, u32, vp, vp, u32, f64, f64, vp]
         _ref = R
     return _ref
+
+
+_ref_kernels = None
+
+
+def ref_kernels():
+    """The reference's own CUDA kernels behind oracle/ref_kernels_shim.cu (oracle/_ref), or None
+    when they were not built.  Needs a GPU to call."""
+    global _ref_kernels
+    if _ref_kernels is None:
+        build()
+        path = os.path.join(HERE, "_ref", "libqllm_ref_kernels.so")
+        if not os.path.exists(path):
+            return None
+        R = C.CDLL(path)
+        u32, f32, vp, sz, i = C.c_uint32, C.c_float, C.c_void_p, C.c_size_t, C.c_int
+        sig = {
+            "qr_last_error": (C.c_char_p, []),
+            "qr_nvfp4_gemv": (i, [vp, vp, f32, f32, u32, u32, vp, vp, vp, u32]),
+            "qr_store_q4h": (i, [vp, vp, vp, u32, u32, u32, u32, u32, u32]),
+            "qr_store_q8": (i, [vp, vp, vp, u32, u32, u32, u32, u32, u32]),
+            "qr_quantize_queries_q8": (i, [vp, vp, vp, u32, u32, u32]),
+            "qr_attention_q4h": (i, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, u32, i]),
+            "qr_attention_q8": (i, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, u32, i]),
+            "qr_argmax_batch": (i, [vp, u32, u32, vp]),
+            "qr_topk_workspace_items": (sz, [u32]),
+            "qr_topk": (i, [vp, u32, u32, vp, vp, vp, sz, vp, sz]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(R, name)
+            fn.restype, fn.argtypes = res, args
+        _ref_kernels = R
+    return _ref_kernels
 
 
 # ------------------------------------------------------------------ helpers

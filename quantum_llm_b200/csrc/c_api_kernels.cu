@@ -40,9 +40,14 @@ int qllm_k_nvfp4_gemv(const qllm_matrix* m, uint32_t first_row, uint32_t row_cou
                       float* y, uint32_t batch, void* workspace, size_t workspace_bytes, int impl,
                       void* stream) {
   if (!m || !m->codes || !m->scales || !x || !y || !workspace || !m->rows || !m->cols ||
-      m->cols % 16U || !batch || !row_count || first_row + row_count > m->rows ||
+      m->cols % 16U || !batch || !row_count || row_count > m->rows || first_row > m->rows - row_count ||
       !(m->weight_scale > 0.0F) || !(m->input_scale > 0.0F))
     return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 GEMV");
+  // the kernels read x as float4, the codes as uint2 and the workspace as uint4
+  if ((reinterpret_cast<uintptr_t>(x) & 15U) || (reinterpret_cast<uintptr_t>(m->codes) & 7U) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15U))
+    return fail(QLLM_INVALID_ARGUMENT,
+                "native NVFP4 GEMV needs x and the workspace on 16-byte and the codes on 8-byte boundaries");
   if (workspace_bytes < qllm_k_nvfp4_gemv_workspace_bytes(batch, row_count, m->cols))
     return fail(QLLM_INVALID_ARGUMENT, "native NVFP4 GEMV workspace is too small");
   auto s = static_cast<cudaStream_t>(stream);

@@ -521,8 +521,8 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream) {
-  if (!w.ready || m.cols % kTileK || first_row % kTileRows || !batch || !row_count ||
-      first_row + row_count > m.rows)
+  if (!w.ready || m.cols % kTileK || first_row % kTileRows || !batch || !row_count || row_count > m.rows ||
+      first_row > m.rows - row_count)
     return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, first row % 128)");
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
   const uint32_t k_chunks = m.cols / kTileK;
@@ -595,7 +595,11 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   uint32_t stages = 4U;
   while (stages > 2U && stages * stage_bytes > 108U * 1024U) --stages;
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024U;
-  static size_t opted = 0;
+  // the opt-in belongs to the device: one entry per device of the process
+  static size_t opted_by_device[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  size_t& opted = opted_by_device[device & 63];
   if (smem > opted) {
     rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");

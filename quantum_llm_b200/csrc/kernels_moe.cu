@@ -635,7 +635,11 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
   int rc = 0;
   const size_t smem_staged = static_cast<size_t>(kStagedStages) * staged_stage_bytes(a.hidden) + smem_gu;
   if (a.staged && a.hidden % 256U == 0U && smem_staged <= 110U * 1024U) {
-    static size_t opted = 48U * 1024U;
+    static size_t opted_by_device[64] = {};  // the opt-in belongs to the device
+    int device = 0;
+    cudaGetDevice(&device);
+    size_t& opted = opted_by_device[device & 63];
+    if (opted < 48U * 1024U) opted = 48U * 1024U;
     if (smem_staged > opted) {
       rc = check_cuda(cudaFuncSetAttribute(moe_gate_up_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(110U * 1024U)), "expert kernel shared memory opt-in");
@@ -657,7 +661,10 @@ int launch_moe_experts(const MoeArgs& a, cudaStream_t stream) {
   const bool wide = (a.expert_ffn / 16U) % 32U == 0U;
   const size_t smem_down_staged = static_cast<size_t>(kDownStages) * 8U * down_tile_bytes(a.expert_ffn) + smem_d;
   if (a.staged && a.expert_ffn % 32U == 0U && a.hidden % kDownTile == 0U && smem_down_staged <= 72U * 1024U) {
-    static bool opted = false;
+    static bool opted_by_device[64] = {};  // the opt-in belongs to the device
+    int device = 0;
+    cudaGetDevice(&device);
+    bool& opted = opted_by_device[device & 63];
     if (!opted) {
       rc = check_cuda(cudaFuncSetAttribute(moe_down_staged_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(72U * 1024U)), "expert kernel shared memory opt-in");

@@ -169,7 +169,7 @@ __global__ void accept_kernel(AcceptArgs a) {
   uint32_t accepted = 0, next_token = 0;
   bool rejected = false;
   for (; accepted < proposals; ++accepted) {
-    if (!target_distribution(s, a, accepted, &target)) { s->error = 2U; return; }
+    if (!target_distribution(s, a, accepted, &target)) { s->error = record->error = 2U; return; }
     const DraftDistribution& d = s->drafts[accepted];
     uint32_t token = 0;
     const int r = rejection_sample(s->verify_tokens[accepted + 1U], target.tokens, target.probs,
@@ -177,11 +177,11 @@ __global__ void accept_kernel(AcceptArgs a) {
                                    counter_uniform(s->seed, position + accepted, 100U, accepted),
                                    counter_uniform(s->seed, position + accepted, 200U, accepted),
                                    &token);
-    if (r < 0) { s->error = 3U; return; }
+    if (r < 0) { s->error = record->error = 3U; return; }
     if (r == 0) { next_token = token; rejected = true; break; }
   }
   if (!rejected) {
-    if (!target_distribution(s, a, accepted, &target)) { s->error = 2U; return; }
+    if (!target_distribution(s, a, accepted, &target)) { s->error = record->error = 2U; return; }
     next_token = sample_distribution(target.tokens, target.probs, target.count,
                                      counter_uniform(s->seed, position + accepted, 300U, 0U));
   }

@@ -1,5 +1,5 @@
 """Regenerates tests/golden/*.json.  Run where the reference tree is present (its location:
-QLLM_REFERENCE, else the default of oracle/Makefile); the parity tests only read the committed
+QLLM_REFERENCE, else a `reference` directory beside the repository); the parity tests only read the committed
 JSON.
 
   fp4_tables.json     decode tables produced by importing the reference's Python
