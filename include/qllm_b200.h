@@ -210,12 +210,18 @@ int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
  *   2. the host exchanges the handles (all-gather in rank order);
  *   3. every rank: qllm_provider_tp_attach(provider, all_handles)  -- maps the peers' areas.
  * Needs the tensor-core GEMV (qllm_provider_set_gemv_impl(1)), K of the local o and down
- * projections a multiple of 256, and peer access between the GPUs.  ranks == 1 runs the same
+ * projections a multiple of 64, and peer access between the GPUs.  ranks == 1 runs the same
  * code path without peers.  A value that has not arrived after about a second of polling sets the kernel
  * error word (the step fails with QLLM_INTERNAL); nothing waits without a limit. */
 #define QLLM_TP_HANDLE_BYTES 64
 int qllm_provider_tp_export(qllm_provider* provider, uint32_t rank, uint32_t ranks, void* handle);
 int qllm_provider_tp_attach(qllm_provider* provider, const void* handles);
+/* Size in bytes of this rank's exchange area (0 before qllm_provider_tp_export). */
+size_t qllm_provider_tp_area_bytes(const qllm_provider* provider);
+/* Step 3 for a host that drives all GPUs from ONE process (peer access enabled): `areas[r]` is rank
+ * r's exchange area as a device pointer of at least qllm_provider_tp_area_bytes() bytes, zeroed
+ * before the first step (the own rank's entry is ignored).  The areas stay owned by the caller. */
+int qllm_provider_tp_attach_local(qllm_provider* provider, void* const* areas);
 
 /* ---- runtime-model.tsv: the artifact's model descriptor -------------------------------------
  * Host-only.  qllm_descriptor_parse reads the descriptor text with the grammar and the validity
@@ -317,6 +323,14 @@ int qllm_provider_read_page(qllm_provider* provider, qllm_request_state* state, 
  * pseudo-random records and advance the cached prefix; stands in for a long prompt. */
 int qllm_provider_fill_synthetic_kv(qllm_provider* provider, qllm_request_state* state,
                                     uint32_t first, uint32_t count, uint64_t seed);
+
+/* Measurement aid without a reference counterpart: runs the verify pass alone (target forward over
+ * the pending guaranteed token and drafts, head, candidate selection) `repeats` times back to back
+ * and returns its mean duration in milliseconds, measured with CUDA events on the provider's
+ * stream.  It recomputes what the next step computes anyway, so decoding can continue afterwards.
+ * Needs pending drafts (after a prefill or a step). */
+int qllm_provider_time_verify(qllm_provider* provider, qllm_request_state* state,
+                              const qllm_request* request, uint32_t repeats, float* mean_ms);
 
 /* ------------------------------------------------------- kernel layer */
 /* All pointers are device memory unless stated; stream is a cudaStream_t. */

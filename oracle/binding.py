@@ -130,6 +130,8 @@ def lib():
             "qo_session_create": (vp, [C.POINTER(Config), C.POINTER(Weights)]),
             "qo_session_destroy": (None, [vp]),
             "qo_prefill": (C.c_int, [vp, vp, u32, u32, C.POINTER(Request), vp]),
+            "qo_prefill_at": (C.c_int, [vp, vp, u32, u32, u32, C.POINTER(Request), vp]),
+            "qo_fill_synthetic_kv": (C.c_int, [vp, u32, u32, u64]),
             "qo_execute_exact_decode": (C.c_int, [vp, C.POINTER(Request), u32, u32, C.POINTER(StepResult)]),
             "qo_draft_count": (u32, [vp]), "qo_drafts": (None, [vp, vp]),
             "qo_last_logits": (vp, [vp]), "qo_last_hidden": (vp, [vp]),
@@ -266,6 +268,18 @@ class Session:
         if lib().qo_prefill(self.h, _ptr(tokens), len(tokens), chunk_rows, C.byref(request), C.byref(first)):
             raise RuntimeError(lib().qo_last_error().decode())
         return first.value
+
+    def prefill_at(self, tokens, base, chunk_rows, request):
+        """Prompt positions [base, base + len(tokens)) behind a cached prefix of `base` positions."""
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        first = C.c_uint32(0)
+        if lib().qo_prefill_at(self.h, _ptr(tokens), len(tokens), base, chunk_rows, C.byref(request), C.byref(first)):
+            raise RuntimeError(lib().qo_last_error().decode())
+        return first.value
+
+    def fill_synthetic_kv(self, first, count, seed):
+        if lib().qo_fill_synthetic_kv(self.h, first, count, seed):
+            raise RuntimeError(lib().qo_last_error().decode())
 
     def execute_exact_decode(self, request, guaranteed_token, position):
         res = StepResult()

@@ -1032,15 +1032,93 @@ qo_session* qo_session_create(const qo_config* config, const qo_weights* weights
 }
 void qo_session_destroy(qo_session* s) { delete s; }
 
-int qo_prefill(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_t chunk_rows,
-               const qo_request* rq, uint32_t* first_token) {
+namespace {
+uint32_t hash32(uint64_t x) {
+  x ^= x >> 33U; x *= 0xff51afd7ed558ccdULL; x ^= x >> 33U; x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33U;
+  return static_cast<uint32_t>(x);
+}
+}  // namespace
+
+// Seeded synthetic cache records for positions [first, first + count) of every layer (target
+// layers, then the draft layer): the host twin of the CUDA library's synthetic cache fill, so
+// that long contexts need no prompt pass on either side.  Same bytes: a record's scale is
+// f16(0.1 + 0.2 u) with u from a 64-bit mix of (seed, position, kv head, K|V), its codes are
+// uniform over the encoding's range.  The cached prefix then ends at first + count.
+int qo_fill_synthetic_kv(qo_session* s, uint32_t first, uint32_t count, uint64_t seed) {
   try {
     const auto& c = s->cfg;
-    if (!count || !chunk_rows || count + 1U >= rq->context_limit || rq->context_limit > c.max_context)
-      throw std::runtime_error("invalid prefill request");
-    s->mtp_length = 0;
+    if (first != s->mtp_length || first + count > c.max_context)
+      throw std::runtime_error("synthetic cache fill must extend the cached prefix");
+    const uint32_t pt = c.page_tokens, kv = c.kv_heads, hd = c.head_dim;
+    const size_t records = static_cast<size_t>(pt) * kv;
+    for (uint32_t l = 0; l <= c.layers; ++l) {
+      const uint32_t enc = l < c.layers ? c.kv_encoding : c.mtp_kv_encoding;
+      const uint64_t layer_seed = seed + 0x9e3779b97f4a7c15ULL * (l + 1U);
+#pragma omp parallel for schedule(static)
+      for (int64_t item = 0; item < static_cast<int64_t>(count) * kv * 2; ++item) {
+        const uint32_t which = static_cast<uint32_t>(item & 1);
+        const uint32_t h = static_cast<uint32_t>((item >> 1) % kv);
+        const uint32_t pos = first + static_cast<uint32_t>((item >> 1) / kv);
+        uint8_t* layer = s->pages[pos / pt] + s->layer_off[l];
+        const uint32_t slot = pos % pt;
+        const uint64_t key = layer_seed ^ (static_cast<uint64_t>(pos) << 20U) ^ (static_cast<uint64_t>(h) << 4U) ^ which;
+        const uint16_t scale = f16_bits(0.1F + 0.2F * static_cast<float>(hash32(key) & 0xffffU) / 65536.0F);
+        if (enc == QO_KV_Q4H) {
+          const size_t rec = static_cast<size_t>(h) * pt + slot;
+          uint8_t* codes = layer + (which ? records * (hd / 2U) + records * 2U : 0U) + rec * (hd / 2U);
+          uint8_t* sc = layer + records * (hd / 2U) + (which ? records * (hd / 2U) + records * 2U : 0U);
+          std::memcpy(sc + rec * 2U, &scale, 2);
+          for (uint32_t d = 0; d < hd / 2U; ++d) {
+            const uint32_t r = hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U);
+            const int lo = static_cast<int>(r % 15U) - 7, hi = static_cast<int>((r >> 8U) % 15U) - 7;
+            codes[d] = static_cast<uint8_t>((lo & 15) | ((hi & 15) << 4));
+          }
+        } else if (enc == QO_KV_Q8) {
+          const size_t rec = static_cast<size_t>(slot) * kv + h;
+          uint8_t* r8 = layer + (which ? records * (hd + 2U) : 0U) + rec * (hd + 2U);
+          const uint16_t small = f16_bits(f16_value(scale) / 16.0F);
+          std::memcpy(r8 + hd, &small, 2);
+          for (uint32_t d = 0; d < hd; ++d)
+            r8[d] = static_cast<uint8_t>(static_cast<int8_t>(
+                static_cast<int>(hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U) % 255U) - 127));
+        } else {
+          const size_t rec = static_cast<size_t>(slot) * kv + h;
+          uint8_t* r16 = layer + (which ? records * hd * 2U : 0U) + rec * hd * 2U;
+          for (uint32_t d = 0; d < hd; ++d) {
+            const uint16_t bits = f16_bits(
+                (static_cast<float>(hash32(key * 0x9e3779b97f4a7c15ULL + d + 1U) & 0xffffU) / 32768.0F - 1.0F) * 1.4F);
+            std::memcpy(r16 + 2U * d, &bits, 2);
+          }
+        }
+      }
+    }
+    s->mtp_length = first + count;
     s->draft_valid = false;
-    for (uint32_t first = 0; first < count; first += chunk_rows) {
+    return 0;
+  } catch (const std::exception& e) {
+    g_error = e.what();
+    return -1;
+  }
+}
+
+int qo_prefill(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_t chunk_rows,
+               const qo_request* rq, uint32_t* first_token) {
+  s->mtp_length = 0;
+  return qo_prefill_at(s, tokens, count, 0U, chunk_rows, rq, first_token);
+}
+
+// The prompt tokens of positions [base, base + count) behind a cached prefix of `base` positions.
+int qo_prefill_at(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_t base, uint32_t chunk_rows,
+                  const qo_request* rq, uint32_t* first_token) {
+  try {
+    const auto& c = s->cfg;
+    if (!count || !chunk_rows || base + count + 1U >= rq->context_limit || rq->context_limit > c.max_context ||
+        s->mtp_length != base)
+      throw std::runtime_error("invalid prefill request");
+    s->draft_valid = false;
+    tokens -= base;  // indexed by absolute position below
+    count += base;
+    for (uint32_t first = base; first < count; first += chunk_rows) {
       const uint32_t rows = std::min(chunk_rows, count - first);
       const bool last = first + rows == count;
       std::vector<uint32_t> positions(rows), next(rows), rotary(rows);

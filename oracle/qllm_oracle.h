@@ -190,6 +190,12 @@ void qo_session_destroy(qo_session* session);
 int qo_prefill(qo_session* session, const uint32_t* tokens, uint32_t count,
                uint32_t chunk_rows, const qo_request* request,
                uint32_t* first_token);
+/* The same for prompt positions [base, base + count) behind a cached prefix of `base` positions. */
+int qo_prefill_at(qo_session* session, const uint32_t* tokens, uint32_t count, uint32_t base,
+                  uint32_t chunk_rows, const qo_request* request, uint32_t* first_token);
+/* Seeded synthetic cache records for positions [first, first + count) of every layer -- the host
+ * twin of the CUDA library's synthetic cache fill (same bytes); extends the cached prefix. */
+int qo_fill_synthetic_kv(qo_session* session, uint32_t first, uint32_t count, uint64_t seed);
 int qo_execute_exact_decode(qo_session* session, const qo_request* request,
                             uint32_t guaranteed_token, uint32_t position,
                             qo_step_result* result);

@@ -14,9 +14,19 @@
 #include <cstdint>
 #include <string>
 
+#include "expert/runtime/cuda/flash_attention.hpp"
 #include "expert/runtime/cuda/transformer_kernels.hpp"
 
 namespace rc = expert::runtime::cuda;
+
+// The reference's prompt path calls into its vendored FlashAttention translation unit, which is not
+// part of this build (it needs CUTLASS); nothing here reaches that call.  Defined so that the
+// library loads.
+namespace expert::runtime::cuda {
+Status flash_gqa_segment_bf16(const FlashGqaSegmentLaunch&) noexcept {
+  return Status(ErrorCode::invalid_argument, "flash attention is not part of the reference-kernel shim");
+}
+}  // namespace expert::runtime::cuda
 
 namespace {
 thread_local std::string g_error;

@@ -61,7 +61,7 @@ int qllm_k_nvfp4_gemv(const qllm_matrix* m, uint32_t first_row, uint32_t row_cou
     MmaWeights w;
     int rc = w.prepare(*m, s);
     if (rc) return rc;
-    if (!w.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+    if (!w.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64)");
     rc = check_cuda(cudaMemsetAsync(workspace, 0, sizeof(uint32_t), s), "clear GEMV status word");
     if (rc) return rc;
     rc = launch_gemv_mma(w, *m, first_row, row_count, x, y, batch, workspace, workspace_bytes, s);
@@ -109,14 +109,14 @@ int qllm_k_nvfp4_gemv_prepared(const qllm_prepared_matrix* p, const float* x, fl
     if (rc) return rc;
     return launch_gemv_simt(p->m, 0U, p->m.rows, workspace, batch, y, batch, s);
   }
-  if (impl != 1 || !p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+  if (impl != 1 || !p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64)");
   return launch_gemv_mma(p->mma, p->m, 0U, p->m.rows, x, y, batch, workspace, workspace_bytes, s);
 }
 
 int qllm_k_nvfp4_gemv_prepared_core(const qllm_prepared_matrix* p, uint32_t batch, void* workspace,
                                     size_t workspace_bytes, void* stream) {
   if (!p || !workspace || !batch) return fail(QLLM_INVALID_ARGUMENT, "invalid native NVFP4 GEMV");
-  if (!p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+  if (!p->mma.ready) return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64)");
   return launch_gemv_mma_core_only(p->mma, p->m, batch, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 

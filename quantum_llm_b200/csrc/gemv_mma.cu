@@ -41,6 +41,10 @@ using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, 
                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                  CUtensorMapFloatOOBfill);
 
+// scale atoms (64 k values each) of a row tile, padded to whole 256-wide pipeline stages
+__host__ __device__ inline uint32_t padded_atoms(uint32_t cols) { return (cols + kTileK - 1U) / kTileK * (kTileK / 64U); }
+inline uint32_t k_chunks_of(uint32_t cols) { return (cols + kTileK - 1U) / kTileK; }
+
 EncodeTiled encode_tiled() {
   static EncodeTiled fn = nullptr;
   static std::once_flag once;
@@ -101,8 +105,11 @@ int MmaWeights::prepare(const qllm_matrix& m, cudaStream_t stream) {
   release();
   rows = m.rows;
   cols = m.cols;
-  if (m.cols % kTileK) return 0;  // shape outside the tensor-core path; the CUDA-core kernel serves it
-  const uint32_t blocks = m.cols / 16U, k_atoms = m.cols / 64U;
+  if (m.cols % 64U) return 0;  // shape outside the tensor-core path; the CUDA-core kernel serves it
+  // K need not be a multiple of the 256-wide pipeline stage (a tensor-parallel K slice): the
+  // re-tiled scales are padded with zeros to whole stages, the codes' last box is filled with
+  // zeros by the TMA unit, and the kernel issues only the 64-wide MMAs that lie inside K
+  const uint32_t blocks = m.cols / 16U, k_atoms = padded_atoms(m.cols);
   const uint32_t row_tiles = (m.rows + kTileRows - 1U) / kTileRows;
   const size_t bytes = static_cast<size_t>(row_tiles) * k_atoms * kAtomBytes;
   int rc = check_cuda(cudaMalloc(&tiled_scales, bytes), "re-tiled scale allocation");
@@ -171,7 +178,7 @@ static MmaWorkspace carve(void* workspace, uint32_t batch, uint32_t rows, uint32
   w.codes = base + off;
   off += align_up(static_cast<size_t>(w.n_tiles) * 128U * (cols / 2U), 1024);
   w.atoms = base + off;
-  off += align_up(static_cast<size_t>(w.n_tiles) * (cols / 64U) * kAtomBytes, 1024);
+  off += align_up(static_cast<size_t>(w.n_tiles) * padded_atoms(cols) * kAtomBytes, 1024);
   w.partials = reinterpret_cast<float*>(base + off);
   off += align_up(static_cast<size_t>(split) * batch * rows * sizeof(float), 1024);
   if (total) *total = off;
@@ -179,11 +186,11 @@ static MmaWorkspace carve(void* workspace, uint32_t batch, uint32_t rows, uint32
 }
 
 size_t gemv_mma_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols) {
-  if (cols % kTileK) return 0;
+  if (cols % 64U) return 0;
   size_t total = 0;
   const uint32_t row_tiles = (rows + kTileRows - 1U) / kTileRows;
   // the split depends on n_tiles only through its product with row_tiles; size for the worst case
-  const uint32_t split = pick_split(row_tiles, 1U, cols / kTileK);
+  const uint32_t split = pick_split(row_tiles, 1U, k_chunks_of(cols));
   carve(nullptr, batch, rows, cols, split, &total);
   return total;
 }
@@ -221,8 +228,8 @@ __global__ void act_quant_mma_kernel(const float* __restrict__ x, uint8_t* __res
   }
   reinterpret_cast<uint2*>(codes + static_cast<size_t>(m) * (cols / 2U))[b] = make_uint2(packed[0], packed[1]);
   const uint32_t tile = m / 128U, r = m % 128U;
-  atoms[(static_cast<size_t>(tile) * (cols / 64U) + b / 4U) * kAtomBytes + (r % 32U) * 16U + (r / 32U) * 4U + b % 4U] =
-      static_cast<uint8_t>(sc);
+  atoms[(static_cast<size_t>(tile) * padded_atoms(cols) + b / 4U) * kAtomBytes + (r % 32U) * 16U + (r / 32U) * 4U +
+        b % 4U] = static_cast<uint8_t>(sc);
 }
 
 // ------------------------------------------------------------------ PTX helpers
@@ -294,7 +301,8 @@ struct GemvMmaParams {
   float* y;                     // [batch][row_count]
   uint32_t* error;
   uint32_t first_tile, row_count, batch, n_pad;
-  uint32_t k_chunks, k_atoms, split, stages;
+  uint32_t k_chunks, k_atoms, split, stages;  // k_atoms: atoms per row tile in memory (whole stages)
+  uint32_t k_valid;             // 64-wide k groups that lie inside K (the last stage may be partial)
   uint32_t raw;                 // 1: always write raw partials (the consumer applies the scale)
   float weight_scale, input_scale;
 };
@@ -406,8 +414,10 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                      "l"(umma_desc_sf(sfb + kb * kAtomBytes))
                      : "memory");
       }
+      const uint32_t groups = min(4U, p.k_valid - (kc0 + i) * 4U);  // beyond K: zero-filled codes, not issued
 #pragma unroll
       for (uint32_t kb = 0; kb < 4U; ++kb) {
+        if (kb >= groups) break;
         const uint64_t adesc = umma_desc_sw128(st + kb * 32U);
         const uint64_t bdesc = umma_desc_sw128(b + kb * 32U);
         const uint32_t accumulate = (i > 0U || kb > 0U) ? 1U : 0U;
@@ -521,11 +531,11 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream) {
-  if (!w.ready || m.cols % kTileK || first_row % kTileRows || !batch || !row_count || row_count > m.rows ||
-      first_row > m.rows - row_count)
-    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, first row % 128)");
+  if (!w.ready || m.cols % 64U || first_row % kTileRows || !batch || !row_count || row_count > m.rows ||
+      first_row > m.rows - row_count || (m.cols % kTileK && batch > 128U))
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64, first row % 128)");
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
-  const uint32_t k_chunks = m.cols / kTileK;
+  const uint32_t k_chunks = k_chunks_of(m.cols);
   const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
   const uint32_t split = pick_split(row_tiles, n_tiles, k_chunks);
   size_t need = 0;
@@ -555,11 +565,11 @@ int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_ro
 // the same workspace, matrix and batch left behind; leaves split-K partials in the workspace.
 int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_t batch, void* workspace,
                               size_t workspace_bytes, cudaStream_t stream) {
-  if (!w.ready || m.cols % kTileK || !batch)
-    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256)");
+  if (!w.ready || m.cols % 64U || !batch || (m.cols % kTileK && batch > 128U))
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64)");
   const uint32_t row_tiles = (m.rows + kTileRows - 1U) / kTileRows;
   const uint32_t n_tiles = ((batch + 15U) / 16U * 16U + 127U) / 128U;  // 128 activation rows per CTA
-  const uint32_t split = pick_split(row_tiles, n_tiles, m.cols / kTileK);
+  const uint32_t split = pick_split(row_tiles, n_tiles, k_chunks_of(m.cols));
   size_t need = 0;
   const MmaWorkspace ws = carve(workspace, batch, m.rows, m.cols, split, &need);
   if (need > workspace_bytes) return fail(QLLM_INVALID_ARGUMENT, "tensor-core GEMV workspace is too small");
@@ -572,7 +582,7 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
              uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange) {
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
-  const uint32_t k_chunks = m.cols / kTileK;
+  const uint32_t k_chunks = k_chunks_of(m.cols);
   const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
   const uint32_t split = pick_split(row_tiles, n_tiles, k_chunks);
   if (split_out) *split_out = split;
@@ -620,7 +630,8 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.batch = batch;
   p.n_pad = n_pad;
   p.k_chunks = k_chunks;
-  p.k_atoms = m.cols / 64U;
+  p.k_atoms = padded_atoms(m.cols);
+  p.k_valid = m.cols / 64U;
   p.split = split;
   p.stages = stages;
   p.raw = raw ? 1U : 0U;
@@ -637,8 +648,9 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
 // ---- operand buffers and the implementation-neutral GEMV core ---------------------------
 size_t quant_buffer_bytes(uint32_t max_rows, uint32_t max_cols) {
   const size_t simt = act_quant_bytes(max_rows, max_cols);
+  // the atoms of a partial last stage are read (never used) up to the end of that stage
   const size_t mma = align_up(static_cast<size_t>(128U) * (max_cols / 2U), 1024) +
-                     align_up(static_cast<size_t>(max_cols / 64U + 1U) * kAtomBytes, 1024);
+                     align_up(static_cast<size_t>(padded_atoms(max_cols) + 4U) * kAtomBytes, 1024);
   return std::max(simt, mma) + 1024U;
 }
 
@@ -660,9 +672,9 @@ QuantSink make_sink(int gemv_impl, void* quant_buffer, uint32_t rows, uint32_t c
 }
 
 size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
-  if (cols % kTileK) return static_cast<size_t>(batch) * rows;
+  if (cols % 64U) return static_cast<size_t>(batch) * rows;
   const uint32_t row_tiles = (rows + kTileRows - 1U) / kTileRows;
-  return static_cast<size_t>(pick_split(row_tiles, 1U, cols / kTileK)) * batch * rows;
+  return static_cast<size_t>(pick_split(row_tiles, 1U, k_chunks_of(cols))) * batch * rows;
 }
 
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
@@ -690,7 +702,7 @@ int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, u
   }
   if (exchange) return fail(QLLM_INVALID_ARGUMENT, "the tensor-parallel exchange needs the tensor-core GEMV");
   if (gemv_impl == 1)
-    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 256, first row % 128, rows <= 128)");
+    return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64, first row % 128, rows <= 128)");
   const int rc = launch_gemv_simt(m, first_row, row_count, quant_buffer, batch, final_out, batch, stream);
   out->data = final_out;
   out->split = 0U;

@@ -159,6 +159,7 @@ struct qllm_provider {
   uint8_t* tp_area = nullptr;                  // this rank's area (cudaMalloc, exported to the peers)
   uint8_t* tp_peer[8] = {};                    // every rank's area as mapped here (own = tp_area)
   bool tp_attached = false;
+  bool tp_local = false;                       // peers' areas are plain device pointers (not IPC mappings)
   size_t tp_slot_pairs = 0;
   GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down)
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
@@ -321,7 +322,7 @@ struct qllm_provider {
 
   ~qllm_provider() {
     for (uint32_t r = 0; r < tp_ranks; ++r)
-      if (tp_peer[r] && tp_peer[r] != tp_area) cudaIpcCloseMemHandle(tp_peer[r]);
+      if (tp_peer[r] && tp_peer[r] != tp_area && !tp_local) cudaIpcCloseMemHandle(tp_peer[r]);
     if (tp_area) cudaFree(tp_area);
     for (void* p : owned) cudaFree(p);
     if (stream) cudaStreamDestroy(stream);
@@ -1019,6 +1020,27 @@ int qllm_provider_tp_attach(qllm_provider* p, const void* handles) {
   });
 }
 
+size_t qllm_provider_tp_area_bytes(const qllm_provider* p) {
+  return p && p->tp_area ? 2U * static_cast<size_t>(p->tp_ranks) * p->tp_slot_pairs * sizeof(uint2) : 0U;
+}
+
+// Exchange areas that are addressable from this process already (one process driving several GPUs
+// with peer access enabled): device pointers instead of inter-process handles.
+int qllm_provider_tp_attach_local(qllm_provider* p, void* const* areas) {
+  if (!p || !areas || !p->tp_area) return fail(QLLM_INVALID_ARGUMENT, "call qllm_provider_tp_export first");
+  if (p->tp_attached) return fail(QLLM_INVALID_ARGUMENT, "the exchange areas of this provider are attached already");
+  for (uint32_t r = 0; r < p->tp_ranks; ++r) {
+    if (r == p->tp_rank) continue;
+    if (!areas[r] || (reinterpret_cast<uintptr_t>(areas[r]) & 15U))
+      return fail(QLLM_INVALID_ARGUMENT, "a peer's exchange area is missing or not 16-byte aligned");
+  }
+  for (uint32_t r = 0; r < p->tp_ranks; ++r)
+    if (r != p->tp_rank) p->tp_peer[r] = static_cast<uint8_t*>(areas[r]);
+  p->tp_local = true;
+  p->tp_describe();
+  return QLLM_OK;
+}
+
 int qllm_provider_set_attention_impl(qllm_provider* p, int impl) {
   if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown attention implementation");
   p->attention_impl = impl;
@@ -1056,6 +1078,63 @@ int qllm_provider_read_drafts(qllm_provider* p, qllm_request_state* st, uint32_t
     for (uint32_t i = 0; i < host.draft_count && i < 4U; ++i) tokens[i] = host.verify_tokens[i + 1U];
   });
 }
+// Measurement aid: the verify pass alone (target forward over the pending guaranteed token and
+// drafts, head, candidate selection), `repeats` times back to back, timed with CUDA events on the
+// provider's stream.  It recomputes what the next step computes anyway (same inputs, same cache
+// slots), so the request can go on decoding afterwards.
+int qllm_provider_time_verify(qllm_provider* p, qllm_request_state* st, const qllm_request* rq, uint32_t repeats,
+                              float* mean_ms) {
+  if (!p || !st || !rq || !mean_ms || !repeats) return fail(QLLM_INVALID_ARGUMENT, "null verify-timing argument");
+  return guarded([&] {
+    std::lock_guard<std::mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    const auto& c = p->cfg;
+    if (!st->draft_valid) throw Error(QLLM_INVALID_ARGUMENT, "no drafts are pending: nothing to verify");
+    p->bind_request(*st, *rq);
+    const bool sampled = rq->sampling_temperature_ppm != 0U;
+    const uint32_t R = c.draft_depth + 1U;
+    const uint32_t splits = p->splits_for(st->mtp_length + 33U * R);
+    auto enqueue = [&] {
+      p->run_target(*st, st->state->verify_tokens, R, &st->state->position, splits, true);
+      p->select_candidates(p->logits.p, R, c.vocab, c.vocab, sampled, rq->sampling_top_k);
+    };
+    cudaGraphExec_t exec = nullptr;
+    if (p->graph_mode) {
+      cudaGraph_t graph = nullptr;
+      cu(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeThreadLocal), "begin verify capture");
+      try {
+        enqueue();
+      } catch (...) {
+        cudaStreamEndCapture(p->stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        throw;
+      }
+      cu(cudaStreamEndCapture(p->stream, &graph), "end verify capture");
+      const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+      cudaGraphDestroy(graph);
+      cu(e, "instantiate verify graph");
+    }
+    cudaEvent_t a = nullptr, b = nullptr;
+    cu(cudaEventCreate(&a), "event");
+    cu(cudaEventCreate(&b), "event");
+    auto run = [&] {
+      if (exec) cu(cudaGraphLaunch(exec, p->stream), "launch verify graph");
+      else enqueue();
+    };
+    run();  // warm-up
+    cu(cudaEventRecord(a, p->stream), "event record");
+    for (uint32_t i = 0; i < repeats; ++i) run();
+    cu(cudaEventRecord(b, p->stream), "event record");
+    cu(cudaStreamSynchronize(p->stream), "verify timing");
+    float ms = 0.0F;
+    cu(cudaEventElapsedTime(&ms, a, b), "event time");
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    if (exec) cudaGraphExecDestroy(exec);
+    *mean_ms = ms / static_cast<float>(repeats);
+  });
+}
+
 size_t qllm_provider_page_bytes(qllm_provider* p) { return p ? p->page_bytes : 0; }
 size_t qllm_provider_layer_offset(qllm_provider* p, uint32_t layer) {
   return p && layer < p->layer_off.size() ? p->layer_off[layer] : 0;

@@ -107,6 +107,8 @@ SIGNATURES = {
     "qllm_descriptor_dump": (sz, [vp, vp, sz]),
     "qllm_provider_tp_export": (ci, [vp, u32, u32, vp]),
     "qllm_provider_tp_attach": (ci, [vp, vp]),
+    "qllm_provider_tp_area_bytes": (sz, [vp]),
+    "qllm_provider_tp_attach_local": (ci, [vp, vp]),
     "qllm_provider_read_logits": (ci, [vp, vp, u32]),
     "qllm_provider_read_hidden": (ci, [vp, vp, ci, vp, u32]),
     "qllm_provider_read_drafts": (ci, [vp, vp, vp, P(u32)]),
@@ -114,6 +116,7 @@ SIGNATURES = {
     "qllm_provider_layer_offset": (sz, [vp, u32]),
     "qllm_provider_read_page": (ci, [vp, vp, u32, vp]),
     "qllm_provider_fill_synthetic_kv": (ci, [vp, vp, u32, u32, u64]),
+    "qllm_provider_time_verify": (ci, [vp, vp, P(Request), u32, P(f32)]),
     "qllm_k_embedding_bf16": (ci, [vp, vp, vp, u32, u32, u32, vp]),
     "qllm_k_rms_norm": (ci, [vp, vp, vp, u32, u32, f32, vp]),
     "qllm_k_nvfp4_fake_quant": (ci, [vp, vp, u32, u32, f32, vp]),

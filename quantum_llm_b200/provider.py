@@ -176,6 +176,14 @@ class Nvfp4MtpProvider:
         buffer = C.create_string_buffer(bytes(handles), len(handles))
         _l.check(self.L.qllm_provider_tp_attach(self.h, buffer))
 
+    def tp_area_bytes(self):
+        return int(self.L.qllm_provider_tp_area_bytes(self.h))
+
+    def tp_attach_local(self, areas):
+        """`areas[r]`: device pointer of rank r's exchange area (one process driving all GPUs)."""
+        table = (C.c_void_p * len(areas))(*[C.c_void_p(a) for a in areas])
+        _l.check(self.L.qllm_provider_tp_attach_local(self.h, table))
+
     def set_gemv_impl(self, impl):
         _l.check(self.L.qllm_provider_set_gemv_impl(self.h, int(impl)))
 
@@ -211,6 +219,13 @@ class Nvfp4MtpProvider:
         out = np.empty(self.page_bytes(), np.uint8)
         _l.check(self.L.qllm_provider_read_page(self.h, state.h, page, out.ctypes.data))
         return out
+
+    def time_verify(self, state, request, repeats=8):
+        """Mean duration (ms, CUDA events) of the verify pass alone over the pending drafts."""
+        ms = C.c_float(0.0)
+        rq = request.c()
+        _l.check(self.L.qllm_provider_time_verify(self.h, state.h, C.byref(rq), repeats, C.byref(ms)))
+        return ms.value
 
     def fill_synthetic_kv(self, state, first, count, seed):
         _l.check(self.L.qllm_provider_fill_synthetic_kv(self.h, state.h, first, count, seed))

@@ -199,6 +199,33 @@ class DeviceModel:
         return Nvfp4MtpProvider(self.config(), w, weights_on_device=True, device=self.device.index or 0,
                                 keepalive=(self, blocks))
 
+    def echo_variant(self):
+        """The same weights as a model whose drafts can be right (dense, unsharded): the attention
+        and FFN output projections are scaled to almost nothing, so the next token is a function of
+        the current token alone, and the fusion matrix passes the normalised embedding through,
+        so the draft block sees what the target saw.  Shares every weight tensor with `self`
+        (only the per-tensor multipliers of o / down and the fusion matrix differ)."""
+        import copy
+        assert self.tp is None and not self.cfg.get("experts", 0)
+        m = copy.copy(self)
+
+        def quiet(block):
+            b = copy.copy(block)
+            b.m = dict(block.m)
+            for name in ("o", "down"):
+                src = block.m[name]
+                b.m[name] = DeviceMatrix(src.codes, src.scales, src.weight_scale * 1e-4, src.rows, src.cols)
+            return b
+
+        m.layers = [quiet(b) for b in self.layers]
+        m.mtp_block = quiet(self.mtp_block)
+        H = self.cfg["hidden"]
+        with torch.cuda.device(self.device):
+            fusion = torch.zeros((H, 2 * H), dtype=torch.float32, device=self.device)
+            fusion[torch.arange(H), torch.arange(H)] = 1.0
+            m.mtp_fusion = quantize(fusion)
+        return m
+
     def tensor_parallel_provider(self, group=None):
         """Provider of this rank's shard with the exchange areas of all ranks attached: the
         inter-process handles travel through `torch.distributed` (all-gather over `group`)."""

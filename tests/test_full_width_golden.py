@@ -1,0 +1,149 @@
+"""The benchmarked kernels against the CPU oracle at the benchmark's own widths.
+
+tests/golden/full_width_<case>.npz holds the oracle's run (tests/golden/make_full_width_golden.py)
+over the two-layer full-width models of tests/full_width.py: 320 prompt tokens, six greedy
+speculative steps.  Here the CUDA provider decodes the same model through the C ABI, twice:
+
+* exact path (CUDA-core GEMV with integer block arithmetic, order-independent attention): every
+  stored quantity must be IDENTICAL -- first token, drafts, emitted tokens, the 64 largest logits
+  of each verify row (ids and values), the strided logit samples, and the SHA-256 of every cache
+  page's committed positions (Q4H target records and Q8 draft records);
+* benchmarked path (tcgen05 GEMV, tensor-core attention, the step replayed from its CUDA graph):
+  every verify row whose inputs are tokens both sides agree on stays within the stated tolerance
+  of the oracle's row -- 2e-2 max-abs, 1e-3 relative RMS -- and the emitted tokens follow the
+  oracle's until a row where the two best logits are closer than that tolerance.
+
+echo27b is the model whose drafts can be right: acceptance lengths 1..4, rollback after a partial
+accept and the bonus token run on the tensor-core kernels, and must match the oracle's counts.
+"""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+
+from tests import full_width as fw
+from tests.gpu_util import provider_from_synth, request_pair
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, REL_RMS = 2e-2, 1e-3
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _decode(model, case, gemv_impl, attention_impl, graph):
+    cfg = model.cfg
+    prq, _ = request_pair(context_limit=cfg["max_context"])
+    p = provider_from_synth(model)
+    p.set_gemv_impl(gemv_impl)
+    p.set_attention_impl(attention_impl)
+    p.set_graph_mode(graph)
+    st = p.create_request_state()
+    prompt = fw.prompt(case)
+    first = p.prefill(st, prq, prompt, chunk_rows=8)
+    run = dict(first=first, initial_drafts=[int(t) for t in p.read_drafts(st)], steps=[], provider=p, state=st)
+    position, token = len(prompt), first
+    for _ in range(fw.STEPS):
+        r = p.execute_exact_decode(st, prq, token, position, cfg["max_context"])
+        logits = p.read_logits(5)
+        run["steps"].append(dict(emitted=list(r.emitted_tokens), next=r.next_token, logits=logits.copy(),
+                                 drafts=[int(t) for t in p.read_drafts(st)]))
+        position += r.positions_advanced
+        token = r.next_token
+    run["position"] = position
+    return run
+
+
+def _fixture_step(g, i):
+    n = int(g["emitted_count"][i])
+    return [int(t) for t in g["emitted"][i][:n]], int(g["next_token"][i]), [int(t) for t in g["drafts"][i]]
+
+
+@pytest.fixture(scope="module", params=list(fw.CASES))
+def built(request):
+    case = request.param
+    path = os.path.join(GOLDEN, f"full_width_{case}.npz")
+    g = np.load(path)
+    model, digest = fw.build(case)
+    assert digest == bytes(g["weights_sha256"]).hex(), \
+        "this host drew other weights than the fixture's generator (numpy version?): regenerate the fixture"
+    assert hashlib.sha256(fw.prompt(case).tobytes()).digest() == bytes(g["prompt_sha256"])
+    return case, model, g
+
+
+def test_exact_path_equals_the_oracle_bit_for_bit(built):
+    case, model, g = built
+    run = _decode(model, case, gemv_impl=0, attention_impl=0, graph=False)
+    assert run["first"] == int(g["first_token"])
+    assert run["initial_drafts"] == [int(t) for t in g["initial_drafts"]]
+    accepted = 0
+    for i, s in enumerate(run["steps"]):
+        emitted, nxt, drafts = _fixture_step(g, i)
+        assert s["emitted"] == emitted and s["next"] == nxt, f"step {i}"
+        assert s["drafts"] == drafts[:len(s["drafts"])], f"drafts after step {i}"
+        accepted += len(emitted) - 1
+        for r in range(5):
+            ids, values, sample = fw.row_summary(s["logits"][r])
+            assert np.array_equal(ids, g["top_ids"][i][r]) and np.array_equal(values, g["top_values"][i][r]), (i, r)
+            assert np.array_equal(sample, g["samples"][i][r]), (i, r)
+    p, st = run["provider"], run["state"]
+    assert run["position"] == int(g["committed"])
+    offsets = [p.layer_offset(l) for l in range(model.cfg["layers"] + 1)]
+    for page, want in enumerate(g["page_sha256"]):
+        got = fw.committed_page_bytes(p.read_page(st, page), model.cfg, offsets, page, run["position"])
+        assert hashlib.sha256(got.tobytes()).digest() == bytes(want), f"cache page {page}"
+    t = p.telemetry(st)
+    assert t["accepted_drafts"] == accepted
+    if case == "echo27b":
+        assert accepted > 0
+
+
+def test_benchmarked_path_stays_within_the_stated_tolerance_of_the_oracle(built):
+    case, model, g = built
+    run = _decode(model, case, gemv_impl=1, attention_impl=1, graph=True)
+    assert run["first"] == int(g["first_token"])
+    verify_gpu = [run["first"]] + run["initial_drafts"]
+    verify_cpu = [int(g["first_token"])] + [int(t) for t in g["initial_drafts"]]
+    rows, worst_abs, worst_rms, accepted, followed = 0, 0.0, 0.0, 0, 0
+    report = []
+    for i, s in enumerate(run["steps"]):
+        emitted, nxt, drafts = _fixture_step(g, i)
+        same_inputs = 0
+        while same_inputs < min(len(verify_gpu), len(verify_cpu), 5) and verify_gpu[same_inputs] == verify_cpu[same_inputs]:
+            same_inputs += 1
+        for r in range(same_inputs):
+            got = s["logits"][r]
+            d_top = np.abs(got[g["top_ids"][i][r]] - g["top_values"][i][r]).max()
+            want = g["samples"][i][r]
+            diff = got[::fw.SAMPLE_STRIDE] - want
+            d_abs = max(float(d_top), float(np.abs(diff).max()))
+            d_rms = float(np.sqrt((diff.astype(np.float64) ** 2).mean()) / np.sqrt((want.astype(np.float64) ** 2).mean()))
+            report.append((i, r, round(d_abs, 5), round(d_rms, 6)))
+            worst_abs, worst_rms, rows = max(worst_abs, d_abs), max(worst_rms, d_rms), rows + 1
+        accepted += len(s["emitted"]) - 1
+        if s["emitted"] != emitted or s["next"] != nxt:
+            # the streams part: it must be at a row whose two candidates are within the tolerance
+            k = 0
+            while k < min(len(emitted), len(s["emitted"])) and emitted[k] == s["emitted"][k]:
+                k += 1
+            row = min(k, 4) if k < len(emitted) else len(emitted) - 1
+            ours = s["emitted"][k] if k < len(s["emitted"]) else s["next"]
+            theirs = emitted[k] if k < len(emitted) else nxt
+            if row < same_inputs and ours != theirs:
+                top_ids, top_values = g["top_ids"][i][row], g["top_values"][i][row]
+                if ours in top_ids:
+                    gap = float(top_values[0] - top_values[list(top_ids).index(ours)])
+                    assert gap <= 2 * MAX_ABS, f"step {i}: streams part at a row with a clear winner (gap {gap})"
+            break
+        followed += 1
+        verify_gpu = [s["next"]] + s["drafts"]
+        verify_cpu = [nxt] + drafts
+    print(f"\n[{case}] benchmarked path vs oracle: {rows} rows compared, worst max-abs {worst_abs:.5f}, "
+          f"worst relative RMS {worst_rms:.6f}, steps followed {followed}/{fw.STEPS}, accepted drafts {accepted}")
+    print("   rows (step, row, max-abs, rel-rms):", report)
+    assert rows >= 5
+    assert worst_abs <= MAX_ABS and worst_rms <= REL_RMS, report
+    if case == "echo27b":
+        t = run["provider"].telemetry(run["state"])
+        assert t["accepted_drafts"] == accepted and accepted > 0
+        assert any(d > 0 for d in t["accepted_depth_calls"][1:])

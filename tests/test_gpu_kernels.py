@@ -72,7 +72,8 @@ def _assert_gemv(got, want, impl):
 
 @pytest.mark.parametrize("impl", [0, 1])
 @pytest.mark.parametrize("rows,cols,batch", [(256, 256, 5), (1024, 1024, 5), (384, 2048, 1), (4096, 512, 8), (640, 1024, 40),
-                                             (640, 1024, 160), (256, 512, 640)])
+                                             (640, 1024, 160), (256, 512, 640),
+                                             (256, 640, 5), (384, 2176, 5), (128, 192, 3)])   # K that is not a whole number of 256-wide stages
 def test_nvfp4_gemv_matches_oracle(L, impl, rows, cols, batch):
     import torch
     from quantum_llm_b200 import lib

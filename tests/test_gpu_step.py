@@ -88,14 +88,14 @@ def compare(gpu, cpu, prompt_len):
 def test_tiny_greedy_tokens_and_logits(graph):
     model = synth.SynthModel(synth.TINY, seed=0)
     prompt = synth.prompt(4096, 128, 0)
-    gpu = run_gpu(model, prompt, 0, 64, graph=graph)
+    # exact path (CUDA-core GEMV, order-independent attention): the same bits as the oracle
+    gpu = run_gpu(model, prompt, 0, 64, graph=graph, attention_impl=0)
     cpu = run_cpu(model, prompt, 0, 64)
     c = compare(gpu, cpu, len(prompt))
     print("greedy parity", c, "drafts", gpu["drafts"], cpu["drafts"])
-    assert gpu["stream"][0] == cpu["stream"][0]
-    assert c["shared"] >= 16 and c["good"] >= 0.9 * c["shared"]
-    if c["prefix"] < 65:
-        assert c["tie"] is not False or c["good"] < c["shared"], "streams differ without a tie or a threshold event"
+    assert gpu["stream"] == cpu["stream"] and gpu["drafts"] == cpu["drafts"]
+    assert gpu["steps"] == cpu["steps"] and gpu["accepted"] == cpu["accepted"]
+    assert c["shared"] >= 64 and c["exact"] == c["shared"]
     t = gpu["provider"].telemetry(gpu["state"])
     assert t["exact_calls"] == gpu["steps"] and t["kernel_launches"] > 0
 
@@ -179,53 +179,56 @@ def test_greedy_stream_equals_plain_target_decoding_on_gpu():
 def test_tiny_kv_pages_match_the_oracle():
     model = synth.SynthModel(synth.TINY, seed=0)
     prompt = synth.prompt(4096, 128, 0)
-    gpu = run_gpu(model, prompt, 0, 4)
+    gpu = run_gpu(model, prompt, 0, 4, attention_impl=0)
     cpu = run_cpu(model, prompt, 0, 4)
     p, st, o = gpu["provider"], gpu["state"], cpu["oracle"]
     assert p.page_bytes() >= o.page(0).size
     for layer in range(3):
         assert p.layer_offset(layer) == o.layer_offset(layer)
-    cfg = model.cfg
-    pt, kv, hd = cfg["page_tokens"], cfg["kv_heads"], cfg["head_dim"]
-    same, total = 0, 0
-    for page in range(2):   # 128 prompt tokens = two 64-token pages
-        g = p.read_page(st, page)[:o.page(page).size]
-        c = o.page(page)
-        lo, hi = o.layer_offset(0), o.layer_offset(1)
-        # first layer: inputs are identical on both sides -> records are byte-identical
-        assert np.array_equal(g[lo:hi], c[lo:hi]) or (g[lo:hi] != c[lo:hi]).mean() < 1e-3
-        # later layers: identical except rows hit by a quantisation-threshold event upstream
-        for layer in (1, 2):
-            lo, hi = o.layer_offset(layer), (o.layer_offset(layer + 1) if layer < 2 else o.page(page).size)
-            width = (hi - lo) // (2 * pt)
-            gr = g[lo:hi].reshape(2, pt, width)
-            cr = c[lo:hi].reshape(2, pt, width)
-            eq = (gr == cr).all(axis=(0, 2))
-            same += int(eq.sum())
-            total += pt
-    print("identical KV token records in layers 1..2:", same, "of", total)
-    assert same >= 0.5 * total
+    # exact path: every record of every layer (F16 target layers, Q8 draft layer) byte for byte --
+    # the two prompt pages whole, and of the page the decode steps reach every committed position
+    # (slots past the accepted prefix hold speculative rows that are overwritten before any read;
+    # the provider also stores the padding rows of its fixed-width draft pass there)
+    committed = o.mtp_length
+    pt = model.cfg["page_tokens"]
+    for page in range(3):
+        want = o.page(page)
+        got = p.read_page(st, page)[:want.size]
+        if (page + 1) * pt <= committed:
+            assert np.array_equal(got, want), f"cache page {page}"
+            continue
+        tokens = committed - page * pt
+        assert tokens > 0
+        for layer in range(3):   # F16 and Q8 layers are token-major: [K: pt records][V: pt records]
+            lo = o.layer_offset(layer)
+            hi = o.layer_offset(layer + 1) if layer < 2 else want.size
+            half = (hi - lo) // 2
+            n = half // pt * tokens
+            for base in (lo, lo + half):
+                assert np.array_equal(got[base:base + n], want[base:base + n]), f"page {page} layer {layer}"
 
 
 def test_tiny_sampled_decisions():
     model = synth.SynthModel(synth.TINY, seed=0)
     prompt = synth.prompt(4096, 128, 0)
-    gpu = run_gpu(model, prompt, 700000, 48, seed=77)
+    gpu = run_gpu(model, prompt, 700000, 48, seed=77, attention_impl=0)
     cpu = run_cpu(model, prompt, 700000, 48, seed=77)
     c = compare(gpu, cpu, len(prompt))
     print("sampled parity", c)
+    # exact path: the same accept / reject / residual decisions, the same rows
+    assert gpu["stream"] == cpu["stream"] and gpu["accepted"] == cpu["accepted"] and c["exact"] == c["shared"]
     # every emitted token must come from the top-k support of the row that chose it
     for pos, row in gpu["rows"].items():
         tok = gpu["stream"][pos + 1 - len(prompt)]
         assert (row > row[tok]).sum() < 20
-    assert c["shared"] >= 1 and c["good"] >= 0.9 * c["shared"]
+    assert c["shared"] >= 16
 
 
 @pytest.mark.parametrize("temperature", [0, 700000])
 def test_echo_model_acceptance_lengths(temperature):
     model = echo_model()
     prompt = synth.prompt(4096, 64, 5)
-    gpu = run_gpu(model, prompt, temperature, 48, graph=True)
+    gpu = run_gpu(model, prompt, temperature, 48, graph=True, attention_impl=0)
     cpu = run_cpu(model, prompt, temperature, 48)
     c = compare(gpu, cpu, len(prompt))
     print("echo parity", c, "accepted gpu/cpu", gpu["accepted"], cpu["accepted"], "steps", gpu["steps"], cpu["steps"])
@@ -233,8 +236,9 @@ def test_echo_model_acceptance_lengths(temperature):
     assert gpu["steps"] < 48
     t = gpu["provider"].telemetry(gpu["state"])
     assert t["accepted_drafts"] == gpu["accepted"] and sum(t["accepted_depth_calls"]) == gpu["steps"]
-    if c["prefix"] >= 49:
-        assert gpu["accepted"] == cpu["accepted"] or temperature != 0
+    # exact path: the same acceptance lengths, partial accepts and bonus tokens as the oracle
+    assert gpu["stream"] == cpu["stream"] and gpu["steps"] == cpu["steps"] and gpu["accepted"] == cpu["accepted"]
+    assert c["exact"] == c["shared"]
 
 
 def test_multi_step_enqueue_equals_single_steps():

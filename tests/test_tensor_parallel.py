@@ -150,6 +150,36 @@ def test_single_rank_exchange_equals_the_plain_path():
 
 
 @pytest.mark.gpu
+def test_a_peer_that_never_delivers_ends_the_step_with_an_error_not_a_hang():
+    # two ranks, one GPU: the "peer" is a zeroed buffer that nobody writes, so the consumer of the
+    # first exchange polls until its limit (about a second), sets the kernel error word and every
+    # later wait gives up at once.  The step reports QLLM_INTERNAL; the context stays usable.
+    import time
+    import torch
+    from quantum_llm_b200.lib import QllmError
+    from tests.gpu_util import provider_from_synth, request_pair
+    model = synth.SynthModel(TP_MODEL, seed=3)
+    p = provider_from_synth(synth.shard_model(model, 0, 2))
+    p.set_gemv_impl(1)
+    p.tp_export(0, 2)
+    silent = torch.zeros(p.tp_area_bytes(), dtype=torch.uint8, device="cuda")
+    p.tp_attach_local([0, silent.data_ptr()])
+    prq, _ = request_pair(context_limit=model.cfg["max_context"])
+    st = p.create_request_state()
+    t0 = time.time()
+    with pytest.raises(QllmError) as failure:
+        p.prefill(st, prq, synth.prompt(model.cfg["vocab"], *TP_PROMPT), chunk_rows=5)
+    assert time.time() - t0 < 60.0
+    assert "device" in str(failure.value) or "failed" in str(failure.value)
+    # the device still answers: a plain provider on the same GPU decodes as usual
+    torch.cuda.synchronize()
+    plain = provider_from_synth(model)
+    plain.set_gemv_impl(1)
+    stream, _, _ = _decode(plain, model, 4)
+    assert len(stream) == 5
+
+
+@pytest.mark.gpu
 def test_exchange_needs_the_tensor_core_gemv_and_an_attached_area():
     from quantum_llm_b200.lib import QllmError
     from tests.gpu_util import provider_from_synth
