@@ -67,6 +67,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemv-impl", type=int, default=int(os.environ.get("QLLM_GEMV_IMPL", "1")))
+    ap.add_argument("--attention-impl", type=int, default=int(os.environ.get("QLLM_ATTENTION_IMPL", "1")),
+                    help="Q4H attention kernel: 1 = INT8 mma.sync, 2 = tcgen05 with tensor-memory accumulators")
     ap.add_argument("--small", action="store_true", help="4-layer model for profiler captures")
     ap.add_argument("--model", default="dense27b", choices=["dense27b", "moe35b"],
                     help="dense27b: the headline workload; moe35b: the routed 35B-A3B-class target")
@@ -381,6 +383,7 @@ def ours(args):
         model = DeviceModel(cfg, seed=rank, device=f"cuda:{local}")
         provider = model.provider()
     provider.set_gemv_impl(args.gemv_impl)
+    provider.set_attention_impl(args.attention_impl)
     request = RequestParameters(sampling_seed=1 + replica, sampling_temperature_ppm=0,
                                 reserved_context_tokens=cfg["max_context"])
     synthetic = context - REAL_PREFILL
@@ -499,6 +502,7 @@ def ours(args):
     if world == 1 and not routed and not tensor_parallel and not args.no_echo_leg and not args.small:
         echo_provider = model.echo_variant().provider()
         echo_provider.set_gemv_impl(args.gemv_impl)
+        echo_provider.set_attention_impl(args.attention_impl)
         echo_provider.set_graph_mode(not args.no_graph)
         es = echo_provider.create_request_state()
         prompt = np.random.default_rng(77).integers(0, cfg["vocab"], context, dtype=np.uint32)
@@ -558,6 +562,8 @@ def ours(args):
                    "l2_policy": f"inputs larger than L2 ({step_bytes / 1e9:.1f} GB streamed per step)",
                    "prompt_cache": f"first {synthetic} positions seeded synthetic records, last {REAL_PREFILL} real prefill",
                    "gemv_impl": "tcgen05" if args.gemv_impl == 1 else "dp4a",
+                   "attention_impl": {0: "scalar", 1: "mma.sync", 2: "tcgen05"}[args.attention_impl],
+                   "split_tokens": cfg["split_tokens"],
                    "launch": "per kernel" if args.no_graph else "CUDA graph per step"},
         "accepted_len_per_step": tokens_a / (args.steps * args.streams * jobs),
         "tok_s_if_all_drafts_accepted": 5.0 * args.steps * args.streams * jobs / (ms_value * 1e-3),

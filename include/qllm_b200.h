@@ -193,8 +193,10 @@ uint32_t qllm_provider_max_chunk_rows(const qllm_provider* provider);
 int qllm_provider_set_graph_mode(qllm_provider* provider, int enabled);
 /* GEMV implementation: 0 = CUDA-core kernel, 1 = tcgen05 block-scaled MMA kernel. */
 int qllm_provider_set_gemv_impl(qllm_provider* provider, int impl);
-/* Attention implementation: 1 (default) = tensor-core kernels where the geometry allows
- * (Q4H and Q8 caches, head_dim 128), 0 = the order-independent scalar kernel everywhere. */
+/* Attention implementation: 0 = the order-independent scalar kernel everywhere (the parity anchor);
+ * 1 (default) = tensor-core kernels through mma.sync where the geometry allows (Q4H, Q8 and F16 caches,
+ * head_dim 128); 2 = as 1, with the Q4H target cache on the tcgen05 kernel (INT8 MMAs with tensor-memory
+ * accumulators; decode steps with at most 32 matrix rows per kv head, 128-token aligned splits). */
 int qllm_provider_set_attention_impl(qllm_provider* provider, int impl);
 
 /* Tensor-parallel verify (no reference counterpart: the reference runs one GPU per model; the

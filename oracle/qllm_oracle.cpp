@@ -46,6 +46,75 @@ float f16_value(uint16_t bits) {
 }
 inline float f16_round(float v) { return f16_value(f16_bits(v)); }
 
+// Transcendentals that give the same bits on the host and on the device: only IEEE double
+// additions, multiplications and divisions in a fixed order (no fused multiply-add on either side),
+// a round-to-nearest-integer and an exponent built from bits.  The library functions (expf, cosf)
+// differ in the last place between vendors, and a last-place difference that crosses a BF16
+// rounding boundary changes every later step of a W4A4 decoder.
+inline double det_exp_core(double x) {  // |x| < 700
+  const double k = std::rint(x * 1.4426950408889634);
+  const double r = (x - k * 6.93147180369123816490e-01) - k * 1.90821492927058770002e-10;
+  // Taylor series of exp(r), |r| <= 0.35, to r^14 / 14!
+  double p = 1.0 / 87178291200.0;
+  p = p * r + 1.0 / 6227020800.0;
+  p = p * r + 1.0 / 479001600.0;
+  p = p * r + 1.0 / 39916800.0;
+  p = p * r + 1.0 / 3628800.0;
+  p = p * r + 1.0 / 362880.0;
+  p = p * r + 1.0 / 40320.0;
+  p = p * r + 1.0 / 5040.0;
+  p = p * r + 1.0 / 720.0;
+  p = p * r + 1.0 / 120.0;
+  p = p * r + 1.0 / 24.0;
+  p = p * r + 1.0 / 6.0;
+  p = p * r + 0.5;
+  p = p * r + 1.0;
+  p = p * r + 1.0;
+  const long long e = static_cast<long long>(k) + 1023LL;  // 2^k as a double, built from its bits
+  const unsigned long long bits = static_cast<unsigned long long>(e) << 52U;
+  double scale;
+  std::memcpy(&scale, &bits, sizeof(scale));
+  return p * scale;
+}
+inline float det_expf(float x) {
+  if (!(x > -104.0F)) return 0.0F;       // below the smallest float (and NaN)
+  if (x > 88.0F) x = 88.0F;
+  return static_cast<float>(det_exp_core(static_cast<double>(x)));
+}
+// sin and cos of a float angle (|angle| < 2^20): three-part reduction by pi/2, Taylor series on
+// [-pi/4, pi/4] to r^17 and r^16.
+inline void det_sincosf(float angle, float* sine, float* cosine) {
+  const double x = static_cast<double>(angle);
+  const double k = std::rint(x * 0.63661977236758134308);
+  const double r = ((x - k * 1.57079632673412561417e+00) - k * 6.07710050630396597660e-11) -
+                   k * 2.02226624879595063154e-21;
+  const double z = r * r;
+  double s = -1.0 / 355687428096000.0;   // r^17 / 17!
+  s = s * z + 1.0 / 1307674368000.0;
+  s = s * z - 1.0 / 6227020800.0;
+  s = s * z + 1.0 / 39916800.0;
+  s = s * z - 1.0 / 362880.0;
+  s = s * z + 1.0 / 5040.0;
+  s = s * z - 1.0 / 120.0;
+  s = s * z + 1.0 / 6.0;
+  s = r - r * z * s;
+  double c = 1.0 / 20922789888000.0;     // r^16 / 16!
+  c = c * z - 1.0 / 87178291200.0;
+  c = c * z + 1.0 / 479001600.0;
+  c = c * z - 1.0 / 3628800.0;
+  c = c * z + 1.0 / 40320.0;
+  c = c * z - 1.0 / 720.0;
+  c = c * z + 1.0 / 24.0;
+  c = c * z - 0.5;
+  c = c * z + 1.0;
+  const long long q = static_cast<long long>(k) & 3LL;
+  const double sv = (q == 0) ? s : (q == 1) ? c : (q == 2) ? -s : -c;
+  const double cv = (q == 0) ? c : (q == 1) ? -s : (q == 2) ? -c : s;
+  *sine = static_cast<float>(sv);
+  *cosine = static_cast<float>(cv);
+}
+
+
 // transformer_kernels.cu:1931-1936
 float e2m1_decode(uint8_t code) {
   static const float levels[8] = {0.0F, 0.5F, 1.0F, 1.5F, 2.0F, 3.0F, 4.0F, 6.0F};
@@ -245,7 +314,9 @@ void rope(float* heads, uint32_t rows, uint32_t head_count, uint32_t head_dim,
           const uint32_t pair = d % half;
           const float angle = static_cast<float>(positions[r]) * inv[pair];
           const float other = d < half ? -src[d + half] : src[d - half];
-          result = src[d] * act(std::cos(angle), bf16) + other * act(std::sin(angle), bf16);
+          float sine, cosine;
+          det_sincosf(angle, &sine, &cosine);
+          result = src[d] * act(cosine, bf16) + other * act(sine, bf16);
         }
         v[d] = act(result, bf16);
       }
@@ -427,10 +498,10 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
           tmax = std::fmax(tmax, score[j]);
         }
         const float next = std::fmax(m, tmax);
-        const float prev = m == kNegInf ? 0.0F : std::exp(m - next);
+        const float prev = m == kNegInf ? 0.0F : det_expf(m - next);
         double tsum_d = 0.0;
         for (uint32_t j = 0; j < n; ++j) {
-          float p = (t0 + j < ctx) ? std::exp(score[j] - next) : 0.0F;
+          float p = (t0 + j < ctx) ? det_expf(score[j] - next) : 0.0F;
           if (enc == QO_KV_Q8) p = bf16_round(p);
           else if (enc == QO_KV_F16) p = f16_round(p);
           prob[j] = p;
@@ -494,13 +565,13 @@ void attention(uint32_t enc, const uint8_t* const* pages, size_t layer_offset, u
     // split terms are FP32 products; their sums are formed in double so that the merge does
     // not depend on the order in which splits are visited
     double gsum_d = 0.0;
-    for (uint32_t s = 0; s < active; ++s) gsum_d += static_cast<double>(psum[s] * std::exp(pmax[s] - gmax));
+    for (uint32_t s = 0; s < active; ++s) gsum_d += static_cast<double>(psum[s] * det_expf(pmax[s] - gmax));
     const float gsum = static_cast<float>(gsum_d);
     float* o = out + (static_cast<size_t>(row) * qh + head) * hd;
     for (uint32_t d = 0; d < hd; ++d) {
       double result = 0.0;
       for (uint32_t s = 0; s < active; ++s)
-        result += static_cast<double>(pout[static_cast<size_t>(s) * hd + d] * std::exp(pmax[s] - gmax));
+        result += static_cast<double>(pout[static_cast<size_t>(s) * hd + d] * det_expf(pmax[s] - gmax));
       o[d] = act(static_cast<float>(result) / gsum, bf16);
     }
   }
@@ -738,7 +809,7 @@ struct qo_session {
         nvfp4_gemv(b.expert_gate[e], 0, W, x, 1, gate.data());
         nvfp4_gemv(b.expert_up[e], 0, W, x, 1, up.data());
         for (uint32_t i = 0; i < W; ++i)
-          mid[i] = bf16_round((gate[i] / (1.0F + std::exp(-gate[i]))) * up[i]);
+          mid[i] = bf16_round((gate[i] / (1.0F + det_expf(-gate[i]))) * up[i]);
         nvfp4_gemv(b.expert_down[e], 0, H, mid.data(), 1, out.data());
         for (uint32_t i = 0; i < H; ++i) total[i] += score[slot] * out[i];  // ordered over the slots
       }
@@ -789,7 +860,7 @@ struct qo_session {
       for (uint32_t i = 0; i < c.ffn; ++i) {
         const float g = gate_up[static_cast<size_t>(r) * 2U * c.ffn + i];
         const float u = gate_up[static_cast<size_t>(r) * 2U * c.ffn + c.ffn + i];
-        const float a = act(g / (1.0F + std::exp(-g)), bf);
+        const float a = act(g / (1.0F + det_expf(-g)), bf);
         inter[static_cast<size_t>(r) * c.ffn + i] = act(a * u, bf);
       }
     nvfp4_gemv(b.down, 0, b.down.rows, inter.data(), rows, hidden.data());

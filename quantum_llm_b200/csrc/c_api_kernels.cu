@@ -148,7 +148,7 @@ int qllm_k_rope_kv_store(float* qkv, uint32_t rows, uint32_t q_heads, uint32_t k
     return fail(QLLM_INVALID_ARGUMENT, "invalid RoPE/KV store batch");
   RopeStoreArgs a{qkv, rows, q_heads, kv_heads, head_dim, rotary_dim, inv_freq, first_position,
                   position_offset, rotary_offset, page_table, layer_offset, page_tokens, encoding,
-                  bf16 != 0};
+                  bf16 != 0, true};
   return launch_rope_kv_store(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -8,6 +8,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstring>
 #include <string>
 
 #include "../../include/qllm_b200.h"
@@ -42,6 +43,74 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffU, v, o));
   return v;
+}
+
+// Transcendentals that give the same bits on the host and on the device: only IEEE double
+// additions, multiplications and divisions in a fixed order (no fused multiply-add on either side),
+// a round-to-nearest-integer and an exponent built from bits.  The library functions (expf, cosf)
+// differ in the last place between vendors, and a last-place difference that crosses a BF16
+// rounding boundary changes every later step of a W4A4 decoder.
+__host__ __device__ __forceinline__ double det_exp_core(double x) {  // |x| < 700
+  const double k = rint(x * 1.4426950408889634);
+  const double r = (x - k * 6.93147180369123816490e-01) - k * 1.90821492927058770002e-10;
+  // Taylor series of exp(r), |r| <= 0.35, to r^14 / 14!
+  double p = 1.0 / 87178291200.0;
+  p = p * r + 1.0 / 6227020800.0;
+  p = p * r + 1.0 / 479001600.0;
+  p = p * r + 1.0 / 39916800.0;
+  p = p * r + 1.0 / 3628800.0;
+  p = p * r + 1.0 / 362880.0;
+  p = p * r + 1.0 / 40320.0;
+  p = p * r + 1.0 / 5040.0;
+  p = p * r + 1.0 / 720.0;
+  p = p * r + 1.0 / 120.0;
+  p = p * r + 1.0 / 24.0;
+  p = p * r + 1.0 / 6.0;
+  p = p * r + 0.5;
+  p = p * r + 1.0;
+  p = p * r + 1.0;
+  const long long e = static_cast<long long>(k) + 1023LL;  // 2^k as a double, built from its bits
+  const unsigned long long bits = static_cast<unsigned long long>(e) << 52U;
+  double scale;
+  memcpy(&scale, &bits, sizeof(scale));
+  return p * scale;
+}
+__host__ __device__ __forceinline__ float det_expf(float x) {
+  if (!(x > -104.0F)) return 0.0F;       // below the smallest float (and NaN)
+  if (x > 88.0F) x = 88.0F;
+  return static_cast<float>(det_exp_core(static_cast<double>(x)));
+}
+// sin and cos of a float angle (|angle| < 2^20): three-part reduction by pi/2, Taylor series on
+// [-pi/4, pi/4] to r^17 and r^16.
+__host__ __device__ __forceinline__ void det_sincosf(float angle, float* sine, float* cosine) {
+  const double x = static_cast<double>(angle);
+  const double k = rint(x * 0.63661977236758134308);
+  const double r = ((x - k * 1.57079632673412561417e+00) - k * 6.07710050630396597660e-11) -
+                   k * 2.02226624879595063154e-21;
+  const double z = r * r;
+  double s = -1.0 / 355687428096000.0;   // r^17 / 17!
+  s = s * z + 1.0 / 1307674368000.0;
+  s = s * z - 1.0 / 6227020800.0;
+  s = s * z + 1.0 / 39916800.0;
+  s = s * z - 1.0 / 362880.0;
+  s = s * z + 1.0 / 5040.0;
+  s = s * z - 1.0 / 120.0;
+  s = s * z + 1.0 / 6.0;
+  s = r - r * z * s;
+  double c = 1.0 / 20922789888000.0;     // r^16 / 16!
+  c = c * z - 1.0 / 87178291200.0;
+  c = c * z + 1.0 / 479001600.0;
+  c = c * z - 1.0 / 3628800.0;
+  c = c * z + 1.0 / 40320.0;
+  c = c * z - 1.0 / 720.0;
+  c = c * z + 1.0 / 24.0;
+  c = c * z - 0.5;
+  c = c * z + 1.0;
+  const long long q = static_cast<long long>(k) & 3LL;
+  const double sv = (q == 0) ? s : (q == 1) ? c : (q == 2) ? -s : -c;
+  const double cv = (q == 0) ? c : (q == 1) ? -s : (q == 2) ? -c : s;
+  *sine = static_cast<float>(sv);
+  *cosine = static_cast<float>(cv);
 }
 
 // E2M1 value of a 4-bit code.

@@ -49,6 +49,7 @@ struct CombineArgs {
   QuantSink sink;
   uint32_t sink_row_offset;  // operand row of this launch's row 0 (a chunk merged in row tiles)
   uint32_t tiles;            // > 1: grid z = row tile; `rows` rows each, partials one tile after the other
+  bool exact;                // exp from the deterministic series shared with the CPU oracle
 };
 int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t stream);
 

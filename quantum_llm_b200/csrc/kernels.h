@@ -52,6 +52,9 @@ struct RopeStoreArgs {
   size_t layer_offset;
   uint32_t page_tokens, encoding;
   bool bf16;
+  // sin / cos from the deterministic double-precision series (the same bits as the CPU oracle)
+  // instead of the device's single-precision library functions
+  bool exact;
 };
 int launch_rope_kv_store(const RopeStoreArgs& a, cudaStream_t stream);
 
@@ -70,7 +73,7 @@ struct AttentionArgs {
   bool bf16;
   void* workspace;
   float* out;                 // [rows, q_heads*head_dim]
-  int impl;                   // 0 scalar, 1 tensor-core (Q4H)
+  int impl;                   // 0 scalar, 1 tensor cores through mma.sync, 2 tcgen05 + tensor memory (Q4H; else as 1)
   uint32_t* error;            // optional device status word (set when a pipeline wait runs out)
   bool skip_combine;          // leave the per-split partials in the workspace (merged by the caller)
   // optional (tensor-core Q4H path): queries already quantised to INT8 by the RoPE kernel,
@@ -102,6 +105,13 @@ __device__ __forceinline__ void attention_row_tile(AttentionArgs& a, P& part) {
 #endif
 int launch_attention_q4h_pipelined(const AttentionArgs& a, float* maxima, float* sums, float* outputs,
                                    uint32_t* error, cudaStream_t stream);
+// tcgen05 (tensor memory) kernel over the Q4H cache: head_dim 128, rows * group <= 32, 128-token
+// aligned pages and splits.  `scratch` (attention_q4h_tc_query_bytes) holds the INT8 queries when the
+// caller passes FP32 queries only.
+bool attention_q4h_tc_supported(const AttentionArgs& a);
+size_t attention_q4h_tc_query_bytes(uint32_t rows, uint32_t q_heads);
+int launch_attention_q4h_tc(const AttentionArgs& a, float* maxima, float* sums, float* outputs, uint32_t* error,
+                            void* scratch, cudaStream_t stream);
 // BF16 tensor-core kernel over the Q8 cache (head_dim 128, at most 8 kv heads).
 bool attention_q8_mma_supported(const AttentionArgs& a);
 int launch_attention_q8_mma(const AttentionArgs& a, float* maxima, float* sums, float* outputs, uint32_t* error,

@@ -58,7 +58,10 @@ __global__ void rope_kv_store_kernel(RopeStoreArgs a, GemvOut src_out, float* q_
     const uint32_t pair = d % half;
     const float angle = static_cast<float>(rotary_position) * a.inv_freq[pair];
     const float other = d < half ? -src[d + half] : src[d - half];
-    result = src[d] * actv(cosf(angle), a.bf16) + other * actv(sinf(angle), a.bf16);
+    float sine, cosine;
+    if (a.exact) det_sincosf(angle, &sine, &cosine);
+    else { sine = sinf(angle); cosine = cosf(angle); }
+    result = src[d] * actv(cosine, a.bf16) + other * actv(sine, a.bf16);
   }
   result = actv(result, a.bf16);
   if (v) v[d] = result;
@@ -165,7 +168,10 @@ rope_kv_store_warp128_kernel(RopeStoreArgs a, GemvOut src_out, float* q_out, int
       const uint32_t pair = (d0 + i) % half;
       const float angle = static_cast<float>(rotary_position) * a.inv_freq[pair];
       const float other = low ? -other_raw : other_raw;
-      result[i] = src[i] * actv(cosf(angle), a.bf16) + other * actv(sinf(angle), a.bf16);
+      float sine, cosine;
+      if (a.exact) det_sincosf(angle, &sine, &cosine);
+      else { sine = sinf(angle); cosine = cosf(angle); }
+      result[i] = src[i] * actv(cosine, a.bf16) + other * actv(sine, a.bf16);
     }
     result[i] = actv(result[i], a.bf16);
   }
@@ -282,7 +288,9 @@ struct Partials {
 size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                                  uint32_t max_splits) {
   const size_t items = static_cast<size_t>(rows) * max_splits * q_heads;
-  return items * (2U + head_dim) * sizeof(float);
+  // partials, then room for INT8 queries made on the fly (tensor-memory kernel without ready-made ones)
+  return ((items * (2U + head_dim) * sizeof(float) + 255U) & ~static_cast<size_t>(255U)) +
+         attention_q4h_tc_query_bytes(rows, q_heads);
 }
 static Partials partials_of(const AttentionArgs& a) {
   const size_t items = static_cast<size_t>(a.rows) * a.max_splits * a.q_heads;
@@ -448,8 +456,8 @@ attention_scalar_kernel(AttentionArgs a, Partials part) {
       const float tmax = warp_max(score);
       const float old = rmax[mr];
       const float next = fmaxf(old, tmax);
-      const float prev = old == kNegInf ? 0.0F : expf(old - next);
-      float p = visible ? expf(score - next) : 0.0F;
+      const float prev = old == kNegInf ? 0.0F : det_expf(old - next);
+      float p = visible ? det_expf(score - next) : 0.0F;
       float stored;
       if (ENC == QLLM_KV_Q4H) {
         const float w = visible ? p * vscale[lane] : 0.0F;
@@ -525,7 +533,7 @@ __global__ void attention_combine_kernel(AttentionArgs a, Partials part) {
     float sum = 0.0F;
     for (uint32_t s = 0; s < active; ++s) {
       const size_t p = base + static_cast<size_t>(s) * a.q_heads;
-      sum += part.sums[p] * expf(part.maxima[p] - m);
+      sum += part.sums[p] * det_expf(part.maxima[p] - m);
     }
     gmax = m;
     gsum = sum;
@@ -534,7 +542,7 @@ __global__ void attention_combine_kernel(AttentionArgs a, Partials part) {
   float result = 0.0F;
   for (uint32_t s = 0; s < active; ++s) {
     const size_t p = base + static_cast<size_t>(s) * a.q_heads;
-    result += part.outputs[p * hd + d] * expf(part.maxima[p] - gmax);
+    result += part.outputs[p * hd + d] * det_expf(part.maxima[p] - gmax);
   }
   a.out[(static_cast<size_t>(row) * a.q_heads + head) * hd + d] = actv(result / gsum, a.bf16);
 }
@@ -548,20 +556,27 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   const Partials part = partials_of(a);
   const dim3 grid(a.kv_heads, a.max_splits, a.tiles > 1U ? a.tiles : 1U);
   if (a.tiles > 1U && !a.skip_combine) return fail(QLLM_INVALID_ARGUMENT, "row tiles are merged by the caller");
-  if (a.impl == 1 && a.encoding == QLLM_KV_F16) {
+  const bool mma = a.impl >= 1;   // 2 asks for the tensor-memory kernel where one exists (Q4H)
+  if (a.impl == 2 && a.encoding == QLLM_KV_Q4H && attention_q4h_tc_supported(a)) {
+    const size_t items = static_cast<size_t>(a.rows) * a.max_splits * a.q_heads;
+    uint8_t* scratch = static_cast<uint8_t*>(a.workspace) +
+                       ((items * (2U + a.head_dim) * sizeof(float) + 255U) & ~static_cast<size_t>(255U));
+    const int rc = launch_attention_q4h_tc(a, part.maxima, part.sums, part.outputs, a.error, scratch, stream);
+    if (rc) return rc;
+  } else if (mma && a.encoding == QLLM_KV_F16) {
     if (!attention_f16_mma_supported(a))
       return fail(QLLM_INVALID_ARGUMENT,
                   "tensor-core F16 attention needs head_dim 128, rows*group <= 32, 32-token aligned pages and splits");
     const int rc = launch_attention_f16_mma(a, part.maxima, part.sums, part.outputs, a.error, stream);
     if (rc) return rc;
-  } else if (a.impl == 1 && a.encoding == QLLM_KV_Q8) {
+  } else if (mma && a.encoding == QLLM_KV_Q8) {
     if (!attention_q8_mma_supported(a))
       return fail(QLLM_INVALID_ARGUMENT,
                   "tensor-core Q8 attention needs head_dim 128, at most 8 kv heads, rows*group <= 32, "
                   "32-token aligned pages and splits");
     const int rc = launch_attention_q8_mma(a, part.maxima, part.sums, part.outputs, a.error, stream);
     if (rc) return rc;
-  } else if (a.impl == 1) {
+  } else if (mma) {
     if (a.encoding != QLLM_KV_Q4H || a.head_dim != 128U || MR > 64U || a.query_row_stride % 4U ||
         a.page_tokens % 64U || a.split_tokens % 64U)
       return fail(QLLM_INVALID_ARGUMENT,
@@ -631,6 +646,7 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   c.max_splits = a.max_splits;
   c.bf16 = a.bf16;
   c.out = a.out;
+  c.exact = a.impl == 0;
   c.sink = no_sink();
   return launch_combine_quant(c, a.rows, stream);
 }

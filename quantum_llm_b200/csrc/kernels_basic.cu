@@ -310,7 +310,7 @@ __global__ void silu_product_kernel(const float* __restrict__ gate_up, float* __
   if (i >= ffn) return;
   const float g = gate_up[static_cast<size_t>(row) * 2U * ffn + i];
   const float u = gate_up[static_cast<size_t>(row) * 2U * ffn + ffn + i];
-  const float a = actv(g / (1.0F + expf(-g)), bf16);
+  const float a = actv(g / (1.0F + det_expf(-g)), bf16);
   out[static_cast<size_t>(row) * ffn + i] = actv(a * u, bf16);
 }
 int launch_silu_product(const float* gate_up, float* out, uint32_t rows, uint32_t ffn, bool bf16,

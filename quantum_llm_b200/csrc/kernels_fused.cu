@@ -125,15 +125,17 @@ silu_quant_kernel(GemvOut gate_up, uint32_t ffn, bool bf16, QuantSink sink, floa
   const uint32_t n4 = ffn / 4U;
   const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
   const bool valid = item < gate_up.batch * n4;
+  // the exact path (CUDA-core operand) takes exp from the deterministic series shared with the oracle
+  const bool exact = sink.kind == 0;
   const uint32_t row = valid ? item / n4 : 0U, f = valid ? item % n4 : 0U;
   float4 v = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
   if (valid) {
     const float4 g = gemv_value4(gate_up, row, 4U * f);
     const float4 u = gemv_value4(gate_up, row, ffn + 4U * f);
-    v.x = actv(actv(g.x / (1.0F + expf(-g.x)), bf16) * u.x, bf16);
-    v.y = actv(actv(g.y / (1.0F + expf(-g.y)), bf16) * u.y, bf16);
-    v.z = actv(actv(g.z / (1.0F + expf(-g.z)), bf16) * u.z, bf16);
-    v.w = actv(actv(g.w / (1.0F + expf(-g.w)), bf16) * u.w, bf16);
+    v.x = actv(actv(g.x / (1.0F + (exact ? det_expf(-g.x) : expf(-g.x))), bf16) * u.x, bf16);
+    v.y = actv(actv(g.y / (1.0F + (exact ? det_expf(-g.y) : expf(-g.y))), bf16) * u.y, bf16);
+    v.z = actv(actv(g.z / (1.0F + (exact ? det_expf(-g.z) : expf(-g.z))), bf16) * u.z, bf16);
+    v.w = actv(actv(g.w / (1.0F + (exact ? det_expf(-g.w) : expf(-g.w))), bf16) * u.w, bf16);
     if (inter) reinterpret_cast<float4*>(inter + static_cast<size_t>(row) * ffn)[f] = v;
   }
   quant_store_quad(sink, row, f / 4U, v, valid);
@@ -221,7 +223,7 @@ combine_quant_kernel(CombineArgs c) {
 #pragma unroll
     for (uint32_t b = 0; b < kBatch; ++b) {
       if (s0 + 8U * b >= active) break;
-      const float w = expf(smax[b] - m);
+      const float w = c.exact ? det_expf(smax[b] - m) : expf(smax[b] - m);
       sum += static_cast<double>(ssum[b] * w);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {

@@ -257,7 +257,7 @@ moe_gate_up_kernel(MoeArgs a) {
     if (lane == static_cast<uint32_t>(r)) {
       const float gate = bf16r(static_cast<float>(g[r]) * G.weight_scale / G.input_scale);
       const float up = bf16r(static_cast<float>(u[r]) * U.weight_scale / U.input_scale);
-      mid_tile[warp * 4U + r] = bf16r((gate / (1.0F + expf(-gate))) * up);
+      mid_tile[warp * 4U + r] = bf16r((gate / (1.0F + det_expf(-gate))) * up);
     }
   }
   __syncthreads();
@@ -398,7 +398,7 @@ moe_gate_up_staged_kernel(MoeArgs a, uint32_t* error) {
       if (lane == static_cast<uint32_t>(r)) {
         const float gate = bf16r(static_cast<float>(g[r]) * G.weight_scale / G.input_scale);
         const float up = bf16r(static_cast<float>(u[r]) * U.weight_scale / U.input_scale);
-        mid_tile[warp * 2U + r] = bf16r((gate / (1.0F + expf(-gate))) * up);
+        mid_tile[warp * 2U + r] = bf16r((gate / (1.0F + det_expf(-gate))) * up);
       }
     }
     __syncthreads();  // the stage is free, mid_tile is complete

@@ -443,11 +443,11 @@ struct qllm_provider {
     rs.q_out = qkv.p;
     rs.base = RopeStoreArgs{nullptr, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
                             first_position, position_offset, rotary_offset, st.page_table, layer_offset,
-                            c.page_tokens, enc, bf};
+                            c.page_tokens, enc, bf, gemv_impl == 0};
     // a chunk wider than kMaxRows rows goes through attention in row tiles: every row sees the
     // cache up to its own position, and the records of the whole chunk are stored before the first tile
     const uint32_t tile_rows = std::min(rows, kMaxRows);
-    const bool tensor_attention = attention_impl == 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
+    const bool tensor_attention = attention_impl >= 1 && enc == QLLM_KV_Q4H && c.head_dim == 128U &&
                                   tile_rows * (c.q_heads / c.kv_heads) <= 64U;
     rs.q8_out = tensor_attention ? q8.p : nullptr;
     rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
@@ -479,13 +479,16 @@ struct qllm_provider {
       at.workspace = attn_ws.p;
       at.out = nullptr;  // the splits are merged by the combine + quantise kernel below
       at.impl = tensor_attention ? 1 : 0;
-      if (attention_impl == 1 && enc == QLLM_KV_Q8 && attention_q8_mma_supported(at)) at.impl = 1;
-      if (attention_impl == 1 && enc == QLLM_KV_F16 && attention_f16_mma_supported(at)) at.impl = 1;
+      if (attention_impl >= 1 && enc == QLLM_KV_Q8 && attention_q8_mma_supported(at)) at.impl = 1;
+      if (attention_impl >= 1 && enc == QLLM_KV_F16 && attention_f16_mma_supported(at)) at.impl = 1;
+      // tensor-memory kernel (one row tile, at most 32 matrix rows); checked below once the INT8 queries are set
+      const bool want_tc = attention_impl == 2 && tensor_attention && tiles == 1U;
       at.query_q8 = rs.q8_out ? rs.q8_out + static_cast<size_t>(r0) * qkv_w : nullptr;
       at.query_q8_scale = rs.q8_scale ? rs.q8_scale + static_cast<size_t>(r0) * c.q_heads : nullptr;
       at.error = kernel_error.p;
       at.skip_combine = true;
       at.tiles = tiles;
+      if (want_tc && attention_q4h_tc_supported(at)) at.impl = 2;
       ok(launch_attention(at, stream));
       CombineArgs cb{};
       const size_t items = static_cast<size_t>(n) * splits * c.q_heads;
@@ -500,6 +503,7 @@ struct qllm_provider {
       cb.max_splits = splits;
       cb.bf16 = bf;
       cb.out = nullptr;
+      cb.exact = attention_impl == 0;
       cb.sink = sink_for(b.o, rows);
       cb.sink_row_offset = r0;
       cb.tiles = tiles;
@@ -1042,7 +1046,7 @@ int qllm_provider_tp_attach_local(qllm_provider* p, void* const* areas) {
 }
 
 int qllm_provider_set_attention_impl(qllm_provider* p, int impl) {
-  if (!p || impl < 0 || impl > 1) return fail(QLLM_INVALID_ARGUMENT, "unknown attention implementation");
+  if (!p || impl < 0 || impl > 2) return fail(QLLM_INVALID_ARGUMENT, "unknown attention implementation");
   p->attention_impl = impl;
   return QLLM_OK;
 }

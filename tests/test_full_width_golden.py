@@ -100,7 +100,7 @@ def test_exact_path_equals_the_oracle_bit_for_bit(built):
 
 def test_benchmarked_path_stays_within_the_stated_tolerance_of_the_oracle(built):
     case, model, g = built
-    run = _decode(model, case, gemv_impl=1, attention_impl=1, graph=True)
+    run = _decode(model, case, gemv_impl=1, attention_impl=2, graph=True)   # 2: tcgen05 attention where the geometry allows
     assert run["first"] == int(g["first_token"])
     verify_gpu = [run["first"]] + run["initial_drafts"]
     verify_cpu = [int(g["first_token"])] + [int(t) for t in g["initial_drafts"]]

@@ -120,7 +120,7 @@ def test_tiny_greedy_with_tensor_core_gemv():
 WIDE = dict(synth.TINY, head_dim=128, rotary_dim=128, kv_encoding=ob.KV_Q4H)
 
 
-@pytest.mark.parametrize("attention_impl", [0, 1])
+@pytest.mark.parametrize("attention_impl", [0, 1, 2])
 @pytest.mark.parametrize("kv_encoding", [ob.KV_Q4H, ob.KV_F16])
 def test_head_dim_128_caches(kv_encoding, attention_impl):
     model = synth.SynthModel(dict(WIDE, kv_encoding=kv_encoding), seed=2)

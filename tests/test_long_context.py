@@ -58,6 +58,14 @@ def _gpu_run(model, prompt, gemv_impl, attention_impl, graph):
     return run
 
 
+def test_mma_sync_attention_at_32k_context(case):
+    model, prompt, cpu = case
+    gpu = _gpu_run(model, prompt, 1, 1, True)
+    assert gpu["first"] == cpu["first"]
+    a, b = gpu["steps"][0]["logits"][0], cpu["steps"][0]["logits"][0]
+    assert np.abs(a - b).max() <= 2e-2
+
+
 @pytest.fixture(scope="module")
 def case():
     model = synth.SynthModel(CFG, seed=5)
@@ -85,7 +93,7 @@ def test_exact_path_at_32k_context(case):
 
 def test_benchmarked_kernels_at_32k_context(case):
     model, prompt, cpu = case
-    gpu = _gpu_run(model, prompt, 1, 1, True)
+    gpu = _gpu_run(model, prompt, 1, 2, True)
     assert gpu["first"] == cpu["first"]
     inputs_gpu, inputs_cpu = [gpu["first"]] + gpu["drafts"], [cpu["first"]] + cpu["drafts"]
     rows, report = 0, []
