@@ -199,7 +199,7 @@ class OracleSteps:
             if hasattr(config, k):
                 setattr(config, k, v)
         self.session = ob.Session(config, weights, (keep, blocks))
-        self.request = ob.Request(1, 0, 950000, 20, 0, c["max_context"])
+        self.request = ob.Request(1, 0, 950000, 20, 0, c["max_context"], 2000000)
         real = 8
         self.session.fill_synthetic_kv(0, context - real, 1234)
         prompt = rng.integers(0, V, real, dtype=np.uint32)

@@ -108,6 +108,11 @@ typedef struct qllm_request {
   uint32_t sampling_top_k; /* 1..64 when sampling */
   uint32_t sampling_min_p_ppm;
   uint32_t reserved_context_tokens; /* context limit of the request */
+  /* sampling_presence_penalty_biased_ppm: penalty * 1e6 + 2 000 000, i.e. 2 000 000 = no penalty
+   * (apply_presence_penalty, runtime/tools/dense_fp4_provider.cpp:8336-8347).  The presence penalty
+   * is not implemented: any other value is refused with QLLM_INVALID_ARGUMENT, so a request can
+   * never be decoded without a penalty it asked for. */
+  uint32_t sampling_presence_penalty_biased_ppm;
 } qllm_request;
 
 /* ExactDecodeExecutionResult (program_executor.hpp:205-212). */

@@ -48,7 +48,8 @@ class Weights(C.Structure):
 class Request(C.Structure):
     _fields_ = [("seed", C.c_uint64), ("temperature_ppm", C.c_uint32),
                 ("top_p_ppm", C.c_uint32), ("top_k", C.c_uint32),
-                ("min_p_ppm", C.c_uint32), ("context_limit", C.c_uint32)]
+                ("min_p_ppm", C.c_uint32), ("context_limit", C.c_uint32),
+                ("presence_penalty_biased_ppm", C.c_uint32)]
 
 
 class StepResult(C.Structure):

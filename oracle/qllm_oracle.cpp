@@ -1183,6 +1183,7 @@ int qo_prefill_at(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_
                   const qo_request* rq, uint32_t* first_token) {
   try {
     const auto& c = s->cfg;
+    if (rq->presence_penalty_biased_ppm != 2000000U) throw std::runtime_error("presence penalty is not restated");
     if (!count || !chunk_rows || base + count + 1U >= rq->context_limit || rq->context_limit > c.max_context ||
         s->mtp_length != base)
       throw std::runtime_error("invalid prefill request");

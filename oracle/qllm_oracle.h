@@ -98,6 +98,7 @@ typedef struct qo_request {
   uint32_t top_k;           /* 1..64 when temperature_ppm != 0 */
   uint32_t min_p_ppm;
   uint32_t context_limit;   /* reserved_context_tokens */
+  uint32_t presence_penalty_biased_ppm; /* 2000000 = none (the only value restated here) */
 } qo_request;
 
 typedef struct qo_step_result {

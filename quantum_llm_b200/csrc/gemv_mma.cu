@@ -302,8 +302,8 @@ struct GemvMmaParams {
   uint32_t* error;
   uint32_t first_tile, row_count, batch, n_pad;
   uint32_t k_chunks, k_atoms, split, stages;  // k_atoms: atoms per row tile in memory (whole stages)
-  uint32_t k_valid;             // 64-wide k groups that lie inside K (the last stage may be partial)
-  uint32_t raw;                 // 1: always write raw partials (the consumer applies the scale)
+  uint32_t raw;                 // bit 0: always write raw partials (the consumer applies the scale);
+                                // bits 1..: 64-wide k groups that lie inside K (the last stage may be partial)
   float weight_scale, input_scale;
 };
 
@@ -314,7 +314,9 @@ struct GemvMmaParams {
 template <bool kExchange> struct ExchangeParam {};
 template <> struct ExchangeParam<true> { GemvExchange x; };
 
-template <bool kExchange>
+// kPartialK: K is not a whole number of 256-wide stages (the last stage issues fewer MMAs); its own
+// instantiation so that the common form carries no extra state.
+template <bool kExchange, bool kPartialK>
 __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                       const __grid_constant__ CUtensorMap act_map, GemvMmaParams p,
@@ -414,10 +416,11 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                      "l"(umma_desc_sf(sfb + kb * kAtomBytes))
                      : "memory");
       }
-      const uint32_t groups = min(4U, p.k_valid - (kc0 + i) * 4U);  // beyond K: zero-filled codes, not issued
+      uint32_t groups = 4U;
+      if constexpr (kPartialK) groups = min(4U, (p.raw >> 1U) - (kc0 + i) * 4U);  // beyond K: zero-filled codes, not issued
 #pragma unroll
       for (uint32_t kb = 0; kb < 4U; ++kb) {
-        if (kb >= groups) break;
+        if (kPartialK && kb >= groups) break;
         const uint64_t adesc = umma_desc_sw128(st + kb * 32U);
         const uint64_t bdesc = umma_desc_sw128(b + kb * 32U);
         const uint32_t accumulate = (i > 0U || kb > 0U) ? 1U : 0U;
@@ -486,7 +489,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
           const uint32_t col = n_tile * 128U + c0 + j;
           if (col >= p.batch) continue;
           const float acc = __uint_as_float(v[j]);
-          if (p.split == 1U && !p.raw)
+          if (p.split == 1U && !(p.raw & 1U))
             p.y[static_cast<size_t>(col) * p.row_count + row] = bf16r(acc * p.weight_scale / p.input_scale);
           else
             p.partials[(static_cast<size_t>(blockIdx.y) * p.batch + col) * p.row_count + row] = acc;
@@ -611,10 +614,13 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   cudaGetDevice(&device);
   size_t& opted = opted_by_device[device & 63];
   if (smem > opted) {
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
+    if (rc) return rc;
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
     opted = smem;
@@ -631,17 +637,19 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.n_pad = n_pad;
   p.k_chunks = k_chunks;
   p.k_atoms = padded_atoms(m.cols);
-  p.k_valid = m.cols / 64U;
   p.split = split;
   p.stages = stages;
-  p.raw = raw ? 1U : 0U;
+  p.raw = (raw ? 1U : 0U) | ((m.cols / 64U) << 1U);
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
   count_launch();
   if (exchange != nullptr)
-    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true, true>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
                                  w.codes_map, act_map, p, ExchangeParam<true>{*exchange}), "nvfp4_gemv_mma");
-  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+  if (m.cols % kTileK)
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, true>, dim3(row_tiles, split, n_tiles), dim3(128), smem,
+                                 stream, w.codes_map, act_map, p, ExchangeParam<false>{}), "nvfp4_gemv_mma");
+  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
                                w.codes_map, act_map, p, ExchangeParam<false>{}), "nvfp4_gemv_mma");
 }
 

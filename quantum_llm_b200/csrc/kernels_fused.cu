@@ -118,6 +118,7 @@ int launch_residual_norm_quant(const NormQuantArgs& a, uint32_t rows, cudaStream
 
 // ------------------------------------------------------------ SiLU product + quantise
 // One thread per 4 outputs: inter = act(act(silu(g)) * u), quantised for the down GEMV.
+template <bool kExact>  // exp from the deterministic series shared with the CPU oracle (the parity path)
 __global__ void __launch_bounds__(256)
 silu_quant_kernel(GemvOut gate_up, uint32_t ffn, bool bf16, QuantSink sink, float* inter) {
   pdl_trigger();
@@ -125,8 +126,7 @@ silu_quant_kernel(GemvOut gate_up, uint32_t ffn, bool bf16, QuantSink sink, floa
   const uint32_t n4 = ffn / 4U;
   const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
   const bool valid = item < gate_up.batch * n4;
-  // the exact path (CUDA-core operand) takes exp from the deterministic series shared with the oracle
-  const bool exact = sink.kind == 0;
+  constexpr bool exact = kExact;
   const uint32_t row = valid ? item / n4 : 0U, f = valid ? item % n4 : 0U;
   float4 v = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
   if (valid) {
@@ -146,7 +146,11 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
   if (ffn % 16U) return fail(QLLM_INVALID_ARGUMENT, "FFN width must be a multiple of 16");
   const uint32_t items = gate_up.batch * (ffn / 4U);
   count_launch();
-  return check_cuda(launch_pdl(silu_quant_kernel, dim3((items + 255U) / 256U), dim3(256), 0, stream, gate_up, ffn,
+  // the exact path (CUDA-core operand) takes exp from the deterministic series shared with the oracle
+  if (sink.kind == 0)
+    return check_cuda(launch_pdl(silu_quant_kernel<true>, dim3((items + 255U) / 256U), dim3(256), 0, stream, gate_up, ffn,
+                                 bf16, sink, inter), "silu_quant");
+  return check_cuda(launch_pdl(silu_quant_kernel<false>, dim3((items + 255U) / 256U), dim3(256), 0, stream, gate_up, ffn,
                                bf16, sink, inter), "silu_quant");
 }
 
@@ -157,7 +161,9 @@ int launch_silu_quant(const GemvOut& gate_up, uint32_t ffn, bool bf16, const Qua
 constexpr uint32_t kCombineSplits = 512;
 
 // two CTAs per SM (128 registers): rows x heads CTAs of a verify pass then fit one wave
-template <bool kTiled>  // grid z = row tile of a wide pass
+// kExact: exp from the deterministic series shared with the CPU oracle (the parity path); its own
+// instantiation, because the benchmarked form sits exactly at its register limit
+template <bool kTiled, bool kExact>  // kTiled: grid z = row tile of a wide pass
 __global__ void __launch_bounds__(256, 2)
 combine_quant_kernel(CombineArgs c) {
   // CTA = (row, query head), 8 warps: warp w merges the splits s = w (mod 8); a lane owns
@@ -223,7 +229,7 @@ combine_quant_kernel(CombineArgs c) {
 #pragma unroll
     for (uint32_t b = 0; b < kBatch; ++b) {
       if (s0 + 8U * b >= active) break;
-      const float w = c.exact ? det_expf(smax[b] - m) : expf(smax[b] - m);
+      const float w = kExact ? det_expf(smax[b] - m) : expf(smax[b] - m);
       sum += static_cast<double>(ssum[b] * w);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -273,9 +279,12 @@ int launch_combine_quant(const CombineArgs& c, uint32_t rows, cudaStream_t strea
     return fail(QLLM_INVALID_ARGUMENT, "unsupported split count or head_dim for the combine");
   count_launch();
   if (c.tiles > 1U)
-    return check_cuda(launch_pdl(combine_quant_kernel<true>, dim3(c.q_heads, rows, c.tiles), dim3(64), 0, stream, c),
+    return check_cuda(c.exact ? launch_pdl(combine_quant_kernel<true, true>, dim3(c.q_heads, rows, c.tiles), dim3(64), 0, stream, c)
+                              : launch_pdl(combine_quant_kernel<true, false>, dim3(c.q_heads, rows, c.tiles), dim3(64), 0, stream, c),
                       "combine_quant");
-  return check_cuda(launch_pdl(combine_quant_kernel<false>, dim3(c.q_heads, rows), dim3(256), 0, stream, c), "combine_quant");
+  return check_cuda(c.exact ? launch_pdl(combine_quant_kernel<false, true>, dim3(c.q_heads, rows), dim3(256), 0, stream, c)
+                            : launch_pdl(combine_quant_kernel<false, false>, dim3(c.q_heads, rows), dim3(256), 0, stream, c),
+                    "combine_quant");
 }
 
 // --------------------------------------------------------- materialise a GEMV result

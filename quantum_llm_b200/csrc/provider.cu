@@ -635,6 +635,10 @@ struct qllm_provider {
       throw Error(QLLM_INVALID_ARGUMENT, "sampled exact decode requires bounded nonzero top-k");
     if (rq.reserved_context_tokens > cfg.max_context)
       throw Error(QLLM_INVALID_ARGUMENT, "request context exceeds the provider's max_context");
+    if (rq.sampling_presence_penalty_biased_ppm != 2000000U)
+      throw Error(QLLM_INVALID_ARGUMENT,
+                  "sampling presence penalty is not implemented by this provider (sampling_presence_penalty_biased_ppm "
+                  "must be 2000000, i.e. no penalty)");
     if (st.request_bound && !std::memcmp(&st.request, &rq, sizeof(rq))) return;
     StepState head{};
     head.seed = rq.sampling_seed;

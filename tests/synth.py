@@ -170,4 +170,4 @@ def prompt(vocab, count, seed):
 
 
 def request(seed=1234, temperature_ppm=0, top_p_ppm=950000, top_k=20, min_p_ppm=0, context_limit=256):
-    return ob.Request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit)
+    return ob.Request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit, 2000000)
