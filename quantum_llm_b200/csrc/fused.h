@@ -79,6 +79,11 @@ size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols);
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                      uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
                      float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream,
-                     const GemvExchange* exchange = nullptr);
+                     const GemvExchange* exchange = nullptr, const struct RopeTail* rope_tail = nullptr);
+// `rope_tail` (tensor-core kernel, decode steps): the projection is the fused q/k/v one and every
+// head is rotated, quantised and stored by the CTA that finishes it (rope_tail.cuh); the caller
+// then launches no separate RoPE / KV-store kernel.
+bool gemv_rope_tail_supported(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t batch, uint32_t head_dim,
+                              uint32_t rotary_dim);
 
 }  // namespace qllm

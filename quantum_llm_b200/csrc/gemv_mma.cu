@@ -24,6 +24,7 @@
 #include "fused.h"
 #include "gemv_mma.h"
 #include "launch.cuh"
+#include "rope_tail.cuh"
 
 namespace qllm {
 
@@ -313,14 +314,21 @@ struct GemvMmaParams {
 // its launch parameters.
 template <bool kExchange> struct ExchangeParam {};
 template <> struct ExchangeParam<true> { GemvExchange x; };
+// kRopeTail: the fused q/k/v projection of a decode step finishes every head itself -- the CTA
+// that takes the last ticket of a 128-row tile (= one head of head_dim 128) adds up the tile's
+// split-K partial sums, rotates the head and stores the INT8 query or the K/V record
+// (rope_tail.cuh), so no separate RoPE / KV-store kernel follows the GEMV.
+template <bool kRopeTail> struct TailParam {};
+template <> struct TailParam<true> { RopeTail t; };
 
 // kPartialK: K is not a whole number of 256-wide stages (the last stage issues fewer MMAs); its own
 // instantiation so that the common form carries no extra state.
-template <bool kExchange, bool kPartialK>
+template <bool kExchange, bool kPartialK, bool kRopeTail>
 __global__ void __launch_bounds__(128)
 nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
                       const __grid_constant__ CUtensorMap act_map, GemvMmaParams p,
-                      const __grid_constant__ ExchangeParam<kExchange> e) {
+                      const __grid_constant__ ExchangeParam<kExchange> e,
+                      const __grid_constant__ TailParam<kRopeTail> tail) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_trigger();  // the consumer kernel may be scheduled; it waits for this grid to finish
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
@@ -503,6 +511,37 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ CUtensorMap weight_map,
   __syncthreads();
   if (warp == 0U)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
+  if constexpr (kRopeTail) {
+    // every CTA of a tile has stored its partial sums (above); the last one to take the tile's
+    // ticket finishes the head.  Release: fence, then ticket; acquire: ticket, then fence.
+    __shared__ uint32_t last_of_tile;
+    __shared__ __align__(16) float head_rows[8][kTileRows];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0U) {
+      const bool last = finished && !*abort_flag && atomicAdd(tail.t.tickets + blockIdx.x, 1U) == p.split - 1U;
+      if (last) tail.t.tickets[blockIdx.x] = 0U;   // for the next launch (stream order)
+      last_of_tile = last ? 1U : 0U;
+    }
+    __syncthreads();
+    if (last_of_tile) {
+      __threadfence();
+      const uint32_t row = blockIdx.x * kTileRows + tid;       // output column of the projection
+      const size_t stride = static_cast<size_t>(p.batch) * p.row_count;
+      for (uint32_t b = 0; b < p.batch; ++b) {
+        float sum = 0.0F;
+        for (uint32_t sp = 0; sp < p.split; ++sp) sum += __ldcg(p.partials + sp * stride + static_cast<size_t>(b) * p.row_count + row);
+        head_rows[b][tid] = bf16r(sum * p.weight_scale / p.input_scale);
+      }
+      __syncthreads();
+      const uint32_t lane = tid & 31U;
+      for (uint32_t b = warp; b < p.batch; b += 4U) {
+        const float4 v = *reinterpret_cast<const float4*>(&head_rows[b][4U * lane]);
+        const float in[4] = {v.x, v.y, v.z, v.w};
+        rope_tail_head_row(tail.t, p.first_tile + blockIdx.x, b, in, lane);
+      }
+    }
+  }
   if (kExchange && tid == 0U) {
     // every thread of this CTA has read the sequence number (barrier above); the last CTA of the
     // launch advances it for the kernels that follow in the stream.  The values carry their own
@@ -529,7 +568,8 @@ __global__ void gemv_mma_finalize_kernel(const float* __restrict__ partials, flo
 
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr);
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange = nullptr,
+             const RopeTail* rope_tail = nullptr);
 
 int launch_gemv_mma(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count,
                     const float* x, float* y, uint32_t batch, void* workspace, size_t workspace_bytes,
@@ -583,7 +623,7 @@ int launch_gemv_mma_core_only(const MmaWeights& w, const qllm_matrix& m, uint32_
 // the result is left as split-K partials for the consumer; otherwise split == 1 writes y.
 int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint32_t row_count, uint32_t batch,
              const uint8_t* codes, const uint8_t* atoms, float* partials, float* y, uint32_t* error, bool raw,
-             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange) {
+             uint32_t* split_out, cudaStream_t stream, const GemvExchange* exchange, const RopeTail* rope_tail) {
   const uint32_t row_tiles = (row_count + kTileRows - 1U) / kTileRows;
   const uint32_t k_chunks = k_chunks_of(m.cols);
   const uint32_t n_pad = (batch + 15U) / 16U * 16U, n_tiles = (n_pad + 127U) / 128U;
@@ -614,13 +654,16 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   cudaGetDevice(&device);
   size_t& opted = opted_by_device[device & 63];
   if (smem > opted) {
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
+    if (rc) return rc;
+    rc = check_cuda(cudaFuncSetAttribute(nvfp4_gemv_mma_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)), "tensor-core GEMV shared memory opt-in");
     if (rc) return rc;
     opted = smem;
@@ -643,14 +686,23 @@ int mma_core(const MmaWeights& w, const qllm_matrix& m, uint32_t first_row, uint
   p.weight_scale = m.weight_scale;
   p.input_scale = m.input_scale;
   count_launch();
+  if (rope_tail != nullptr) {
+    if (exchange != nullptr || m.cols % kTileK || first_row != 0U || row_count % kTileRows || batch > 8U || !raw ||
+        rope_tail->a.head_dim != kTileRows || rope_tail->a.rotary_dim % 8U ||
+        row_count != (rope_tail->a.q_heads + 2U * rope_tail->a.kv_heads) * kTileRows || !rope_tail->tickets)
+      return fail(QLLM_INVALID_ARGUMENT, "the fused RoPE / KV-store tail needs head_dim 128, whole heads and at most 8 rows");
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, false, true>, dim3(row_tiles, split, n_tiles), dim3(128), smem,
+                                 stream, w.codes_map, act_map, p, ExchangeParam<false>{}, TailParam<true>{*rope_tail}),
+                      "nvfp4_gemv_mma");
+  }
   if (exchange != nullptr)
-    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true, true>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
-                                 w.codes_map, act_map, p, ExchangeParam<true>{*exchange}), "nvfp4_gemv_mma");
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<true, true, false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+                                 w.codes_map, act_map, p, ExchangeParam<true>{*exchange}, TailParam<false>{}), "nvfp4_gemv_mma");
   if (m.cols % kTileK)
-    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, true>, dim3(row_tiles, split, n_tiles), dim3(128), smem,
-                                 stream, w.codes_map, act_map, p, ExchangeParam<false>{}), "nvfp4_gemv_mma");
-  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
-                               w.codes_map, act_map, p, ExchangeParam<false>{}), "nvfp4_gemv_mma");
+    return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, true, false>, dim3(row_tiles, split, n_tiles), dim3(128), smem,
+                                 stream, w.codes_map, act_map, p, ExchangeParam<false>{}, TailParam<false>{}), "nvfp4_gemv_mma");
+  return check_cuda(launch_pdl(nvfp4_gemv_mma_kernel<false, false, false>, dim3(row_tiles, split, n_tiles), dim3(128), smem, stream,
+                               w.codes_map, act_map, p, ExchangeParam<false>{}, TailParam<false>{}), "nvfp4_gemv_mma");
 }
 
 // ---- operand buffers and the implementation-neutral GEMV core ---------------------------
@@ -679,6 +731,12 @@ QuantSink make_sink(int gemv_impl, void* quant_buffer, uint32_t rows, uint32_t c
   return s;
 }
 
+bool gemv_rope_tail_supported(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t batch, uint32_t head_dim,
+                              uint32_t rotary_dim) {
+  return gemv_impl == 1 && w.ready && m.cols % kTileK == 0U && m.rows % kTileRows == 0U && batch <= 8U &&
+         head_dim == kTileRows && rotary_dim % 8U == 0U;
+}
+
 size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
   if (cols % 64U) return static_cast<size_t>(batch) * rows;
   const uint32_t row_tiles = (rows + kTileRows - 1U) / kTileRows;
@@ -688,7 +746,7 @@ size_t gemv_partial_floats(uint32_t batch, uint32_t rows, uint32_t cols) {
 int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, uint32_t first_row,
                      uint32_t row_count, uint32_t batch, void* quant_buffer, float* partials,
                      float* final_out, uint32_t* error, GemvOut* out, cudaStream_t stream,
-                     const GemvExchange* exchange) {
+                     const GemvExchange* exchange, const RopeTail* rope_tail) {
   *out = GemvOut{};
   out->n = row_count;
   out->batch = batch;
@@ -698,7 +756,7 @@ int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, u
     const QuantSink s = make_sink(1, quant_buffer, batch, m.cols, m.input_scale);
     uint32_t split = 1;
     const int rc = mma_core(w, m, first_row, row_count, batch, s.codes, s.atoms, partials, nullptr, error, true,
-                            &split, stream, exchange);
+                            &split, stream, exchange, rope_tail);
     out->data = partials;
     out->split = split;
     if (exchange) {
@@ -709,6 +767,7 @@ int launch_gemv_core(int gemv_impl, const MmaWeights& w, const qllm_matrix& m, u
     return rc;
   }
   if (exchange) return fail(QLLM_INVALID_ARGUMENT, "the tensor-parallel exchange needs the tensor-core GEMV");
+  if (rope_tail) return fail(QLLM_INVALID_ARGUMENT, "the fused RoPE / KV-store tail needs the tensor-core GEMV");
   if (gemv_impl == 1)
     return fail(QLLM_INVALID_ARGUMENT, "shape is outside the tensor-core GEMV (K % 64, first row % 128, rows <= 128)");
   const int rc = launch_gemv_simt(m, first_row, row_count, quant_buffer, batch, final_out, batch, stream);

@@ -18,6 +18,7 @@
 #include "fused.h"
 #include "kernels.h"
 #include "moe.h"
+#include "rope_tail.cuh"
 
 namespace qllm {
 
@@ -163,6 +164,8 @@ struct qllm_provider {
   size_t tp_slot_pairs = 0;
   GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down)
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
+  DeviceBuffer<uint32_t> tile_tickets;         // per-tile arrival counters of the fused RoPE tail (zero between launches)
+  bool rope_tail_enabled = true;               // QLLM_ROPE_TAIL=0: always the separate RoPE / KV-store kernel
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
   DeviceBuffer<float> top_values;
@@ -297,6 +300,9 @@ struct qllm_provider {
     partial_buf.alloc(partial_floats, "split-K partial sums");
     gemv_out.alloc(static_cast<size_t>(R) * most_outputs, "GEMV results");
     // [0] status, [1] [2] the tensor-parallel exchange's sequence and ticket counters
+    tile_tickets.alloc(4096, "tile tickets");
+    cu(cudaMemsetAsync(tile_tickets.p, 0, 4096U * sizeof(uint32_t), stream), "tile tickets");
+    if (const char* env = std::getenv("QLLM_ROPE_TAIL")) rope_tail_enabled = env[0] != '0';
     kernel_error.alloc(4, "kernel status word");
     cu(cudaMemsetAsync(kernel_error.p, 0, 4U * sizeof(uint32_t), stream), "kernel status word");
     if (c.experts) {
@@ -341,7 +347,7 @@ struct qllm_provider {
   // ahead never writes the slot a slower peer is still reading (it cannot get two exchanges ahead:
   // every exchange is consumed, which needs the peers' parts, before the next but one is produced).
   GemvOut gemv(const Matrix& w, uint32_t rows, uint32_t row_count = 0, float* final_out = nullptr,
-               int exchange_slot = -1) {
+               int exchange_slot = -1, const RopeTail* rope_tail = nullptr) {
     if (!row_count) row_count = w.m.rows;
     GemvOut o{};
     const bool exchange = tp_ranks != 0U && exchange_slot >= 0;
@@ -349,7 +355,7 @@ struct qllm_provider {
       throw Error(QLLM_INVALID_ARGUMENT, "tensor-parallel provider used before qllm_provider_tp_attach");
     ok(launch_gemv_core(impl_for(w), w.mma, w.m, 0U, row_count, rows, quant_buf.p, partial_buf.p,
                         final_out ? final_out : gemv_out.p, kernel_error.p, &o, stream,
-                        exchange ? &tp_exchange[exchange_slot] : nullptr));
+                        exchange ? &tp_exchange[exchange_slot] : nullptr, rope_tail));
     return o;
   }
   // Fills the two per-slot exchange descriptors once all areas are mapped.
@@ -439,7 +445,11 @@ struct qllm_provider {
     const bool bf = c.activation_bf16 != 0U;
     norm_quant(h_valid ? h : nullptr, c.hidden, has_pending ? pending : nullptr, h, b.input_norm, &b.qkv, rows);
     RopeStoreFusedArgs rs{};
-    rs.qkv = gemv(b.qkv, rows);
+    // decode steps on the tensor-core GEMV: every head is rotated and stored by the GEMV CTA that
+    // finishes it; otherwise a RoPE / KV-store kernel consumes the projection
+    const bool fused_tail = rope_tail_enabled && rows <= kMaxRows &&
+                            gemv_rope_tail_supported(impl_for(b.qkv), b.qkv.mma, b.qkv.m, rows, c.head_dim, c.rotary_dim);
+    if (!fused_tail) rs.qkv = gemv(b.qkv, rows);
     rs.q_out = qkv.p;
     rs.base = RopeStoreArgs{nullptr, rows, c.q_heads, c.kv_heads, c.head_dim, c.rotary_dim, inv_freq.p,
                             first_position, position_offset, rotary_offset, st.page_table, layer_offset,
@@ -451,7 +461,12 @@ struct qllm_provider {
                                   tile_rows * (c.q_heads / c.kv_heads) <= 64U;
     rs.q8_out = tensor_attention ? q8.p : nullptr;
     rs.q8_scale = tensor_attention ? q8_scale.p : nullptr;
-    ok(launch_rope_kv_store_fused(rs, stream));
+    if (fused_tail) {
+      const RopeTail tail{rs.base, rs.q_out, rs.q8_out, rs.q8_scale, tile_tickets.p};
+      gemv(b.qkv, rows, 0U, nullptr, -1, &tail);
+    } else {
+      ok(launch_rope_kv_store_fused(rs, stream));
+    }
     const uint32_t qkv_w = c.q_heads * c.head_dim;  // rotated queries only
     // the full tiles go out as one launch (grid z = tile), a ragged last tile as a second one
     const uint32_t full_tiles = rows / tile_rows;

@@ -147,6 +147,27 @@ def test_head_dim_128_caches(kv_encoding, attention_impl):
         assert c["shared"] >= 8 and c["good"] >= 0.8 * c["shared"]
 
 
+@pytest.mark.parametrize("kv_encoding", [ob.KV_Q4H, ob.KV_F16])
+def test_rope_and_kv_store_fused_into_the_projection_give_the_same_bits(kv_encoding, monkeypatch):
+    # tensor-core GEMV, head_dim 128: the CTA that finishes a head of the fused q/k/v projection
+    # rotates and stores it itself.  Same arithmetic as the separate kernel -> same tokens, logits
+    # and cache bytes (target records and the Q8 records of the draft layer).
+    model = synth.SynthModel(dict(WIDE, kv_encoding=kv_encoding), seed=4)
+    prompt = synth.prompt(4096, 96, 4)
+    runs = []
+    for fused in ("1", "0"):
+        monkeypatch.setenv("QLLM_ROPE_TAIL", fused)
+        runs.append(run_gpu(model, prompt, 0, 24, graph=True, gemv_impl=1, attention_impl=1))
+    a, b = runs
+    assert a["stream"] == b["stream"] and a["drafts"] == b["drafts"]
+    for pos in a["rows"]:
+        assert np.array_equal(a["rows"][pos], b["rows"][pos])
+    for page in range(2):
+        assert np.array_equal(a["provider"].read_page(a["state"], page), b["provider"].read_page(b["state"], page))
+    launches = [r["provider"].telemetry(r["state"])["kernel_launches"] for r in runs]
+    print("kernel launches with / without the fused tail:", launches)
+
+
 def test_group_8_tensor_core_attention_inside_a_step():
     # 8 query heads on one kv head (the routed model's grouping: 40 matrix rows per kv head),
     # two layers, so that the second layer's records sit at a non-zero layer offset
