@@ -165,7 +165,10 @@ struct qllm_provider {
   GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down)
   DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
   DeviceBuffer<uint32_t> tile_tickets;         // per-tile arrival counters of the fused RoPE tail (zero between launches)
-  bool rope_tail_enabled = true;               // QLLM_ROPE_TAIL=0: always the separate RoPE / KV-store kernel
+  // QLLM_ROPE_TAIL=1: the q/k/v projection finishes every head itself (rope_tail.cuh).  Off by default:
+  // measured on the 27B step it saves a launch per block but costs what the separate kernel costs
+  // (qkv GEMV 10.4 -> 18.6 us against a 7.9 us RoPE kernel that overlaps its launch), 7.36 vs 7.00 ms per step.
+  bool rope_tail_enabled = false;
   DeviceBuffer<uint32_t> kernel_error;         // set by a kernel whose pipeline wait ran out
   DeviceBuffer<uint32_t> argmax_out, top_tokens, tokens_dev, first_token_dev;
   DeviceBuffer<float> top_values;
@@ -302,7 +305,7 @@ struct qllm_provider {
     // [0] status, [1] [2] the tensor-parallel exchange's sequence and ticket counters
     tile_tickets.alloc(4096, "tile tickets");
     cu(cudaMemsetAsync(tile_tickets.p, 0, 4096U * sizeof(uint32_t), stream), "tile tickets");
-    if (const char* env = std::getenv("QLLM_ROPE_TAIL")) rope_tail_enabled = env[0] != '0';
+    if (const char* env = std::getenv("QLLM_ROPE_TAIL")) rope_tail_enabled = env[0] == '1';
     kernel_error.alloc(4, "kernel status word");
     cu(cudaMemsetAsync(kernel_error.p, 0, 4U * sizeof(uint32_t), stream), "kernel status word");
     if (c.experts) {

@@ -329,7 +329,8 @@ def test_reference_gemv_time_on_this_gpu(R, L, capsys):
     # ANY FP32-accumulating kernel -- the reference's included -- differ from the oracle's by
     # percents of their RMS; that is the reference's own reproducibility, not a tolerance this
     # library may be held below.
-    om = ob.matrix(codes.cpu().numpy(), scales.cpu().numpy(), 1e-3, 336.0)
+    host_codes, host_scales = codes.cpu().numpy(), scales.cpu().numpy()   # kept alive: the oracle matrix holds pointers
+    om = ob.matrix(host_codes, host_scales, 1e-3, 336.0)
     want = ob.gemv(om, x.cpu().numpy())
     y0 = torch.empty_like(y)
     _okl(L, L.qllm_k_nvfp4_gemv(C.byref(cm), 0, rows, x.data_ptr(), y0.data_ptr(), batch, ws.data_ptr(), ws_bytes, 0, None)); _sync()
