@@ -160,6 +160,29 @@ int qllm_provider_prefill_chunk(qllm_provider* provider, qllm_request_state* sta
 int qllm_provider_first_token(qllm_provider* provider, qllm_request_state* state,
                               const qllm_request* request, uint32_t sample_position,
                               uint32_t* token);
+/* One non-speculative decode step: the runner's fallback when a request is not eligible for
+ * exact decode (session.execute({token, position}) followed by synchronize_exact_decode,
+ * moe_vm_runner.cpp:349-360 and :1151-1157; head sampling dense_fp4_provider.cpp:8433-8517,
+ * sample_token :771-802).  Runs `token` at `position` (the end of the cached stream) through the
+ * target model, selects the next token with the request's sampler at sample position
+ * `position` (dense_fp4_provider.cpp:10962-10964) -- greedy, sorted top-k (1..64), or the whole vocabulary ordered on the device
+ * when sampling_top_k is 0 or above 64 -- and advances the draft cache by a one-row
+ * synchronisation batch; produce_final_draft != 0 also primes the drafts (the request must then
+ * be one the speculative path accepts). */
+int qllm_provider_scalar_decode(qllm_provider* provider, qllm_request_state* state,
+                                const qllm_request* request, uint32_t token, uint32_t position,
+                                int produce_final_draft, uint32_t* next_token);
+/* IOperationProvider::checkpoint_request_state / rewind_request_state (program_executor.hpp,
+ * dense_fp4_provider.cpp:9209-9269 and :9271-9338) for a full-attention model.  A checkpoint
+ * can be taken at next_position == the length of the cached stream with no chunk waiting for
+ * its synchronisation batch; a rewind returns to exactly that position, drops the drafts and
+ * expects the stream to continue with a chunk or a scalar decode step at next_position.  The
+ * cache is rolled back by overwriting; the recurrent, PLE and sliding-window state the reference
+ * also copies belongs to model families this provider does not run. */
+int qllm_provider_checkpoint_request_state(qllm_provider* provider, qllm_request_state* state,
+                                           uint32_t next_position);
+int qllm_provider_rewind_request_state(qllm_provider* provider, qllm_request_state* state,
+                                       uint32_t next_position);
 /* IOperationProvider::synchronize_exact_decode_batch (program_executor.hpp:344;
  * dense_fp4_provider.cpp:11011-11137). next_tokens: host. */
 int qllm_provider_synchronize_exact_decode_batch(qllm_provider* provider,
@@ -353,7 +376,7 @@ int qllm_k_nvfp4_fake_quant(const float* x, float* out, uint32_t rows, uint32_t 
                             float global_scale, void* stream);
 /* nvfp4_gemv_f32_batch (transformer_kernels.cu:7970-8001): y[batch, row_count] =
  * bf16(fakequant(x) . W[first_row..]^T).  workspace: device scratch of at least
- * qllm_k_nvfp4_gemv_workspace_bytes(batch, cols) bytes. impl as in
+ * qllm_k_nvfp4_gemv_workspace_bytes(batch, row_count, cols) bytes. impl as in
  * qllm_provider_set_gemv_impl. */
 size_t qllm_k_nvfp4_gemv_workspace_bytes(uint32_t batch, uint32_t rows, uint32_t cols);
 int qllm_k_nvfp4_gemv(const qllm_matrix* matrix, uint32_t first_row, uint32_t row_count,
@@ -435,6 +458,15 @@ size_t qllm_k_topk_workspace_bytes(uint32_t rows, uint32_t count, uint32_t k);
 int qllm_k_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row_stride,
                 uint32_t k, float* out_values, uint32_t* out_tokens, void* workspace,
                 void* stream);
+/* sample_token (dense_fp4_provider.cpp:771-802): every id ordered by (logit descending, NaN last,
+ * id ascending), the first top_k kept (0 = all), make_sampling_distribution and
+ * sample_distribution (speculative_sampling.cpp:52-128) with counter_uniform(seed, position, 0).
+ * logits, workspace (qllm_k_sample_token_workspace_bytes), status and token are device pointers;
+ * *status = 5 where the reference throws "no retained mass" / "invalid sorted sampling candidates". */
+size_t qllm_k_sample_token_workspace_bytes(uint32_t vocabulary);
+int qllm_k_sample_token(const float* logits, uint32_t vocabulary, uint64_t seed, uint32_t temperature_ppm,
+                        uint32_t top_p_ppm, uint32_t top_k, uint32_t min_p_ppm, uint32_t position,
+                        void* workspace, uint32_t* status, uint32_t* token, void* stream);
 /* Device form of rejection_sample / make_sampling_distribution / counter_uniform
  * (runtime/src/speculative_sampling.cpp:52-182) over host-visible arrays, for the
  * parity tests of the acceptance kernel: one decision per call.

@@ -128,6 +128,7 @@ def lib():
             "qo_make_distribution": (C.c_int, [vp, vp, u32, u32, u32, u32, vp, vp]),
             "qo_sample_distribution": (u32, [vp, vp, u32, f64]),
             "qo_rejection_sample": (C.c_int, [u32, vp, vp, u32, vp, vp, u32, f64, f64, vp]),
+            "qo_sample_token": (C.c_int, [vp, u32, C.POINTER(Request), u32, vp]),
             "qo_session_create": (vp, [C.POINTER(Config), C.POINTER(Weights)]),
             "qo_session_destroy": (None, [vp]),
             "qo_prefill": (C.c_int, [vp, vp, u32, u32, C.POINTER(Request), vp]),
@@ -234,6 +235,14 @@ def make_distribution(logits, tokens, temperature_ppm, top_p_ppm, min_p_ppm, imp
     if n < 0:
         return None
     return ot[:n].copy(), op[:n].copy()
+
+
+def sample_token(logits, request, position):
+    """The scalar decode fallback's sampler over a whole logits row; None where the reference throws."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    token = C.c_uint32(0)
+    rc = lib().qo_sample_token(_ptr(logits), logits.size, C.byref(request), int(position), C.byref(token))
+    return token.value if rc == 0 else None
 
 
 def rejection_sample(proposal, target, draft, ua, uc, impl=None):

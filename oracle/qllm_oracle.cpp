@@ -1055,6 +1055,39 @@ uint32_t qo_sample_distribution(const uint32_t* tokens, const double* probs, uin
   Dist d{std::vector<uint32_t>(tokens, tokens + count), std::vector<double>(probs, probs + count)};
   return sample_distribution(d, u);
 }
+// sample_token, runtime/tools/dense_fp4_provider.cpp:771-802 (the scalar decode fallback's sampler
+// for top_k == 0 or > 64) with sample_sorted_candidates :748-769.  The reference's comparator leaves
+// the order among NaN logits open; here they follow each other by id (their weight is 0 either way).
+int qo_sample_token(const float* logits, uint32_t vocabulary, const qo_request* rq, uint32_t position,
+                    uint32_t* token) {
+  try {
+    if (!vocabulary || rq->top_k > vocabulary) throw std::invalid_argument("invalid token sampling contract");
+    const size_t candidate_count = rq->top_k == 0U ? vocabulary : rq->top_k;
+    std::vector<uint32_t> candidates(vocabulary);
+    for (uint32_t i = 0; i < vocabulary; ++i) candidates[i] = i;
+    const auto greater_logit = [&](uint32_t left, uint32_t right) {
+      const float a = logits[left], b = logits[right];
+      if (std::isnan(a) || std::isnan(b)) return std::isnan(a) == std::isnan(b) ? left < right : std::isnan(b);
+      return a == b ? left < right : a > b;
+    };
+    if (candidate_count != candidates.size()) {
+      std::partial_sort(candidates.begin(), candidates.begin() + static_cast<long>(candidate_count), candidates.end(),
+                        greater_logit);
+      candidates.resize(candidate_count);
+    } else {
+      std::sort(candidates.begin(), candidates.end(), greater_logit);
+    }
+    std::vector<float> sorted(candidates.size());
+    for (size_t i = 0; i < candidates.size(); ++i) sorted[i] = logits[candidates[i]];
+    const Dist d = make_distribution(sorted.data(), candidates.data(), static_cast<uint32_t>(candidates.size()),
+                                     rq->temperature_ppm, rq->top_p_ppm, rq->min_p_ppm);
+    *token = sample_distribution(d, counter_uniform(rq->seed, position, 0U, 0U));
+    return 0;
+  } catch (const std::exception& e) {
+    g_error = e.what();
+    return -1;
+  }
+}
 int qo_rejection_sample(uint32_t proposal, const uint32_t* tt, const double* tp, uint32_t tc,
                         const uint32_t* dt, const double* dp, uint32_t dc, double ua, double uc,
                         uint32_t* token) {

@@ -173,6 +173,11 @@ int qo_make_distribution(const float* sorted_logits,
 uint32_t qo_sample_distribution(const uint32_t* tokens,
                                 const double* probabilities, uint32_t count,
                                 double uniform);
+/* sample_token (dense_fp4_provider.cpp:771-802): full-vocabulary ordering, the first top_k kept
+ * (0 = all), distribution and sample at counter_uniform(seed, position, 0).  0, or -1 on the
+ * inputs the reference throws on. */
+int qo_sample_token(const float* logits, uint32_t vocabulary, const qo_request* request,
+                    uint32_t position, uint32_t* token);
 /* returns 1 accepted, 0 rejected (token = residual sample), -1 error */
 int qo_rejection_sample(uint32_t proposal, const uint32_t* target_tokens,
                         const double* target_probabilities,

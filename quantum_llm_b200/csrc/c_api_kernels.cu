@@ -230,4 +230,16 @@ int qllm_k_topk(const float* values, uint32_t rows, uint32_t count, uint32_t row
                      static_cast<cudaStream_t>(stream));
 }
 
+size_t qllm_k_sample_token_workspace_bytes(uint32_t vocabulary) { return full_sampler_workspace_bytes(vocabulary); }
+
+int qllm_k_sample_token(const float* logits, uint32_t vocabulary, uint64_t seed, uint32_t temperature_ppm,
+                        uint32_t top_p_ppm, uint32_t top_k, uint32_t min_p_ppm, uint32_t position,
+                        void* workspace, uint32_t* status, uint32_t* token, void* stream) {
+  if (!logits || !vocabulary || !workspace || !status || !token || top_k > vocabulary)
+    return fail(QLLM_INVALID_ARGUMENT, "invalid token sampling contract");
+  const FullSampleParams q{seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, position};
+  return launch_full_vocabulary_sample(q, logits, vocabulary, workspace, status, token,
+                                       static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -184,5 +184,16 @@ int launch_draft_sample(const DraftSampleArgs& a, cudaStream_t stream);
 int launch_first_token(StepState* state, const uint32_t* argmax_token, const float* top_values,
                        const uint32_t* top_tokens, uint32_t sample_position, uint32_t* out,
                        cudaStream_t stream);
+// Scalar decode fallback (top_k == 0 or > 64): full-vocabulary ordering + the sequential
+// double-precision distribution of sample_token (dense_fp4_provider.cpp:771-802) on the device.
+struct FullSampleParams {
+  unsigned long long seed;
+  uint32_t temperature_ppm, top_p_ppm, top_k, min_p_ppm;   // top_k 0 = the whole vocabulary
+  uint32_t sample_position;
+};
+size_t full_sampler_workspace_bytes(uint32_t vocab);
+// *error = 5 when the candidates hold no finite mass (the reference throws); *out: the token.
+int launch_full_vocabulary_sample(const FullSampleParams& q, const float* logits, uint32_t vocab, void* workspace,
+                                  uint32_t* error, uint32_t* out, cudaStream_t stream);
 
 }  // namespace qllm

@@ -115,6 +115,8 @@ struct qllm_request_state {
   uint32_t retained_rows = 0;
   uint32_t retained_first = 0;
   uint32_t ring_cursor = 0;  // host mirror of StepState::step_index
+  uint32_t retention_position = 0;  // checkpoint_request_state / rewind_request_state
+  bool retention_valid = false;
   bool request_bound = false;
   qllm_request request{};
   cudaGraphExec_t step_graph = nullptr;
@@ -133,7 +135,7 @@ struct qllm_provider {
   int device = 0;
   bool borrowed = false;
   cudaStream_t stream = nullptr;
-  std::mutex mutex;
+  std::recursive_mutex mutex;   // recursive: the scalar decode step is composed of the chunk, token and synchronisation calls
   std::vector<void*> owned;          // uploads
   const uint16_t* embedding = nullptr;
   std::vector<Block> layers;
@@ -163,7 +165,7 @@ struct qllm_provider {
   bool tp_local = false;                       // peers' areas are plain device pointers (not IPC mappings)
   size_t tp_slot_pairs = 0;
   GemvExchange tp_exchange[2] = {};            // per inbox slot (o, down)
-  DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf;
+  DeviceBuffer<uint8_t> attn_ws, topk_ws, quant_buf, full_sampler_ws;
   DeviceBuffer<uint32_t> tile_tickets;         // per-tile arrival counters of the fused RoPE tail (zero between launches)
   // QLLM_ROPE_TAIL=1: the q/k/v projection finishes every head itself (rope_tail.cuh).  Off by default:
   // measured on the 27B step it saves a launch per block but costs what the separate kernel costs
@@ -321,6 +323,7 @@ struct qllm_provider {
     max_splits = (c.max_context + 2U * kMaxRows + c.split_tokens - 1U) / c.split_tokens;
     attn_ws.alloc(attention_workspace_bytes(R, c.q_heads, c.head_dim, max_splits), "attention partials");
     topk_ws.alloc(topk_workspace_bytes(H, c.vocab, 64), "top-k partials");
+    full_sampler_ws.alloc(full_sampler_workspace_bytes(c.vocab), "full-vocabulary sampler workspace");
     argmax_out.alloc(H, "argmax");
     top_tokens.alloc(static_cast<size_t>(H) * 64U, "top-k tokens");
     top_values.alloc(static_cast<size_t>(H) * 64U, "top-k values");
@@ -644,13 +647,18 @@ struct qllm_provider {
     rollout(st, mtp_splits, sampled, top_k);
   }
 
-  void bind_request(qllm_request_state& st, const qllm_request& rq) {
+  // `bounded_top_k`: the speculative path (acceptance over sorted top-k lists) needs 0 < top_k <= 64;
+  // the scalar decode fallback samples from the whole vocabulary and takes any top_k <= vocab.
+  void bind_request(qllm_request_state& st, const qllm_request& rq, bool bounded_top_k = true) {
     if (rq.sampling_temperature_ppm > 2000000U ||
         (rq.sampling_temperature_ppm != 0U &&
-         (rq.sampling_top_k == 0U || rq.sampling_top_k > 64U || rq.sampling_top_k > cfg.draft_vocab ||
-          rq.sampling_top_p_ppm == 0U || rq.sampling_top_p_ppm > 1000000U ||
-          rq.sampling_min_p_ppm > 1000000U)))
+         (rq.sampling_top_p_ppm == 0U || rq.sampling_top_p_ppm > 1000000U || rq.sampling_min_p_ppm > 1000000U)))
+      throw Error(QLLM_INVALID_ARGUMENT, "invalid token sampling contract");
+    if (rq.sampling_temperature_ppm != 0U && bounded_top_k &&
+        (rq.sampling_top_k == 0U || rq.sampling_top_k > 64U || rq.sampling_top_k > cfg.draft_vocab))
       throw Error(QLLM_INVALID_ARGUMENT, "sampled exact decode requires bounded nonzero top-k");
+    if (rq.sampling_temperature_ppm != 0U && rq.sampling_top_k > cfg.vocab)
+      throw Error(QLLM_INVALID_ARGUMENT, "invalid token sampling contract");
     if (rq.reserved_context_tokens > cfg.max_context)
       throw Error(QLLM_INVALID_ARGUMENT, "request context exceeds the provider's max_context");
     if (rq.sampling_presence_penalty_biased_ppm != 2000000U)
@@ -728,7 +736,7 @@ int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** ou
   *out = nullptr;
   auto st = std::make_unique<qllm_request_state>();
   const int rc = guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     st->pages = (c.max_context + 2U * qllm_provider::kMaxRows + c.page_tokens - 1U) / c.page_tokens;
@@ -774,7 +782,7 @@ int qllm_provider_prefill_chunk(qllm_provider* p, qllm_request_state* st, const 
                                 uint32_t count, uint32_t first_position) {
   if (!p || !st || !tokens) return fail(QLLM_INVALID_ARGUMENT, "null prefill argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     if (!count || count > p->chunk_limit() || first_position + count > c.max_context)
@@ -798,16 +806,24 @@ int qllm_provider_first_token(qllm_provider* p, qllm_request_state* st, const ql
                               uint32_t sample_position, uint32_t* token) {
   if (!p || !st || !rq || !token) return fail(QLLM_INVALID_ARGUMENT, "null first-token argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     if (!st->retained_rows) throw Error(QLLM_INVALID_ARGUMENT, "no prefill rows retained");
-    p->bind_request(*st, *rq);
+    p->bind_request(*st, *rq, false);
     const bool sampled = rq->sampling_temperature_ppm != 0U;
     const float* row = p->logits.p + static_cast<size_t>(st->retained_logits_row) * c.vocab;
-    p->select_candidates(row, 1, c.vocab, c.vocab, sampled, rq->sampling_top_k);
-    ok(launch_first_token(st->state, p->argmax_out.p, p->top_values.p, p->top_tokens.p, sample_position,
-                          p->first_token_dev.p, p->stream));
+    if (sampled && (rq->sampling_top_k == 0U || rq->sampling_top_k > 64U)) {
+      // no truncation, or more candidates than the sorted top-k kernels hold: order the whole row
+      const FullSampleParams q{rq->sampling_seed, rq->sampling_temperature_ppm, rq->sampling_top_p_ppm,
+                               rq->sampling_top_k, rq->sampling_min_p_ppm, sample_position};
+      ok(launch_full_vocabulary_sample(q, row, c.vocab, p->full_sampler_ws.p, &st->state->error,
+                                       p->first_token_dev.p, p->stream));
+    } else {
+      p->select_candidates(row, 1, c.vocab, c.vocab, sampled, rq->sampling_top_k);
+      ok(launch_first_token(st->state, p->argmax_out.p, p->top_values.p, p->top_tokens.p, sample_position,
+                            p->first_token_dev.p, p->stream));
+    }
     cu(cudaMemcpyAsync(token, p->first_token_dev.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, p->stream), "copy first token");
     check_device_error(*p, *st);
   });
@@ -819,7 +835,7 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
                                                  int produce_final_draft) {
   if (!p || !st || !rq || !next_tokens) return fail(QLLM_INVALID_ARGUMENT, "null synchronization argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     if (!count || count > p->chunk_limit() || count != st->retained_rows ||
@@ -828,9 +844,9 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
       throw Error(QLLM_INVALID_ARGUMENT, "MTP synchronization stream is invalid");
     for (uint32_t r = 0; r < count; ++r)
       if (next_tokens[r] >= c.vocab) throw Error(QLLM_INVALID_ARGUMENT, "MTP synchronization stream is invalid");
-    p->bind_request(*st, *rq);
-    const bool sampled = rq->sampling_temperature_ppm != 0U;
     const bool produce = produce_final_draft != 0;
+    p->bind_request(*st, *rq, produce);
+    const bool sampled = rq->sampling_temperature_ppm != 0U;
     if (produce && (rq->reserved_context_tokens > c.max_context ||
                     first_target_position + count + 1U >= rq->reserved_context_tokens))
       throw Error(QLLM_INVALID_ARGUMENT, "MTP rollout root exceeds context");
@@ -932,13 +948,74 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
   st->draft_valid = drafts != 0U;
 }
 
+// checkpoint_request_state (dense_fp4_provider.cpp:9209-9269) for a full-attention model: the cache
+// is append-only and rolled back by overwriting, so the checkpoint is the position itself; the
+// reference additionally copies recurrent, PLE and sliding-window state, which this provider's
+// models do not have.
+int qllm_provider_checkpoint_request_state(qllm_provider* p, qllm_request_state* st, uint32_t next_position) {
+  if (!p || !st) return fail(QLLM_INVALID_ARGUMENT, "null retention argument");
+  return guarded([&] {
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
+    if (next_position == 0U || next_position > p->cfg.max_context || st->retained_rows != 0U)
+      throw Error(QLLM_INVALID_ARGUMENT, "retention checkpoint position is invalid");
+    if (st->retention_position == next_position && st->mtp_length != next_position) {
+      st->retention_valid = true;   // the state has moved on; the older checkpoint is declared valid again
+      return;
+    }
+    if (st->mtp_length != next_position)
+      throw Error(QLLM_INVALID_ARGUMENT, "retention checkpoint position is invalid");
+    st->retention_position = next_position;
+    st->retention_valid = true;
+  });
+}
+
+// rewind_request_state (dense_fp4_provider.cpp:9271-9338): back to the checkpointed position; the
+// drafts are dropped, so the next call is a chunk (or a scalar decode step) at next_position
+// followed by a synchronisation batch that primes the drafts again.
+int qllm_provider_rewind_request_state(qllm_provider* p, qllm_request_state* st, uint32_t next_position) {
+  if (!p || !st) return fail(QLLM_INVALID_ARGUMENT, "null retention argument");
+  return guarded([&] {
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
+    cu(cudaSetDevice(p->device), "select device");
+    if (!st->retention_valid || st->retention_position != next_position || st->retained_rows != 0U)
+      throw Error(QLLM_INVALID_ARGUMENT, "retention rewind position is invalid");
+    st->mtp_length = next_position;
+    st->draft_valid = false;
+    st->draft_count = 0U;
+    st->retained_rows = 0U;
+    p->poke(&st->state->position, next_position);
+    p->poke(&st->state->draft_count, 0U);
+  });
+}
+
+// One non-speculative decode step (the runner's start_step fallback, moe_vm_runner.cpp:349-360 and
+// 1151-1157): the token at `position` through the target model, the next token chosen by the
+// request's sampler -- any top_k, the whole vocabulary included -- at sample position `position`
+// (run_head is called with current_position, dense_fp4_provider.cpp:10962-10964), and the draft
+// cache kept in step by a one-row synchronisation batch
+// (produce_final_draft as in qllm_provider_synchronize_exact_decode_batch; it needs a request the
+// speculative path accepts).
+int qllm_provider_scalar_decode(qllm_provider* p, qllm_request_state* st, const qllm_request* rq,
+                                uint32_t token, uint32_t position, int produce_final_draft,
+                                uint32_t* next_token) {
+  if (!p || !st || !rq || !next_token) return fail(QLLM_INVALID_ARGUMENT, "null scalar-decode argument");
+  std::lock_guard<std::recursive_mutex> lock(p->mutex);
+  if (st->retained_rows != 0U || position != st->mtp_length)
+    return fail(QLLM_INVALID_ARGUMENT, "scalar decode position is not the end of the cached stream");
+  int rc = qllm_provider_prefill_chunk(p, st, &token, 1U, position);
+  if (rc) return rc;
+  rc = qllm_provider_first_token(p, st, rq, position, next_token);
+  if (rc) { st->retained_rows = 0U; return rc; }
+  return qllm_provider_synchronize_exact_decode_batch(p, st, rq, next_token, 1U, position, produce_final_draft);
+}
+
 int qllm_provider_execute_exact_decode(qllm_provider* p, qllm_request_state* st,
                                        const qllm_request* rq, uint32_t guaranteed_token,
                                        uint32_t position, uint32_t context_limit,
                                        qllm_exact_result* result) {
   if (!p || !st || !rq || !result) return fail(QLLM_INVALID_ARGUMENT, "null exact-decode argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     if (!st->draft_valid || guaranteed_token != st->synchronized_token || position != st->mtp_length ||
         position + 1U >= context_limit || context_limit > p->cfg.max_context ||
@@ -962,7 +1039,7 @@ int qllm_provider_execute_exact_decode_steps(qllm_provider* p, qllm_request_stat
                                              uint32_t steps, qllm_exact_result* results) {
   if (!p || !st || !rq || !results) return fail(QLLM_INVALID_ARGUMENT, "null exact-decode argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     if (!st->draft_valid || context_limit > p->cfg.max_context || context_limit != rq->reserved_context_tokens)
       throw Error(QLLM_INVALID_ARGUMENT, "exact MTP invocation stream is invalid");
@@ -1112,7 +1189,7 @@ int qllm_provider_time_verify(qllm_provider* p, qllm_request_state* st, const ql
                               float* mean_ms) {
   if (!p || !st || !rq || !mean_ms || !repeats) return fail(QLLM_INVALID_ARGUMENT, "null verify-timing argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     if (!st->draft_valid) throw Error(QLLM_INVALID_ARGUMENT, "no drafts are pending: nothing to verify");
@@ -1179,7 +1256,7 @@ int qllm_provider_fill_synthetic_kv(qllm_provider* p, qllm_request_state* st, ui
                                     uint32_t count, uint64_t seed) {
   if (!p || !st) return fail(QLLM_INVALID_ARGUMENT, "null synthetic-fill argument");
   return guarded([&] {
-    std::lock_guard<std::mutex> lock(p->mutex);
+    std::lock_guard<std::recursive_mutex> lock(p->mutex);
     cu(cudaSetDevice(p->device), "select device");
     const auto& c = p->cfg;
     if (first != st->mtp_length || first + count > c.max_context)

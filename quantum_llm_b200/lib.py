@@ -87,6 +87,9 @@ SIGNATURES = {
     "qllm_provider_destroy_request_state": (None, [vp, vp]),
     "qllm_provider_prefill_chunk": (ci, [vp, vp, vp, u32, u32]),
     "qllm_provider_first_token": (ci, [vp, vp, P(Request), u32, P(u32)]),
+    "qllm_provider_scalar_decode": (ci, [vp, vp, P(Request), u32, u32, ci, P(u32)]),
+    "qllm_provider_checkpoint_request_state": (ci, [vp, vp, u32]),
+    "qllm_provider_rewind_request_state": (ci, [vp, vp, u32]),
     "qllm_provider_synchronize_exact_decode_batch": (ci, [vp, vp, P(Request), vp, u32, u32, ci]),
     "qllm_provider_execute_exact_decode": (ci, [vp, vp, P(Request), u32, u32, u32, P(ExactResult)]),
     "qllm_provider_execute_exact_decode_steps": (ci, [vp, vp, P(Request), u32, u32, P(ExactResult)]),
@@ -140,6 +143,8 @@ SIGNATURES = {
     "qllm_k_argmax": (ci, [vp, u32, u32, u32, vp, vp]),
     "qllm_k_topk_workspace_bytes": (sz, [u32, u32, u32]),
     "qllm_k_topk": (ci, [vp, u32, u32, u32, u32, vp, vp, vp, vp]),
+    "qllm_k_sample_token_workspace_bytes": (sz, [u32]),
+    "qllm_k_sample_token": (ci, [vp, u32, u64, u32, u32, u32, u32, u32, vp, vp, vp, vp]),
     "qllm_k_rejection_sample_host": (ci, [u32, vp, vp, u32, vp, vp, u32, f64, f64, P(u32)]),
     "qllm_k_make_distribution_host": (ci, [vp, vp, u32, u32, u32, u32, vp, vp]),
     "qllm_k_counter_uniform_host": (ci, [u64, u32, u32, u32, P(f64)]),

@@ -112,6 +112,21 @@ class Nvfp4MtpProvider:
         _l.check(self.L.qllm_provider_first_token(self.h, state.h, C.byref(rq), sample_position, C.byref(token)))
         return token.value
 
+    def scalar_decode(self, state, request, token, position, produce_final_draft=False):
+        """One non-speculative step: `token` at `position` through the target, next token by the
+        request's sampler (any top_k), draft cache advanced by a one-row synchronisation batch."""
+        nxt = C.c_uint32(0)
+        rq = request.c()
+        _l.check(self.L.qllm_provider_scalar_decode(self.h, state.h, C.byref(rq), token, position,
+                                                    1 if produce_final_draft else 0, C.byref(nxt)))
+        return nxt.value
+
+    def checkpoint_request_state(self, state, next_position):
+        _l.check(self.L.qllm_provider_checkpoint_request_state(self.h, state.h, next_position))
+
+    def rewind_request_state(self, state, next_position):
+        _l.check(self.L.qllm_provider_rewind_request_state(self.h, state.h, next_position))
+
     def synchronize_exact_decode_batch(self, state, request, next_tokens, first_target_position,
                                        produce_final_draft):
         next_tokens = np.ascontiguousarray(next_tokens, np.uint32)

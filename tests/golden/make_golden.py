@@ -8,6 +8,7 @@ JSON.
                       (runtime/src/speculative_sampling.cpp through oracle/_ref)
                       on seeded inputs
 """
+import ctypes as C
 import json
 import os
 import sys
@@ -66,7 +67,45 @@ def sampler_cases():
         r, token = ob.rejection_sample(proposal, target, draft, ua, uc, impl=ref)
         rejections.append({"proposal": proposal, "target": target, "draft": draft, "ua": ua, "uc": uc,
                            "accepted": r, "token": token})
-    return {"counter_uniform": uniforms, "distributions": dists, "rejections": rejections}
+    return {"counter_uniform": uniforms, "distributions": dists, "rejections": rejections,
+            "sample_token": sample_token_cases(ref, ob)}
+
+
+def sample_token_cases(ref, ob):
+    """sample_token (runtime/tools/dense_fp4_provider.cpp:771-802) composed from the reference's own
+    functions: numpy orders the ids by the reference's comparator (logit descending, NaN last, id
+    ascending), the reference's make_sampling_distribution / sample_distribution /
+    counter_uniform do the rest.  Rows carry ties, infinities and (some) NaNs."""
+    rng = np.random.default_rng(21)
+    cases = []
+    for case in range(40):
+        n = int(rng.integers(70, 400))
+        logits = rng.normal(0, 2.5, n).astype(np.float32)
+        logits[rng.integers(0, n, 6)] = logits[int(rng.integers(0, n))]       # ties
+        if case % 4 == 1:
+            logits[rng.integers(0, n, 3)] = -np.inf
+        if case % 4 == 2:
+            logits[rng.integers(0, n, 2)] = np.nan
+        if case % 8 == 7:
+            logits[int(rng.integers(0, n))] = 0.0
+            logits[int(rng.integers(0, n))] = -0.0
+        top_k = min(n, [0, 0, 65, 100, n][case % 5])
+        t_ppm = int(rng.choice([300000, 700000, 1000000, 2000000]))
+        p_ppm = int(rng.choice([500000, 900000, 1000000]))
+        m_ppm = int(rng.choice([0, 0, 20000]))
+        seed, position = int(rng.integers(0, 2**63)), int(rng.integers(0, 2**20))
+        nan = np.isnan(logits)
+        order = np.lexsort((np.arange(n), -np.where(nan, 0, logits).astype(np.float64), nan))
+        keep = order[:top_k or n].astype(np.uint32)
+        d = ob.make_distribution(logits[keep], keep, t_ppm, p_ppm, m_ppm, impl=ref)
+        u = ref.ref_counter_uniform(seed, position, 0, 0)
+        token = C.c_uint32(0)
+        tt, tp = np.ascontiguousarray(d[0], np.uint32), np.ascontiguousarray(d[1], np.float64)
+        assert ref.ref_sample_distribution(tt.ctypes.data, tp.ctypes.data, len(tt), u, C.byref(token)) == 0
+        cases.append({"logits_f32_bits": [int(x) for x in logits.view(np.uint32)], "top_k": top_k,
+                      "temperature_ppm": t_ppm, "top_p_ppm": p_ppm, "min_p_ppm": m_ppm, "seed": seed,
+                      "position": position, "token": int(token.value), "retained": len(tt)})
+    return cases
 
 
 if __name__ == "__main__":

@@ -87,6 +87,22 @@ def test_rejection_matches_reference_vectors(golden_dir):
         assert (r, token) == (case["accepted"], case["token"])
 
 
+def test_sample_token_matches_reference_vectors(golden_dir):
+    """The scalar decode fallback's sampler (whole-row ordering, top_k 0 or above 64) against
+    tokens produced by the reference's own distribution / sampling / counter functions."""
+    cases = json.load(open(os.path.join(golden_dir, "sampler_cases.json")))["sample_token"]
+    assert len(cases) >= 40
+    for case in cases:
+        logits = np.array(case["logits_f32_bits"], np.uint32).view(np.float32)
+        rq = ob.Request(case["seed"], case["temperature_ppm"], case["top_p_ppm"], case["top_k"], case["min_p_ppm"],
+                        0, 2000000)
+        assert ob.sample_token(logits, rq, case["position"]) == case["token"]
+    # what the reference throws on: no finite maximum, top_k beyond the row
+    rq = ob.Request(1, 700000, 900000, 0, 0, 0, 2000000)
+    assert ob.sample_token(np.full(100, -np.inf, np.float32), rq, 3) is None
+    assert ob.sample_token(np.zeros(10, np.float32), ob.Request(1, 700000, 900000, 11, 0, 0, 2000000), 3) is None
+
+
 def test_nucleus_known_answer():
     # runtime/tests/cache_state_test.cpp:105-114
     tokens, probs = ob.make_distribution([4.0, 3.0, 2.0, 1.0], [9, 5, 2, 1], 1_000_000, 800_000, 0)
