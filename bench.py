@@ -220,6 +220,29 @@ class OracleSteps:
         return seconds, int(r.positions_advanced)
 
 
+def reference_cpu_ffn(cfg, threads):
+    """Second CPU figure: the reference's OWN host code (Fp4HostExecutor, runtime/src/cpu/
+    fp4_host_executor.cpp, compiled unmodified into oracle/_ref) running one FFN layer of the
+    workload's widths over the 5 verify rows.  Its weight format is the reference's CPU-lane FP4
+    (E2M1 with one UE8M0 scale per 32 values, Q8 activations), not NVFP4 block-16, so this is a
+    throughput figure for the same layer shape, not the same arithmetic.  None when not built."""
+    import ctypes as C
+    from oracle import binding as ob
+    R = ob.ref_fp4_host()
+    if R is None:
+        return None
+    H, F, rows, threads = cfg["hidden"], cfg["ffn"], cfg["draft_depth"] + 1, max(1, min(int(threads), 64))
+    checksum = C.c_double(0.0)
+    seconds = R.ref_fp4_host_ffn_seconds(H, F, rows, threads, 20, 7, C.byref(checksum))
+    if not seconds > 0.0:
+        return None
+    layer_bytes = 3 * H * F * 17 // 32          # 4-bit codes + one scale byte per 32
+    return {"kind": "_ref", "what": "Fp4HostExecutor, one SwiGLU FFN layer (gate, up, down) of the workload's widths, "
+            f"{rows} rows, FP4 block-32 weights (the reference's CPU lane format), mean of 20 runs",
+            "ms_per_ffn_layer": seconds * 1e3, "gb_per_s": layer_bytes / seconds / 1e9, "cores": threads,
+            "gpu_ffn_layer_note": "the GPU path's FFN layer at the same widths is the gate/up GEMV + SiLU + down GEMV"}
+
+
 def algorithmic_step_bytes(cfg, context):
     """Bytes one MTP-4 step must read: verify weights + target KV + 4 draft passes."""
     nv = lambda r, c: r * c * 9 // 16   # NVFP4: 4-bit codes + one E4M3 scale per 16
@@ -272,7 +295,8 @@ def reference_arm(args):
                        "layers_of_the_model": DENSE_27B["layers"],
                        "parallelism": "host cores of rank 0", "implementation": "CPU port of the reference arithmetic"},
             "accepted_len_per_step": tokens / args.steps,
-            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.threads, "kind": "port", "sample": text},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.threads, "kind": "port", "sample": text,
+                             "reference_ffn": reference_cpu_ffn(DENSE_27B, sample.threads)},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -600,6 +624,20 @@ def ours(args):
             seconds, tokens, steps = seconds + s, tokens + n, steps + 1
         line["cpu_baseline"] = {"value": tokens / seconds, "unit": "tok/s", "cores": sample.threads, "kind": "port",
                                 "sample": f"{sample.description}; {steps} steps in {seconds:.1f} s"}
+        # what a whole 64-layer step would take, from two MEASURED slices (1 and 2 layers): the time one
+        # more layer adds, times the layers left out -- reported beside the measured value, not in its place
+        per_step = seconds / steps
+        del sample
+        shallow = OracleSteps(DENSE_27B, context, 1)
+        shallow.step()
+        shallow_seconds = sum(shallow.step()[0] for _ in range(3)) / 3.0
+        per_layer = max(per_step - shallow_seconds, 0.0) / (REFERENCE_LAYERS - 1)
+        whole = per_step + (DENSE_27B["layers"] - REFERENCE_LAYERS) * per_layer
+        line["cpu_baseline"]["whole_model_estimate"] = {
+            "value": (tokens / steps) / whole, "unit": "tok/s", "seconds_per_step": whole,
+            "how": f"measured {per_step:.3f} s per step with {REFERENCE_LAYERS} layers and {shallow_seconds:.3f} s with 1: "
+                   f"{per_layer:.3f} s per layer x {DENSE_27B['layers']} layers + the rest"}
+        line["cpu_baseline"]["reference_ffn"] = reference_cpu_ffn(DENSE_27B, line["cpu_baseline"]["cores"])
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

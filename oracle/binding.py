@@ -92,6 +92,13 @@ def build(force=False):
             force or not os.path.exists(kernels) or os.path.getmtime(kernels) < os.path.getmtime(shim)):
         subprocess.run(["make", "-C", HERE, "ref_kernels", f"REFERENCE={reference}"], check=True,
                        stdout=subprocess.DEVNULL)
+    # the reference's own CPU FFN executor (benchmark's CPU leg)
+    host = os.path.join(HERE, "_ref", "libqllm_ref_fp4_host.so")
+    host_shim = os.path.join(HERE, "ref_fp4_host_shim.cpp")
+    if reference and os.path.isdir(reference) and (
+            force or not os.path.exists(host) or os.path.getmtime(host) < os.path.getmtime(host_shim)):
+        subprocess.run(["make", "-C", HERE, "ref_fp4_host", f"REFERENCE={reference}"], check=True,
+                       stdout=subprocess.DEVNULL)
     return lib
 
 
@@ -170,6 +177,29 @@ def ref_sampler():
 
 
 _ref_kernels = None
+
+
+_ref_fp4_host = None
+
+
+def ref_fp4_host():
+    """The reference's own CPU FFN executor (runtime/src/cpu/fp4_host_executor.cpp) behind
+    oracle/ref_fp4_host_shim.cpp, or None when it was not built or this host has no AVX2."""
+    global _ref_fp4_host
+    if _ref_fp4_host is None:
+        build()
+        path = os.path.join(HERE, "_ref", "libqllm_ref_fp4_host.so")
+        try:
+            flags = open("/proc/cpuinfo").read()
+        except OSError:
+            flags = ""
+        if not os.path.exists(path) or " avx2" not in flags:
+            return None
+        R = C.CDLL(path)
+        R.ref_fp4_host_ffn_seconds.restype = C.c_double
+        R.ref_fp4_host_ffn_seconds.argtypes = [C.c_uint32] * 5 + [C.c_uint64, C.POINTER(C.c_double)]
+        _ref_fp4_host = R
+    return _ref_fp4_host
 
 
 def ref_kernels():

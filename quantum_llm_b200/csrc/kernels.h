@@ -84,6 +84,16 @@ struct AttentionArgs {
   // rows z*rows.. of the pass (queries, positions) and its partials follow tile z-1's in the workspace
   uint32_t tiles;
 };
+// Floats in the maxima (and in the sums) section of the split partials [maxima][sums][outputs] of one
+// row tile: rows x splits x heads rounded up to a multiple of four, so that the outputs section,
+// which the kernels read and write as float4, starts on a 16-byte boundary for every head count
+// (5 query heads, one row, 65 splits gave an odd count and a misaligned section).
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline size_t attention_partial_items(uint32_t rows, uint32_t max_splits, uint32_t q_heads) {
+  return (static_cast<size_t>(rows) * max_splits * q_heads + 3U) & ~static_cast<size_t>(3U);
+}
 #ifdef __CUDACC__
 // Entry of every attention kernel: moves the arguments to the row tile of this block.
 template <typename P>
@@ -91,7 +101,7 @@ __device__ __forceinline__ void attention_row_tile(AttentionArgs& a, P& part) {
   const uint32_t z = blockIdx.z;
   if (z == 0U) return;
   const uint32_t r0 = z * a.rows;
-  const size_t shift = static_cast<size_t>(r0) * a.max_splits * a.q_heads * (2U + a.head_dim);
+  const size_t shift = z * attention_partial_items(a.rows, a.max_splits, a.q_heads) * (2U + a.head_dim);
   part.maxima += shift;
   part.sums += shift;
   part.outputs += shift;

@@ -287,13 +287,13 @@ struct Partials {
 };
 size_t attention_workspace_bytes(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                                  uint32_t max_splits) {
-  const size_t items = static_cast<size_t>(rows) * max_splits * q_heads;
+  const size_t items = attention_partial_items(rows, max_splits, q_heads);
   // partials, then room for INT8 queries made on the fly (tensor-memory kernel without ready-made ones)
   return ((items * (2U + head_dim) * sizeof(float) + 255U) & ~static_cast<size_t>(255U)) +
          attention_q4h_tc_query_bytes(rows, q_heads);
 }
 static Partials partials_of(const AttentionArgs& a) {
-  const size_t items = static_cast<size_t>(a.rows) * a.max_splits * a.q_heads;
+  const size_t items = attention_partial_items(a.rows, a.max_splits, a.q_heads);
   float* base = static_cast<float*>(a.workspace);
   return {base, base + items, base + 2U * items};
 }
@@ -558,7 +558,7 @@ int launch_attention(const AttentionArgs& a, cudaStream_t stream) {
   if (a.tiles > 1U && !a.skip_combine) return fail(QLLM_INVALID_ARGUMENT, "row tiles are merged by the caller");
   const bool mma = a.impl >= 1;   // 2 asks for the tensor-memory kernel where one exists (Q4H)
   if (a.impl == 2 && a.encoding == QLLM_KV_Q4H && attention_q4h_tc_supported(a)) {
-    const size_t items = static_cast<size_t>(a.rows) * a.max_splits * a.q_heads;
+    const size_t items = attention_partial_items(a.rows, a.max_splits, a.q_heads) * (a.tiles > 1U ? a.tiles : 1U);
     uint8_t* scratch = static_cast<uint8_t*>(a.workspace) +
                        ((items * (2U + a.head_dim) * sizeof(float) + 255U) & ~static_cast<size_t>(255U));
     const int rc = launch_attention_q4h_tc(a, part.maxima, part.sums, part.outputs, a.error, scratch, stream);

@@ -180,7 +180,7 @@ combine_quant_kernel(CombineArgs c) {
   // grid z = row tile of a wide pass: gridDim.y rows each, partials one tile after the other
   const uint32_t tile_row0 = kTiled ? blockIdx.z * gridDim.y : 0U;
   if constexpr (kTiled) {
-    const size_t tile_shift = static_cast<size_t>(tile_row0) * c.max_splits * c.q_heads * (2U + hd);
+    const size_t tile_shift = blockIdx.z * attention_partial_items(gridDim.y, c.max_splits, c.q_heads) * (2U + hd);
     c.maxima += tile_shift;
     c.sums += tile_shift;
     c.outputs += tile_shift;

@@ -512,7 +512,7 @@ struct qllm_provider {
       if (want_tc && attention_q4h_tc_supported(at)) at.impl = 2;
       ok(launch_attention(at, stream));
       CombineArgs cb{};
-      const size_t items = static_cast<size_t>(n) * splits * c.q_heads;
+      const size_t items = attention_partial_items(n, splits, c.q_heads);
       cb.maxima = reinterpret_cast<const float*>(attn_ws.p);
       cb.sums = cb.maxima + items;
       cb.outputs = cb.maxima + 2U * items;

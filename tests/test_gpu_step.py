@@ -185,6 +185,27 @@ def test_group_8_tensor_core_attention_inside_a_step():
     assert e["prefix"] == 25 and e["exact"] == e["shared"]
 
 
+@pytest.mark.parametrize("attention_impl", [0, 1, 2])
+def test_one_eighth_shard_geometry(attention_impl):
+    # what one rank of an 8-way split of the 27B model sees: 5 query heads on one kv head, an
+    # o projection with K = 640 and a down projection whose K is not a multiple of 256, and
+    # rows x splits x heads odd (one draft row or five verify rows, three splits, five heads),
+    # which once left the float4 section of the split partials on an 8-byte boundary
+    cfg = dict(WIDE, q_heads=5, kv_heads=1, ffn=1088, kv_encoding=ob.KV_Q4H)
+    model = synth.SynthModel(cfg, seed=8)
+    prompt = synth.prompt(4096, 130, 8)
+    cpu = run_cpu(model, prompt, 0, 24)
+    gemv_impl = 0 if attention_impl == 0 else 1
+    gpu = run_gpu(model, prompt, 0, 24, graph=True, gemv_impl=gemv_impl, attention_impl=attention_impl)
+    c = compare(gpu, cpu, len(prompt))
+    print("one-eighth shard geometry, attention_impl", attention_impl, c)
+    assert gpu["stream"][0] == cpu["stream"][0]
+    if attention_impl == 0:
+        assert c["prefix"] == 25 and c["exact"] == c["shared"]
+    else:
+        assert c["shared"] >= 4 and c["good"] >= 0.5 * c["shared"]
+
+
 def test_greedy_stream_equals_plain_target_decoding_on_gpu():
     # property that needs no oracle: speculative greedy output does not depend on the drafts,
     # so a provider with a different draft block emits the same tokens
