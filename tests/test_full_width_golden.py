@@ -15,8 +15,9 @@ speculative steps.  Here the CUDA provider decodes the same model through the C 
 * tensor-core attention (INT8 mma.sync or tcgen05): each kernel alone stays within 1e-3 of the
   oracle's attention (tests/test_long_context.py, tests/test_gpu_kernels.py; the reference gates
   its own tensor-core kernel at 2e-3 against its host check), but the deviation is not zero: the
-  kernels quantise the softmax weights to INT8 per 64-key tile against the running maximum of
-  their own tile order, the oracle per 32-key tile.  A W4A4 decoder does not damp a perturbation,
+  kernels take exp from ex2.approx and sum in FP32 where the oracle uses its deterministic series
+  and double, so now and then one of the INT8-quantised softmax weights rounds to the
+  neighbouring code.  A W4A4 decoder does not damp a perturbation,
   it amplifies it: a relative difference e in an activation flips an E2M1 code (spacing about a
   third of the value) with probability about 3 e, and a flipped code moves its element by a third,
   so one quantiser later the difference is about sqrt(0.3 e): 1e-3 -> 2 % -> 8 % -> the level of
