@@ -209,6 +209,14 @@ int main() {
                                          const er::OperationInvocation&) override {
       return {};
     }
+    // stateless fixture: nothing to checkpoint
+    er::Status checkpoint_request_state(const std::shared_ptr<er::IOperationProviderRequestState>&,
+                                        std::uint32_t) override {
+      return er::Status::success();
+    }
+    er::Status rewind_request_state(const std::shared_ptr<er::IOperationProviderRequestState>&, std::uint32_t) override {
+      return er::Status::success();
+    }
   };
   er::ExecutionProviderRegistry registry;
   require(registry.add(created.module.definition).ok(), "registering the module failed");
@@ -240,12 +248,18 @@ int main() {
               stub->last_request.sampling_seed == 77U && stub->last_request.reserved_context_tokens == 128U &&
               stub->last_request.sampling_presence_penalty_biased_ppm == 2000000U,
           "synchronisation did not reach the C ABI with the request's parameters");
+  // retention through the executor's session: a checkpoint at the end of the cached stream
+  // (position 2 after the one-row synchronisation at position 1), none anywhere else
+  require(!begun.session.checkpoint_retention(7U).ok(), "a checkpoint away from the end of the stream was accepted");
+  require(begun.session.checkpoint_retention(2U).ok(), "the retention checkpoint did not reach the C ABI");
   auto exact = begun.session.execute_exact_decode(110U, 2U, 128U);
   const auto result = exact.handle.poll();
   require(exact.status.ok() && result && result->status.ok() &&
               result->emitted_tokens == std::vector<std::uint32_t>({110U, 111U}) && result->next_token == 112U &&
               result->positions_advanced == 2U && stub->executions == 1U,
           "the step's result did not survive the executor's re-validation");
+  require(!begun.session.rewind_retention(3U).ok(), "a rewind to a position that was not checkpointed was accepted");
+  require(begun.session.rewind_retention(2U).ok(), "the retention rewind did not reach the C ABI");
   begun.session.cancel();
   require(stub->states == 0U, "closing the session leaked the request state");
 

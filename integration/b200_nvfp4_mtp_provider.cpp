@@ -280,6 +280,26 @@ class B200Nvfp4MtpProvider final : public IOperationProvider {
         [done] { done->taken = true; });
   }
 
+  // Session retention (runtime/tools/dense_fp4_provider.cpp:9209-9338): the library keeps the
+  // checkpointed position per request state and applies the reference's admission conditions.
+  bool supports_request_state_retention() const noexcept override { return true; }
+  Status checkpoint_request_state(const std::shared_ptr<IOperationProviderRequestState>& state,
+                                  std::uint32_t next_position) override {
+    std::lock_guard lock(mutex_);
+    auto* st = dynamic_cast<RequestState*>(state.get());
+    if (st == nullptr || provider_ == nullptr)
+      return {ErrorCode::invalid_argument, "retention checkpoint position is invalid"};
+    return to_status(qllm_provider_checkpoint_request_state(provider_, st->state, next_position));
+  }
+  Status rewind_request_state(const std::shared_ptr<IOperationProviderRequestState>& state,
+                              std::uint32_t next_position) override {
+    std::lock_guard lock(mutex_);
+    auto* st = dynamic_cast<RequestState*>(state.get());
+    if (st == nullptr || provider_ == nullptr)
+      return {ErrorCode::invalid_argument, "retention rewind position is invalid"};
+    return to_status(qllm_provider_rewind_request_state(provider_, st->state, next_position));
+  }
+
   // exact_calls, accepted_drafts, accepted_depth_calls (runtime/tools/dense_fp4_provider.cpp:11313-11316)
   // are kept per request by the library (qllm_provider_telemetry); the module publishes the
   // geometry it bound.

@@ -15,6 +15,7 @@ struct qllm_provider {
 };
 struct qllm_request_state {
   unsigned length;
+  unsigned checkpoint;   // 0: none
 };
 
 namespace {
@@ -83,6 +84,20 @@ int qllm_provider_execute_exact_decode(qllm_provider* p, qllm_request_state* s, 
   out->emitted_count = 2U;
   out->next_token = token + 2U;
   out->positions_advanced = 2U;
+  s->length = position + 2U;
+  return QLLM_OK;
+}
+
+int qllm_provider_checkpoint_request_state(qllm_provider* p, qllm_request_state* s, uint32_t next_position) {
+  if (!p || !s || !next_position || next_position != s->length)
+    return fail(QLLM_INVALID_ARGUMENT, "retention checkpoint position is invalid");
+  s->checkpoint = next_position;
+  return QLLM_OK;
+}
+int qllm_provider_rewind_request_state(qllm_provider* p, qllm_request_state* s, uint32_t next_position) {
+  if (!p || !s || !s->checkpoint || s->checkpoint != next_position)
+    return fail(QLLM_INVALID_ARGUMENT, "retention rewind position is invalid");
+  s->length = next_position;
   return QLLM_OK;
 }
 
