@@ -108,11 +108,16 @@ typedef struct qllm_request {
   uint32_t sampling_top_k; /* 1..64 when sampling */
   uint32_t sampling_min_p_ppm;
   uint32_t reserved_context_tokens; /* context limit of the request */
-  /* sampling_presence_penalty_biased_ppm: penalty * 1e6 + 2 000 000, i.e. 2 000 000 = no penalty
-   * (apply_presence_penalty, runtime/tools/dense_fp4_provider.cpp:8336-8347).  The presence penalty
-   * is not implemented: any other value is refused with QLLM_INVALID_ARGUMENT, so a request can
-   * never be decoded without a penalty it asked for. */
+  /* sampling_presence_penalty_biased_ppm: penalty * 1e6 + 2 000 000, i.e. 2 000 000 = no penalty,
+   * at most 4 000 000 (apply_presence_penalty, runtime/tools/dense_fp4_provider.cpp:8336-8347):
+   * logits[token] -= penalty for every token the request has emitted, and inside a speculative step
+   * also for the proposals that precede the row being judged (:11182-11202); accepted proposals and
+   * the selected token are committed to the request's mask by the step (:11261-11270). */
   uint32_t sampling_presence_penalty_biased_ppm;
+  /* sampling_first_output_position (moe_vm_runner.cpp:341): the scalar head (first token, scalar
+   * decode) penalises and marks only sample positions at or after it. */
+  uint32_t sampling_first_output_position;
+  uint32_t reserved; /* 0 */
 } qllm_request;
 
 /* ExactDecodeExecutionResult (program_executor.hpp:205-212). */

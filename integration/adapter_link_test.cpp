@@ -263,15 +263,27 @@ int main() {
   begun.session.cancel();
   require(stub->states == 0U, "closing the session leaked the request state");
 
-  // a request that asks for a presence penalty is refused, not decoded without it
+  // a request's presence penalty and first output position reach the C ABI; an invalid one is refused
   er::ProgramRequestContext penalised;
   penalised.request_id = 2U;
   penalised.parameters.emplace("reserved_context_tokens", 128U);
   penalised.parameters.emplace("sampling_presence_penalty_biased_ppm", 2500000U);
+  penalised.parameters.emplace("sampling_first_output_position", 9U);
   auto second = executor.begin_session(std::move(penalised));
   require(second.status.ok(), "second session");
-  require(!second.session.synchronize_exact_decode(5U, 1U, true).ok(), "a presence penalty was silently dropped");
+  require(second.session.synchronize_exact_decode(5U, 1U, true).ok() &&
+              stub->last_request.sampling_presence_penalty_biased_ppm == 2500000U &&
+              stub->last_request.sampling_first_output_position == 9U,
+          "the presence penalty did not reach the C ABI");
   second.session.cancel();
+  er::ProgramRequestContext invalid;
+  invalid.request_id = 3U;
+  invalid.parameters.emplace("reserved_context_tokens", 128U);
+  invalid.parameters.emplace("sampling_presence_penalty_biased_ppm", 4000001U);
+  auto third = executor.begin_session(std::move(invalid));
+  require(third.status.ok(), "third session");
+  require(!third.session.synchronize_exact_decode(5U, 1U, true).ok(), "an invalid presence penalty was accepted");
+  third.session.cancel();
   std::cout << "PASS adapter link test\n";
   return 0;
 }

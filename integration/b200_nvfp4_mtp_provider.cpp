@@ -57,6 +57,7 @@ Status request_of(const ProgramRequestContext& context, qllm_request* out) {
   // value + 2 000 000 (runtime/tools/dense_fp4_provider.cpp:8336-8341); absent = neutral
   r.sampling_presence_penalty_biased_ppm =
       static_cast<std::uint32_t>(get("sampling_presence_penalty_biased_ppm", 2'000'000U));
+  r.sampling_first_output_position = static_cast<std::uint32_t>(get("sampling_first_output_position", 0U));
   if (get("sampling_presence_penalty_biased_ppm", 2'000'000U) > 4'000'000U)
     return {ErrorCode::invalid_argument, "sampling presence penalty is invalid"};
   *out = r;

@@ -63,8 +63,8 @@ void qllm_provider_destroy_request_state(qllm_provider* p, qllm_request_state* s
 int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_state* s, const qllm_request* rq,
                                                  const uint32_t* tokens, uint32_t count, uint32_t first, int) {
   if (!p || !s || !rq || !tokens || !count) return fail(QLLM_INVALID_ARGUMENT, "stub: bad synchronization");
-  if (rq->sampling_presence_penalty_biased_ppm != 2000000U)
-    return fail(QLLM_INVALID_ARGUMENT, "sampling presence penalty is not implemented by this provider");
+  if (rq->sampling_presence_penalty_biased_ppm > 4000000U)
+    return fail(QLLM_INVALID_ARGUMENT, "sampling presence penalty is invalid");
   p->last_request = *rq;
   ++p->synchronizations;
   s->length = first + count;
@@ -73,8 +73,8 @@ int qllm_provider_synchronize_exact_decode_batch(qllm_provider* p, qllm_request_
 int qllm_provider_execute_exact_decode(qllm_provider* p, qllm_request_state* s, const qllm_request* rq, uint32_t token,
                                        uint32_t position, uint32_t limit, qllm_exact_result* out) {
   if (!p || !s || !rq || !out) return fail(QLLM_INVALID_ARGUMENT, "stub: bad step");
-  if (rq->sampling_presence_penalty_biased_ppm != 2000000U)
-    return fail(QLLM_INVALID_ARGUMENT, "sampling presence penalty is not implemented by this provider");
+  if (rq->sampling_presence_penalty_biased_ppm > 4000000U)
+    return fail(QLLM_INVALID_ARGUMENT, "sampling presence penalty is invalid");
   if (position + 2U >= limit) return fail(QLLM_INVALID_ARGUMENT, "exact MTP invocation stream is invalid");
   p->last_request = *rq;
   ++p->executions;

@@ -49,7 +49,8 @@ class Request(C.Structure):
     _fields_ = [("seed", C.c_uint64), ("temperature_ppm", C.c_uint32),
                 ("top_p_ppm", C.c_uint32), ("top_k", C.c_uint32),
                 ("min_p_ppm", C.c_uint32), ("context_limit", C.c_uint32),
-                ("presence_penalty_biased_ppm", C.c_uint32)]
+                ("presence_penalty_biased_ppm", C.c_uint32), ("first_output_position", C.c_uint32),
+                ("reserved", C.c_uint32)]
 
 
 class StepResult(C.Structure):

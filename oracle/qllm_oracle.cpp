@@ -761,6 +761,20 @@ struct qo_session {
   bool draft_valid = false;
   std::vector<uint32_t> draft_tokens;
   std::vector<Dist> draft_dists;
+  // sampling presence (dense_fp4_provider.cpp:5168-5171): tokens this request has emitted, and the
+  // working copy a verify pass / a rollout advances with its own proposals
+  std::vector<uint8_t> emitted, proposal_presence;
+
+  // (biased - 2 000 000) / 1 000 000, dense_fp4_provider.cpp:8336-8341
+  static float presence_penalty(const qo_request& rq) {
+    if (rq.presence_penalty_biased_ppm > 4000000U) throw std::runtime_error("sampling presence penalty is invalid");
+    return static_cast<float>((static_cast<double>(rq.presence_penalty_biased_ppm) - 2000000.0) / 1000000.0);
+  }
+  // presence_penalty_kernel, runtime/src/cuda/transformer_kernels.cu:7180-7186 (in place)
+  static void apply_presence(float* row_logits, uint32_t count, const uint8_t* presence, float penalty) {
+    for (uint32_t i = 0; i < count; ++i)
+      if (presence[i] != 0U) row_logits[i] -= penalty;
+  }
 
   void ensure_rows(uint32_t rows) {
     const auto& c = cfg;
@@ -885,7 +899,13 @@ struct qo_session {
   }
 
   // dense_fp4_provider.cpp:8331-8391
-  Dist distribution(const float* row_logits, uint32_t vocabulary, const qo_request& rq) const {
+  Dist distribution(float* row_logits, uint32_t vocabulary, const qo_request& rq,
+                    const uint8_t* presence = nullptr) const {
+    const float penalty = presence_penalty(rq);
+    if (penalty != 0.0F) {
+      if (!presence) throw std::runtime_error("sampling presence state is absent");
+      apply_presence(row_logits, vocabulary, presence, penalty);
+    }
     if (rq.temperature_ppm == 0U) return Dist{{argmax(row_logits, vocabulary)}, {1.0}};
     if (rq.top_k == 0U || rq.top_k > 64U || rq.top_k > vocabulary)
       throw std::runtime_error("sampled exact decode requires bounded nonzero top-k");
@@ -930,7 +950,7 @@ struct qo_session {
     mtp_logits.resize(c.draft_vocab);
     nvfp4_gemv(w.head, 0, c.draft_vocab, dn.data(), 1, mtp_logits.data());
     if (rq) {
-      *dist = distribution(mtp_logits.data(), c.draft_vocab, *rq);
+      *dist = distribution(mtp_logits.data(), c.draft_vocab, *rq, proposal_presence.data());
       *token = sample_distribution(*dist, counter_uniform(rq->seed, sample_position, stream, 0));
     } else {
       *token = argmax(mtp_logits.data(), c.draft_vocab);
@@ -951,6 +971,7 @@ struct qo_session {
     if (committed + 1U >= rq.context_limit) throw std::runtime_error("MTP rollout root exceeds context");
     draft_tokens.push_back(first_token);
     draft_dists.push_back(std::move(first_dist));
+    proposal_presence[first_token] = 1U;   // mark speculative proposal presence, :8822-8825
     while (draft_tokens.size() < c.draft_depth && mtp_length + 2U < rq.context_limit) {
       const std::vector<float> prev = mtp_last_hidden;
       const uint32_t sample_position = mtp_length;
@@ -962,6 +983,7 @@ struct qo_session {
               1U + static_cast<uint32_t>(draft_tokens.size()), &next, &d);
       draft_tokens.push_back(next);
       draft_dists.push_back(std::move(d));
+      proposal_presence[next] = 1U;
     }
     draft_valid = !draft_tokens.empty();
     mtp_length = committed;
@@ -1216,7 +1238,11 @@ int qo_prefill_at(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_
                   const qo_request* rq, uint32_t* first_token) {
   try {
     const auto& c = s->cfg;
-    if (rq->presence_penalty_biased_ppm != 2000000U) throw std::runtime_error("presence penalty is not restated");
+    (void)qo_session::presence_penalty(*rq);   // validates the field
+    if (s->emitted.size() != c.vocab) {
+      s->emitted.assign(c.vocab, 0U);
+      s->proposal_presence.assign(c.vocab, 0U);
+    }
     if (!count || !chunk_rows || base + count + 1U >= rq->context_limit || rq->context_limit > c.max_context ||
         s->mtp_length != base)
       throw std::runtime_error("invalid prefill request");
@@ -1232,11 +1258,16 @@ int qo_prefill_at(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_
       if (last) {
         // first output token: scalar head branch (dense_fp4_provider.cpp:8453-8480),
         // uniform stream 0 at the last prompt position
-        const float* row_logits = s->logits.data() + static_cast<size_t>(rows - 1U) * c.vocab;
-        const Dist d = s->distribution(row_logits, c.vocab, *rq);
+        // the penalty and the emitted mark apply to output positions only (:8440-8453, :8514-8516)
+        float* row_logits = s->logits.data() + static_cast<size_t>(rows - 1U) * c.vocab;
+        const bool output_sampling = count - 1U >= rq->first_output_position;
+        qo_request head_request = *rq;
+        if (!output_sampling) head_request.presence_penalty_biased_ppm = 2000000U;
+        const Dist d = s->distribution(row_logits, c.vocab, head_request, s->emitted.data());
         *first_token = rq->temperature_ppm == 0U
                            ? d.tokens[0]
                            : sample_distribution(d, counter_uniform(rq->seed, count - 1U, 0, 0));
+        if (output_sampling) s->emitted[*first_token] = 1U;
       }
       // synchronize_exact_decode_batch (dense_fp4_provider.cpp:11011-11137)
       if (s->mtp_length != first) throw std::runtime_error("MTP synchronization stream is invalid");
@@ -1248,6 +1279,7 @@ int qo_prefill_at(qo_session* s, const uint32_t* tokens, uint32_t count, uint32_
       const std::vector<float> target_hidden = s->hidden;
       uint32_t token = 0;
       Dist d;
+      if (last) s->proposal_presence = s->emitted;   // initialize speculative proposal presence, :11091-11098
       const bool produced = s->run_mtp(next.data(), target_hidden.data(), rotary.data(), rows,
                                        last, last ? rq : nullptr, first + rows, 1U, &token, &d);
       if (last) {
@@ -1280,9 +1312,18 @@ int qo_execute_exact_decode(qo_session* s, const qo_request* rq, uint32_t guaran
       tp.push_back(position + i + 1U);
     }
     s->run_target(tt.data(), tp.data(), proposals + 1U, true);
+    if (s->emitted.size() != c.vocab) {
+      s->emitted.assign(c.vocab, 0U);
+      s->proposal_presence.assign(c.vocab, 0U);
+    }
+    // row r is judged against what was emitted plus the proposals before it, :11182-11202
+    s->proposal_presence = s->emitted;
     std::vector<Dist> target;
-    for (uint32_t r = 0; r <= proposals; ++r)
-      target.push_back(s->distribution(s->logits.data() + static_cast<size_t>(r) * c.vocab, c.vocab, *rq));
+    for (uint32_t r = 0; r <= proposals; ++r) {
+      target.push_back(s->distribution(s->logits.data() + static_cast<size_t>(r) * c.vocab, c.vocab, *rq,
+                                       s->proposal_presence.data()));
+      if (r < proposals) s->proposal_presence[s->draft_tokens[r]] = 1U;
+    }
     uint32_t accepted = 0, next_token = 0;
     bool rejected = false;
     for (; accepted < proposals; ++accepted) {
@@ -1296,6 +1337,9 @@ int qo_execute_exact_decode(qo_session* s, const qo_request* rq, uint32_t guaran
     if (!rejected)
       next_token = sample_distribution(target.back(),
                                        counter_uniform(rq->seed, position + accepted, 300U, 0));
+    // commit accepted proposal presence and the sampled next token, :11261-11270
+    for (uint32_t i = 0; i < accepted; ++i) s->emitted[s->draft_tokens[i]] = 1U;
+    s->emitted[next_token] = 1U;
     std::vector<uint32_t> mt, mp;
     for (uint32_t i = 0; i < accepted; ++i) mt.push_back(s->draft_tokens[i]);
     mt.push_back(next_token);
@@ -1316,6 +1360,7 @@ int qo_execute_exact_decode(qo_session* s, const qo_request* rq, uint32_t guaran
     const std::vector<float> target_hidden = s->hidden;
     uint32_t token = 0;
     Dist d;
+    s->proposal_presence = s->emitted;   // initialize next MTP rollout presence, :11290-11292
     const bool produced =
         s->run_mtp(mt.data(), target_hidden.data(), mp.data(), advanced, future,
                    future ? rq : nullptr, position + advanced, 1U, &token, &d);

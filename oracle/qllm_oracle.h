@@ -98,7 +98,9 @@ typedef struct qo_request {
   uint32_t top_k;           /* 1..64 when temperature_ppm != 0 */
   uint32_t min_p_ppm;
   uint32_t context_limit;   /* reserved_context_tokens */
-  uint32_t presence_penalty_biased_ppm; /* 2000000 = none (the only value restated here) */
+  uint32_t presence_penalty_biased_ppm; /* penalty * 1e6 + 2000000; 2000000 = none; at most 4000000 */
+  uint32_t first_output_position;       /* the scalar head penalises and marks from this position on */
+  uint32_t reserved;                    /* 0 */
 } qo_request;
 
 typedef struct qo_step_result {

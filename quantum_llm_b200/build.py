@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libqllm_b200.so")
-SOURCES = ["kernels_basic.cu", "kernels_attention.cu", "kernels_attention_q4h.cu", "kernels_attention_q4h_tc.cu", "kernels_attention_q8.cu", "kernels_attention_f16.cu", "kernels_sampler.cu", "kernels_sampler_full.cu", "kernels_fused.cu", "kernels_moe.cu", "gemv_mma.cu",
+SOURCES = ["kernels_basic.cu", "kernels_attention.cu", "kernels_attention_q4h.cu", "kernels_attention_q4h_tc.cu", "kernels_attention_q8.cu", "kernels_attention_f16.cu", "kernels_sampler.cu", "kernels_sampler_full.cu", "kernels_presence.cu", "kernels_fused.cu", "kernels_moe.cu", "gemv_mma.cu",
            "provider.cu", "c_api_kernels.cu", "no_alloc.cu", "descriptor.cpp", "pack.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-fmad=false", "-ccbin", "/usr/bin/g++"]

@@ -196,6 +196,24 @@ int launch_first_token(StepState* state, const uint32_t* argmax_token, const flo
                        cudaStream_t stream);
 // Scalar decode fallback (top_k == 0 or > 64): full-vocabulary ordering + the sequential
 // double-precision distribution of sample_token (dense_fp4_provider.cpp:771-802) on the device.
+// Presence penalty over `rows` logits rows of `stride` floats, the first `count` entries of each:
+// mode 0: tokens of the emitted mask; mode 1: verify rows -- row r also sees the step's proposals
+// 1..r (StepState::verify_tokens); mode 2: draft pass `pass` -- also the drafts 1..pass of the
+// running rollout.  In place, like the reference's kernel.
+struct PresenceArgs {
+  float* logits;
+  uint32_t rows;
+  size_t stride;
+  uint32_t count;
+  const uint8_t* emitted;   // [vocabulary] bytes, non-zero = emitted
+  const StepState* state;   // device; may be null for mode 0
+  uint32_t mode, pass;
+  float penalty;            // [-2, 2]
+};
+int launch_presence_penalty(const PresenceArgs& a, cudaStream_t stream);
+int launch_presence_commit_step(const StepState* state, uint8_t* emitted, uint32_t vocab, cudaStream_t stream);
+int launch_presence_commit_token(const uint32_t* token, uint8_t* emitted, uint32_t vocab, cudaStream_t stream);
+
 struct FullSampleParams {
   unsigned long long seed;
   uint32_t temperature_ppm, top_p_ppm, top_k, min_p_ppm;   // top_k 0 = the whole vocabulary

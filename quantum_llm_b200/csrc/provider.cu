@@ -117,11 +117,14 @@ struct qllm_request_state {
   uint32_t ring_cursor = 0;  // host mirror of StepState::step_index
   uint32_t retention_position = 0;  // checkpoint_request_state / rewind_request_state
   bool retention_valid = false;
+  uint8_t* emitted = nullptr;       // [vocab] sampling presence: tokens this request has emitted
+  float presence_penalty = 0.0F;    // of the bound request; 0 = none (no presence kernel is launched)
   bool request_bound = false;
   qllm_request request{};
   cudaGraphExec_t step_graph = nullptr;
   uint32_t graph_splits = 0, graph_mtp_splits = 0;
   int graph_sampled = -1, graph_gemv = -1;
+  float graph_presence = 0.0F;      // penalty baked into the captured step
 };
 
 struct qllm_provider {
@@ -588,7 +591,7 @@ struct qllm_provider {
   void run_mtp(qllm_request_state& st, const uint32_t* tokens, const float* previous_hidden,
                uint32_t rows, const uint32_t* first_position, uint32_t position_offset,
                uint32_t splits, bool produce, const uint32_t* select_row, bool sampled,
-               uint32_t top_k) {
+               uint32_t top_k, uint32_t draft_pass = 0U) {
     const auto& c = cfg;
     ok(launch_embedding(embedding, tokens, mtp_emb.p, rows, c.hidden, c.vocab, stream));
     // [norm(embedding) | norm(previous hidden)] quantised straight into the two halves of
@@ -609,6 +612,10 @@ struct qllm_provider {
     norm_quant(mtp_hidden.p, c.hidden, &pending, st.mtp_last_hidden, mtp_draft_norm, &head, 1U, 0U, select_row);
     const GemvOut lg = gemv(head, 1U, c.draft_vocab, draft_logits.p);
     ok(launch_gemv_finalize(lg, draft_logits.p, stream));
+    // the draft is drawn from logits penalised by what was emitted and by the rollout's own drafts so far
+    if (st.presence_penalty != 0.0F)
+      ok(launch_presence_penalty(PresenceArgs{draft_logits.p, 1U, c.draft_vocab, c.draft_vocab, st.emitted, st.state,
+                                              2U, draft_pass, st.presence_penalty}, stream));
     select_candidates(draft_logits.p, 1, c.draft_vocab, c.draft_vocab, sampled, top_k);
   }
 
@@ -618,7 +625,7 @@ struct qllm_provider {
     const auto& c = cfg;
     for (uint32_t i = 1; i < c.draft_depth; ++i) {
       run_mtp(st, &st.state->verify_tokens[i], st.mtp_last_hidden, 1, &st.state->new_position,
-              i - 1U, splits, true, nullptr, sampled, top_k);
+              i - 1U, splits, true, nullptr, sampled, top_k, i);
       DraftSampleArgs ds{st.state, argmax_out.p, top_values.p, top_tokens.p,
                          i | (i + 1U == c.draft_depth ? 0x80000000U : 0U), from_sync ? 1U : 0U,
                          st.results, kResultRing, kernel_error.p};
@@ -633,9 +640,15 @@ struct qllm_provider {
     const uint32_t R = c.draft_depth + 1U;
     StepState* s = st.state;
     run_target(st, s->verify_tokens, R, &s->position, splits, true);
+    // presence penalty: row r is judged against the emitted tokens plus the proposals before it
+    if (st.presence_penalty != 0.0F)
+      ok(launch_presence_penalty(PresenceArgs{logits.p, R, c.vocab, c.vocab, st.emitted, s, 1U, 0U,
+                                              st.presence_penalty}, stream));
     select_candidates(logits.p, R, c.vocab, c.vocab, sampled, top_k);
     AcceptArgs aa{s, argmax_out.p, top_values.p, top_tokens.p, st.results, kResultRing};
     ok(launch_accept(aa, stream));
+    // the accepted proposals and the selected token are emitted from here on
+    if (st.presence_penalty != 0.0F) ok(launch_presence_commit_step(s, st.emitted, c.vocab, stream));
     // first draft pass: accepted drafts + selected token against the target's hidden rows;
     // rows past accepted+1 are padding whose cache records are overwritten before any read
     run_mtp(st, s->mtp_tokens, hidden.p, R, &s->position, 0U, mtp_splits, true,
@@ -661,10 +674,13 @@ struct qllm_provider {
       throw Error(QLLM_INVALID_ARGUMENT, "invalid token sampling contract");
     if (rq.reserved_context_tokens > cfg.max_context)
       throw Error(QLLM_INVALID_ARGUMENT, "request context exceeds the provider's max_context");
-    if (rq.sampling_presence_penalty_biased_ppm != 2000000U)
-      throw Error(QLLM_INVALID_ARGUMENT,
-                  "sampling presence penalty is not implemented by this provider (sampling_presence_penalty_biased_ppm "
-                  "must be 2000000, i.e. no penalty)");
+    if (rq.sampling_presence_penalty_biased_ppm > 4000000U)
+      throw Error(QLLM_INVALID_ARGUMENT, "sampling presence penalty is invalid");
+    if (rq.sampling_first_output_position >= cfg.max_context)
+      throw Error(QLLM_INVALID_ARGUMENT, "request has an invalid sampling profile");
+    // (biased - 2 000 000) / 1 000 000 (dense_fp4_provider.cpp:8340-8341)
+    st.presence_penalty =
+        static_cast<float>((static_cast<double>(rq.sampling_presence_penalty_biased_ppm) - 2000000.0) / 1000000.0);
     if (st.request_bound && !std::memcmp(&st.request, &rq, sizeof(rq))) return;
     StepState head{};
     head.seed = rq.sampling_seed;
@@ -753,6 +769,9 @@ int qllm_provider_create_request_state(qllm_provider* p, qllm_request_state** ou
     cu(cudaMallocHost(&st->host_records, qllm_provider::kResultRing * sizeof(StepRecord)), "pinned result ring");
     cu(cudaMalloc(&st->retained_hidden, static_cast<size_t>(qllm_provider::kChunkRows) * c.hidden * sizeof(float)), "retained hidden");
     cu(cudaMalloc(&st->mtp_last_hidden, c.hidden * sizeof(float)), "draft hidden");
+    // sampling presence of the request, all clear (dense_fp4_provider.cpp:5519-5525)
+    cu(cudaMalloc(&st->emitted, c.vocab), "sampling presence");
+    cu(cudaMemsetAsync(st->emitted, 0, c.vocab, p->stream), "sampling presence");
     cu(cudaStreamSynchronize(p->stream), "request state set-up");
   });
   if (rc) {
@@ -775,6 +794,7 @@ void qllm_provider_destroy_request_state(qllm_provider* p, qllm_request_state* s
   if (st->host_records) cudaFreeHost(st->host_records);
   cudaFree(st->retained_hidden);
   cudaFree(st->mtp_last_hidden);
+  cudaFree(st->emitted);
   delete st;
 }
 
@@ -812,7 +832,12 @@ int qllm_provider_first_token(qllm_provider* p, qllm_request_state* st, const ql
     if (!st->retained_rows) throw Error(QLLM_INVALID_ARGUMENT, "no prefill rows retained");
     p->bind_request(*st, *rq, false);
     const bool sampled = rq->sampling_temperature_ppm != 0U;
-    const float* row = p->logits.p + static_cast<size_t>(st->retained_logits_row) * c.vocab;
+    float* row = p->logits.p + static_cast<size_t>(st->retained_logits_row) * c.vocab;
+    // the scalar head penalises and marks output positions only (dense_fp4_provider.cpp:8440-8453, :8514-8516)
+    const bool penalised = st->presence_penalty != 0.0F && sample_position >= rq->sampling_first_output_position;
+    if (penalised)
+      ok(launch_presence_penalty(PresenceArgs{row, 1U, c.vocab, c.vocab, st->emitted, nullptr, 0U, 0U,
+                                              st->presence_penalty}, p->stream));
     if (sampled && (rq->sampling_top_k == 0U || rq->sampling_top_k > 64U)) {
       // no truncation, or more candidates than the sorted top-k kernels hold: order the whole row
       const FullSampleParams q{rq->sampling_seed, rq->sampling_temperature_ppm, rq->sampling_top_p_ppm,
@@ -824,6 +849,7 @@ int qllm_provider_first_token(qllm_provider* p, qllm_request_state* st, const ql
       ok(launch_first_token(st->state, p->argmax_out.p, p->top_values.p, p->top_tokens.p, sample_position,
                             p->first_token_dev.p, p->stream));
     }
+    if (penalised) ok(launch_presence_commit_token(p->first_token_dev.p, st->emitted, c.vocab, p->stream));
     cu(cudaMemcpyAsync(token, p->first_token_dev.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, p->stream), "copy first token");
     check_device_error(*p, *st);
   });
@@ -901,7 +927,7 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
   const uint32_t ring_start = st->ring_cursor;
   if (p->graph_mode) {
     if (!st->step_graph || st->graph_splits != splits || st->graph_sampled != static_cast<int>(sampled) ||
-        st->graph_gemv != p->gemv_impl + 2 * p->attention_impl) {
+        st->graph_gemv != p->gemv_impl + 2 * p->attention_impl || st->graph_presence != st->presence_penalty) {
       if (st->step_graph) { cudaGraphExecDestroy(st->step_graph); st->step_graph = nullptr; }
       cudaGraph_t graph = nullptr;
       cu(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeThreadLocal), "begin step capture");
@@ -919,6 +945,7 @@ static void run_steps(qllm_provider* p, qllm_request_state* st, const qllm_reque
       st->graph_splits = splits;
       st->graph_sampled = sampled;
       st->graph_gemv = p->gemv_impl + 2 * p->attention_impl;  // kernel selection baked into the graph
+      st->graph_presence = st->presence_penalty;
     }
     for (uint32_t i = 0; i < steps; ++i) cu(cudaGraphLaunch(st->step_graph, p->stream), "launch step graph");
   } else {

@@ -63,7 +63,8 @@ class Request(C.Structure):
     _fields_ = [("sampling_seed", C.c_uint64), ("sampling_temperature_ppm", C.c_uint32),
                 ("sampling_top_p_ppm", C.c_uint32), ("sampling_top_k", C.c_uint32),
                 ("sampling_min_p_ppm", C.c_uint32), ("reserved_context_tokens", C.c_uint32),
-                ("sampling_presence_penalty_biased_ppm", C.c_uint32)]
+                ("sampling_presence_penalty_biased_ppm", C.c_uint32),
+                ("sampling_first_output_position", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class ExactResult(C.Structure):

@@ -23,12 +23,13 @@ class RequestParameters:
     sampling_top_k: int = 20
     sampling_min_p_ppm: int = 0
     reserved_context_tokens: int = 0
-    sampling_presence_penalty_biased_ppm: int = 2_000_000   # penalty * 1e6 + 2e6: no penalty (the only supported value)
+    sampling_presence_penalty_biased_ppm: int = 2_000_000   # penalty * 1e6 + 2e6; 2e6 = none, at most 4e6
+    sampling_first_output_position: int = 0                 # the scalar head penalises and marks from here on
 
     def c(self):
         return _l.Request(self.sampling_seed, self.sampling_temperature_ppm, self.sampling_top_p_ppm,
                           self.sampling_top_k, self.sampling_min_p_ppm, self.reserved_context_tokens,
-                          self.sampling_presence_penalty_biased_ppm)
+                          self.sampling_presence_penalty_biased_ppm, self.sampling_first_output_position, 0)
 
 
 @dataclass

@@ -39,11 +39,14 @@ def provider_from_synth(model, device=0):
     return Nvfp4MtpProvider(c_config(model.cfg), w, weights_on_device=False, device=device, keepalive=(model, blocks))
 
 
-def request_pair(seed=1234, temperature_ppm=0, top_p_ppm=950000, top_k=20, min_p_ppm=0, context_limit=256):
+def request_pair(seed=1234, temperature_ppm=0, top_p_ppm=950000, top_k=20, min_p_ppm=0, context_limit=256,
+                 presence_penalty_ppm=0, first_output_position=0):
     """The same request for the CUDA provider and for the oracle."""
     from tests import synth
-    return (RequestParameters(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit),
-            synth.request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit))
+    return (RequestParameters(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit,
+                              2_000_000 + presence_penalty_ppm, first_output_position),
+            synth.request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit,
+                          presence_penalty_ppm, first_output_position))
 
 
 def dev(array):

@@ -169,5 +169,7 @@ def prompt(vocab, count, seed):
     return np.random.default_rng(seed).integers(0, vocab, count, dtype=np.uint32)
 
 
-def request(seed=1234, temperature_ppm=0, top_p_ppm=950000, top_k=20, min_p_ppm=0, context_limit=256):
-    return ob.Request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit, 2000000)
+def request(seed=1234, temperature_ppm=0, top_p_ppm=950000, top_k=20, min_p_ppm=0, context_limit=256,
+            presence_penalty_ppm=0, first_output_position=0):
+    return ob.Request(seed, temperature_ppm, top_p_ppm, top_k, min_p_ppm, context_limit,
+                      2000000 + presence_penalty_ppm, first_output_position)

@@ -1,7 +1,9 @@
 """CPU checks of the whole-step oracle: properties that must hold whatever the
 weights are (the reference holds no end-to-end vector for its MTP loop)."""
 import numpy as np
+import pytest
 
+from oracle import binding as ob
 from tests import synth
 
 
@@ -102,3 +104,76 @@ def test_invocation_stream_is_validated():
     with pytest.raises(RuntimeError):
         s.execute_exact_decode(rq, first, 17)           # position != draft cache length
     s.execute_exact_decode(rq, first, 16)
+
+
+def _decode(o, rq, prompt, generate):
+    first = o.prefill(prompt, 5, rq)
+    stream, pos, tok = [first], len(prompt), first
+    while len(stream) < generate + 1:
+        r = o.execute_exact_decode(rq, tok, pos)
+        stream += list(r.emitted[1:r.emitted_count]) + [r.next_token]
+        pos += r.positions_advanced
+        tok = r.next_token
+    return [int(t) for t in stream[:generate + 1]]
+
+
+@pytest.mark.parametrize("penalty_ppm", [1500000, -1000000])
+def test_presence_penalty_in_the_speculative_step_equals_plain_penalised_decoding(penalty_ppm):
+    """Greedy decoding with a presence penalty (dense_fp4_provider.cpp:8336-8347, :11182-11202,
+    :11261-11270): a verify row must be judged against the tokens emitted so far PLUS the proposals
+    before it, and accepted proposals must be committed -- then the speculative stream equals
+    token-by-token decoding with the same penalty, computed here from the target's plain logits and
+    a mask kept in the test."""
+    cfg = synth.TINY
+    model = synth.SynthModel(cfg, seed=4)
+    prompt = synth.prompt(cfg["vocab"], 48, 4)
+    rq = synth.request(context_limit=cfg["max_context"], presence_penalty_ppm=penalty_ppm,
+                       first_output_position=len(prompt) - 1)
+    got = _decode(model.oracle_session(), rq, prompt, 40)
+    # plain decoding: one target row at a time, the mask and the penalty applied by the test
+    plain = synth.request(context_limit=cfg["max_context"])
+    o = model.oracle_session()
+    o.prefill(prompt[:-1], 5, plain)
+    penalty = np.float32(penalty_ppm / 1e6)
+    mask = np.zeros(cfg["vocab"], bool)
+    want, token = [], int(prompt[-1])
+    for position in range(len(prompt) - 1, len(prompt) + 40):
+        o.prefill_at(np.array([token], np.uint32), position, 5, plain)
+        row = o.last_logits(1)[0].copy()
+        row[mask] -= penalty
+        token = int(ob.lib().qo_argmax(ob._ptr(row), row.size))
+        mask[token] = True
+        want.append(token)
+    assert got == want
+    if penalty_ppm > 0:
+        free = _decode(model.oracle_session(), synth.request(context_limit=cfg["max_context"]), prompt, 40)
+        assert got != free and len(set(got)) > len(set(free))     # the penalty does move the stream
+
+
+def test_presence_penalty_is_validated_and_neutral_by_default():
+    cfg = synth.TINY
+    model = synth.SynthModel(cfg, seed=4)
+    prompt = synth.prompt(cfg["vocab"], 32, 1)
+    a = _decode(model.oracle_session(), synth.request(context_limit=cfg["max_context"]), prompt, 16)
+    b = _decode(model.oracle_session(), synth.request(context_limit=cfg["max_context"], presence_penalty_ppm=0,
+                                                      first_output_position=7), prompt, 16)
+    assert a == b
+    with pytest.raises(RuntimeError):
+        model.oracle_session().prefill(prompt, 5, ob.Request(1, 0, 950000, 20, 0, cfg["max_context"], 4000001, 0))
+
+
+def test_sampled_presence_penalty_keeps_acceptance_consistent():
+    """Sampled mode with a penalty: reproducible, seed dependent, and the acceptance counters stay
+    within the draft depth (the proposal mask of a rollout feeds the draft distributions that the
+    next verify pass divides by)."""
+    cfg = synth.TINY
+    model = synth.SynthModel(cfg, seed=4)
+    prompt = synth.prompt(cfg["vocab"], 32, 2)
+    rq = synth.request(seed=5, temperature_ppm=800000, context_limit=cfg["max_context"], presence_penalty_ppm=700000,
+                       first_output_position=len(prompt) - 1)
+    a = _decode(model.oracle_session(), rq, prompt, 32)
+    b = _decode(model.oracle_session(), rq, prompt, 32)
+    c = _decode(model.oracle_session(), synth.request(seed=6, temperature_ppm=800000, context_limit=cfg["max_context"],
+                                                      presence_penalty_ppm=700000,
+                                                      first_output_position=len(prompt) - 1), prompt, 32)
+    assert a == b and a != c
