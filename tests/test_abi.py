@@ -65,3 +65,30 @@ def test_no_gpu_means_error_not_fallback():
     out = ctypes.c_double(0)
     assert L.qllm_k_counter_uniform_host(1, 2, 3, 4, ctypes.byref(out)) < 0
     assert b"probe alloc" in L.qllm_last_error() or L.qllm_last_error()
+
+
+def test_gemv_entry_points_reject_bad_arguments_before_any_cuda_call():
+    """Row ranges that wrap around 2^32 and misaligned operands are refused on the host (status -4,
+    QLLM_INVALID_ARGUMENT) by the caller-workspace GEMV and by the static-scratch GEMV alike; the
+    checks precede every CUDA call, so they run here without a GPU (the pointers are never read)."""
+    from quantum_llm_b200 import lib
+    L = lib.load()
+    rows, cols, batch = 256, 512, 2
+    m = lib.Matrix(0x10000, 0x20000, 1.0, 1.0, rows, cols)
+    odd = lib.Matrix(0x10001, 0x20000, 1.0, 1.0, rows, cols)
+    x, y, ws = 0x30000, 0x40000, 0x50000
+    static, plain = L.qllm_k_nvfp4_gemv_static, L.qllm_k_nvfp4_gemv
+    for first, count in ((0xFFFFFF00, 0x200), (rows, 1), (0, rows + 1), (1, 0xFFFFFFFF)):
+        assert static(ctypes.byref(m), first, count, x, y, batch, None) == -4
+        assert plain(ctypes.byref(m), first, count, x, y, batch, ws, 1 << 20, 0, None) == -4
+    assert static(ctypes.byref(m), 0, rows, x + 4, y, batch, None) == -4
+    assert static(ctypes.byref(odd), 0, rows, x, y, batch, None) == -4
+    assert plain(ctypes.byref(m), 0, rows, x + 4, y, batch, ws, 1 << 20, 0, None) == -4
+    assert plain(ctypes.byref(m), 0, rows, x, y, batch, ws + 8, 1 << 20, 0, None) == -4
+    assert plain(ctypes.byref(odd), 0, rows, x, y, batch, ws, 1 << 20, 0, None) == -4
+    assert b"boundar" in L.qllm_last_error()
+    # the static array's size limit is a host-side check too
+    limit = L.qllm_k_nvfp4_gemv_static_scratch_bytes()
+    wide = lib.Matrix(0x10000, 0x20000, 1.0, 1.0, 128, 4096)
+    assert static(ctypes.byref(wide), 0, 128, x, y, limit // 4096 + 1, None) == -4
+    assert b"static array holds" in L.qllm_last_error()
