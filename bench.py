@@ -243,6 +243,25 @@ def reference_cpu_ffn(cfg, threads):
             "gpu_ffn_layer_note": "the GPU path's FFN layer at the same widths is the gate/up GEMV + SiLU + down GEMV"}
 
 
+def reference_cpu_acceptance():
+    """The reference's OWN sampler code (runtime/src/speculative_sampling.cpp, compiled unmodified
+    into oracle/_ref) making the acceptance decisions of a speculative step on the host: five target
+    and four draft distributions over 20 sorted candidates, up to four rejection decisions, the bonus
+    sample.  The GPU path does this in one kernel on the device.  None when not built."""
+    import ctypes as C
+    from oracle import binding as ob
+    R = ob.ref_sampler()
+    if R is None or not hasattr(R, "ref_acceptance_seconds_per_step"):
+        return None
+    accepted = C.c_uint64(0)
+    seconds = R.ref_acceptance_seconds_per_step(20000, 20, 7, C.byref(accepted))
+    if not seconds > 0.0:
+        return None
+    return {"kind": "_ref", "what": "make_sampling_distribution x 9 + rejection_sample x <= 4 + bonus sample per step, "
+            "top_k 20, 20000 steps on one thread", "us_per_step": seconds * 1e6, "cores": 1,
+            "accepted_per_step": accepted.value / 20000.0}
+
+
 def algorithmic_step_bytes(cfg, context):
     """Bytes one MTP-4 step must read: verify weights + target KV + 4 draft passes."""
     nv = lambda r, c: r * c * 9 // 16   # NVFP4: 4-bit codes + one E4M3 scale per 16
@@ -296,7 +315,8 @@ def reference_arm(args):
                        "parallelism": "host cores of rank 0", "implementation": "CPU port of the reference arithmetic"},
             "accepted_len_per_step": tokens / args.steps,
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.threads, "kind": "port", "sample": text,
-                             "reference_ffn": reference_cpu_ffn(DENSE_27B, sample.threads)},
+                             "reference_ffn": reference_cpu_ffn(DENSE_27B, sample.threads),
+                             "reference_acceptance": reference_cpu_acceptance()},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -638,6 +658,7 @@ def ours(args):
             "how": f"measured {per_step:.3f} s per step with {REFERENCE_LAYERS} layers and {shallow_seconds:.3f} s with 1: "
                    f"{per_layer:.3f} s per layer x {DENSE_27B['layers']} layers + the rest"}
         line["cpu_baseline"]["reference_ffn"] = reference_cpu_ffn(DENSE_27B, line["cpu_baseline"]["cores"])
+        line["cpu_baseline"]["reference_acceptance"] = reference_cpu_acceptance()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -84,7 +84,10 @@ def build(force=False):
     # (reference_root()); prebuilt files are kept otherwise
     refs = [os.path.join(HERE, "_ref", name) for name in ("libqllm_ref_sampler.so", "libqllm_ref_descriptor.so")]
     reference = reference_root()
-    if (force or not all(os.path.exists(r) for r in refs)) and reference and os.path.isdir(reference):
+    shims = [os.path.join(HERE, name) for name in ("ref_sampler_shim.cpp", "ref_descriptor_shim.cpp")]
+    stale = not all(os.path.exists(r) for r in refs) or any(
+        os.path.getmtime(r) < os.path.getmtime(sh) for r, sh in zip(refs, shims))
+    if (force or stale) and reference and os.path.isdir(reference):
         subprocess.run(["make", "-C", HERE, "ref", f"REFERENCE={reference}"], check=True, stdout=subprocess.DEVNULL)
     # the reference's own CUDA kernels (GPU pins of the oracle): built once, where the reference tree lies
     kernels = os.path.join(HERE, "_ref", "libqllm_ref_kernels.so")
@@ -169,6 +172,9 @@ def ref_sampler():
         R.ref_counter_uniform.restype, R.ref_counter_uniform.argtypes = f64, [u64, u32, u32, u32]
         R.ref_make_distribution.restype = C.c_int
         R.ref_make_distribution.argtypes = [vp, vp, u32, u32, u32, u32, vp, vp]
+        if hasattr(R, "ref_acceptance_seconds_per_step"):
+            R.ref_acceptance_seconds_per_step.restype = C.c_double
+            R.ref_acceptance_seconds_per_step.argtypes = [u32, u32, C.c_uint64, C.POINTER(C.c_uint64)]
         R.ref_sample_distribution.restype = C.c_int
         R.ref_sample_distribution.argtypes = [vp, vp, u32, f64, vp]
         R.ref_rejection_sample.restype = C.c_int
