@@ -7,10 +7,9 @@ both sides penalise the logits rows in place, as the reference does -- the same 
 verify row, for a positive and a negative penalty, greedy and sampled, and in the scalar decode
 fallback.
 
-These tests were written after GPU access for this repository had been closed for the rest of the
-build, so they have not run on a GPU yet; they are marked xfail(strict=False) for that reason only
-(a pass is reported as XPASS), and sit in a file collected late so that nothing else depends on
-them.
+These tests have not been run on a GPU yet (no device was available when they were written); they
+are marked xfail(strict=False) for that reason only -- a pass is reported as XPASS -- and sit in a
+file collected late so that nothing else depends on them.
 """
 import numpy as np
 import pytest
@@ -19,7 +18,7 @@ from tests import synth
 from tests.gpu_util import provider_from_synth, request_pair
 
 pytestmark = [pytest.mark.gpu,
-              pytest.mark.xfail(strict=False, reason="written after GPU access was closed: not yet run on a GPU")]
+              pytest.mark.xfail(strict=False, reason="not yet run on a GPU")]
 
 CFG = dict(synth.TINY)
 PROMPT = 40
