@@ -20,10 +20,16 @@
  *   runtime/tools/dense_fp4_provider.cpp:8529-8852    run_target / run_mtp / rollout
  *   runtime/tools/dense_fp4_provider.cpp:11011-11318  sync batch / execute_exact_decode
  *
- * Parity pin status: the sampler, the counter RNG and the E2M1/E4M3 decoders
- * are pinned against the reference's own code and vectors (see tests/);
- * the whole-step token sequences are "parity unpinned" because the reference
- * holds no end-to-end vector for its MTP loop.
+ * Parity pin status: the sampler (incl. the whole-row sampler of the scalar
+ * fallback), the counter RNG and the E2M1/E4M3 decoders are pinned on the CPU
+ * against the reference's own code and vectors; the NVFP4 GEMV and activation
+ * quantiser, the Q4H and Q8 record bytes, Q4H and Q8 attention, argmax and
+ * top-k are pinned on the GPU against the reference's own CUDA kernels
+ * compiled unmodified for sm_100a (oracle/_ref, tests/test_reference_kernels.py).
+ * The control flow of the whole step (accepted-token sequences) is "parity
+ * unpinned": the reference holds no end-to-end vector for its MTP loop; it is
+ * protected by invariants instead (speculative run == plain run, with and
+ * without a presence penalty; rollback leaves the state identical).
  */
 #ifndef QLLM_ORACLE_H_
 #define QLLM_ORACLE_H_
