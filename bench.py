@@ -85,6 +85,8 @@ def parse():
     ap.add_argument("--split-tokens", type=int, default=0,
                     help="cached tokens per attention CTA (multiple of 64; 0 = the model configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-full-step", action="store_true",
+                    help="skip the one whole 64-layer step of the CPU port (half a minute of host time)")
     ap.add_argument("--microbench", action="store_true",
                     help="kernel microbenchmark of the NVFP4 GEMV on the verify-step shapes at M = 5, 40, 128, 160, 640")
     ap.add_argument("--prefill-bench", type=int, default=0, metavar="TOKENS",
@@ -158,7 +160,7 @@ class OracleSteps:
     synthetic records the GPU arm uses, the last 8 prompt tokens run for real.  Nothing is scaled:
     the reported rate is that of the sliced model, and the slice is named in the JSON line."""
 
-    def __init__(self, cfg, context, layers=2, threads=None):
+    def __init__(self, cfg, context, layers=2, threads=None, share_layer_bytes=False):
         import numpy as np
         from oracle import binding as ob
         self.ob, self.O = ob, ob.lib()
@@ -191,7 +193,15 @@ class OracleSteps:
         embedding = (rng.integers(0x3c00, 0x3d00, (V, H), dtype=np.uint16) |
                      (rng.integers(0, 2, (V, H), dtype=np.uint16) << 15))
         keep.append(embedding)
-        blocks = (ob.Block * layers)(*[block() for _ in range(layers)])
+        # share_layer_bytes: every target layer points at ONE layer's random bytes.  The arithmetic and
+        # the memory traffic per layer are those of distinct layers (a layer is 186 MB, far beyond any
+        # last-level cache), the host needs 0.2 GB instead of 12 GB and no minute of random-number
+        # generation -- which is what lets a whole 64-layer step be timed for real.
+        if share_layer_bytes:
+            one = block()
+            blocks = (ob.Block * layers)(*[one for _ in range(layers)])
+        else:
+            blocks = (ob.Block * layers)(*[block() for _ in range(layers)])
         weights = ob.Weights(ob._ptr(embedding), blocks, ones(), matrix(V, H), ones(), ones(), matrix(H, 2 * H),
                              block(), ones())
         config = ob.Config()
@@ -208,7 +218,10 @@ class OracleSteps:
         self.context = context
         self.description = (f"real speculative steps of the oracle port on a {layers}-layer slice of the "
                             f"{cfg['layers']}-layer model (full widths, vocabulary and {context}-token Q4H/Q8 caches; "
-                            f"nothing scaled)")
+                            f"nothing scaled)") if layers != cfg["layers"] else (
+            f"a real speculative step of the oracle port on all {layers} layers (full widths, vocabulary and "
+            f"{context}-token Q4H/Q8 caches; the layers share one layer's random weight bytes, 186 MB per layer "
+            f"streamed from memory each time)")
 
     def step(self):
         """One speculative step; returns (seconds, tokens emitted)."""
@@ -306,6 +319,15 @@ def reference_arm(args):
         tokens += n
     value = tokens / seconds
     text = f"{sample.description}; {args.steps} timed steps on {sample.threads} threads"
+    threads = sample.threads
+    del sample
+    whole_step = None
+    if not args.no_cpu_full_step:   # one whole step of all 64 layers, measured
+        whole_model = OracleSteps(DENSE_27B, args.context, DENSE_27B["layers"], share_layer_bytes=True)
+        step_seconds, step_tokens = whole_model.step()
+        whole_step = {"value": step_tokens / step_seconds, "unit": "tok/s", "seconds_per_step": step_seconds,
+                      "cores": whole_model.threads, "kind": "port", "sample": whole_model.description}
+        del whole_model
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4xnvfp4->f32",
@@ -314,8 +336,9 @@ def reference_arm(args):
                        "layers_of_the_model": DENSE_27B["layers"],
                        "parallelism": "host cores of rank 0", "implementation": "CPU port of the reference arithmetic"},
             "accepted_len_per_step": tokens / args.steps,
-            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.threads, "kind": "port", "sample": text,
-                             "reference_ffn": reference_cpu_ffn(DENSE_27B, sample.threads),
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": text,
+                             "whole_model_step": whole_step,
+                             "reference_ffn": reference_cpu_ffn(DENSE_27B, threads),
                              "reference_acceptance": reference_cpu_acceptance()},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -635,7 +658,8 @@ def ours(args):
     }
     if tensor_parallel:
         line["step_bytes_scope"] = "per GPU: this rank's shard of the blocks and of the KV, plus the replicated heads"
-    if not args.no_cpu_baseline and not routed:
+    # the CPU leg runs at N = 1 only: at N > 1 the other ranks would sit in the closing barrier meanwhile
+    if not args.no_cpu_baseline and not routed and world == 1:
         sample = OracleSteps(DENSE_27B, context, REFERENCE_LAYERS)
         sample.step()
         seconds, tokens, steps = 0.0, 0, 0
@@ -653,12 +677,21 @@ def ours(args):
         shallow_seconds = sum(shallow.step()[0] for _ in range(3)) / 3.0
         per_layer = max(per_step - shallow_seconds, 0.0) / (REFERENCE_LAYERS - 1)
         whole = per_step + (DENSE_27B["layers"] - REFERENCE_LAYERS) * per_layer
+        del shallow
         line["cpu_baseline"]["whole_model_estimate"] = {
             "value": (tokens / steps) / whole, "unit": "tok/s", "seconds_per_step": whole,
             "how": f"measured {per_step:.3f} s per step with {REFERENCE_LAYERS} layers and {shallow_seconds:.3f} s with 1: "
                    f"{per_layer:.3f} s per layer x {DENSE_27B['layers']} layers + the rest"}
         line["cpu_baseline"]["reference_ffn"] = reference_cpu_ffn(DENSE_27B, line["cpu_baseline"]["cores"])
         line["cpu_baseline"]["reference_acceptance"] = reference_cpu_acceptance()
+        # ... and one whole step measured, all 64 layers (about as long as the estimate says)
+        if not args.no_cpu_full_step:
+            whole_model = OracleSteps(DENSE_27B, context, DENSE_27B["layers"], share_layer_bytes=True)
+            step_seconds, step_tokens = whole_model.step()
+            line["cpu_baseline"]["whole_model_step"] = {
+                "value": step_tokens / step_seconds, "unit": "tok/s", "seconds_per_step": step_seconds,
+                "cores": whole_model.threads, "kind": "port", "sample": whole_model.description}
+            del whole_model
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

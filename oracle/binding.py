@@ -307,7 +307,10 @@ class Session:
             self.h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:   # interpreter shutdown: the module globals may be gone already
+            pass
 
     def prefill(self, tokens, chunk_rows, request):
         tokens = np.ascontiguousarray(tokens, np.uint32)
